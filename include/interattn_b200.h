@@ -1,0 +1,187 @@
+/*
+ * interattn_b200 - C ABI of the B200 (sm_100a) condition-block sparse
+ * decode-attention path.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers and sizes,
+ * enqueues its kernels on the given CUDA stream and returns immediately with
+ * an `ia_status`.  Unless an entry point's comment says otherwise it allocates
+ * nothing, synchronises nothing and keeps no state; all device memory,
+ * including scratch, belongs to the caller.  Calls are CUDA-graph capturable:
+ * per-step quantities (sequence lengths, selection results) are read from
+ * device memory.
+ *
+ * Reference interfaces these entry points stand behind (paths relative to the
+ * reference project; IMPL = llama/script/analysis/condition_block_gen/methods/
+ * condition_block_triton_impl):
+ *   ia_build_summaries  <- _build_prompt_blocks                 IMPL/core.py:449-500
+ *   ia_select           <- _run_condition_block_selection_stats IMPL/core.py:573-698
+ *                          + the routing half of the fused finalize kernel
+ *                            IMPL/page_attention.py:84-171, and the eager rule
+ *                            _select_prompt_blocks_eager        IMPL/core.py:509-555
+ *   ia_sparse_decode    <- _condition_block_finalize_attention_kernel
+ *                            IMPL/page_attention.py:173-309 (attention half)
+ *   ia_finalize         <- _condition_block_stage2_reduce_kernel IMPL/legacy.py:765-794
+ *   ia_decode_attention <- _condition_block_decode_output_fused_triton
+ *                            IMPL/core.py:1035-1155 (the three launches of one layer-step)
+ *
+ * Tensor conventions
+ *   q            [batch, n_kv_heads * group_size, head_dim]   dtype; query head = kv * G + g
+ *   k_pool/v_pool physical KV pages; element (page p, kv head h, token t, dim d) lives at
+ *                p * pool_page_stride + h * pool_head_stride + t * head_dim + d   (dtype)
+ *                so one (page, kv head) is a contiguous page_size x head_dim run.
+ *   block_table  int32 [batch, max_pages]; entry j = physical page of logical tokens
+ *                [j * page_size, (j + 1) * page_size)
+ *   prefix_lens  int32 [batch]; tokens covered by block summaries (the prompt)
+ *   seq_lens     int32 [batch]; all visible tokens (prefix + generated suffix)
+ *   summaries    per (sequence, kv head, logical block): see ia_summaries
+ *   sel_idx      int32 [batch, n_kv_heads, max_sel] ascending block indices
+ *   sel_count    int32 [batch, n_kv_heads]
+ */
+#ifndef INTERATTN_B200_H_
+#define INTERATTN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* ia_stream_t; /* same type as cudaStream_t */
+
+typedef enum ia_status {
+  IA_OK = 0,
+  IA_ERR_BAD_ARG = -1,      /* null pointer, non-positive size, inconsistent geometry */
+  IA_ERR_UNSUPPORTED = -2,  /* geometry outside what the kernels are built for */
+  IA_ERR_LAUNCH = -3,       /* CUDA reported an error at launch */
+  IA_ERR_NO_DEVICE = -4
+} ia_status;
+
+typedef enum ia_dtype { IA_F32 = 0, IA_BF16 = 1 } ia_dtype;
+typedef enum ia_select_mode { IA_SELECT_TOPK = 0, IA_SELECT_EPS = 1 } ia_select_mode;
+typedef enum ia_rep_mode {
+  IA_REP_SPARSE_ONLY = 0, /* selected blocks + suffix */
+  IA_REP_HYBRID = 1       /* + one (z, v_bar) representative per unselected block */
+} ia_rep_mode;
+
+typedef struct ia_geom {
+  int32_t batch;
+  int32_t n_kv_heads;
+  int32_t group_size;   /* query heads per kv head (1..16) */
+  int32_t head_dim;     /* 64 or 128 */
+  int32_t page_size;    /* tokens per physical page: 16 */
+  int32_t block_size;   /* tokens per selection block: multiple of page_size, <= 128 */
+  int32_t max_pages;    /* row length of block_table */
+  int32_t max_blocks;   /* blocks per (sequence, kv head) in the summary arrays */
+  int32_t dtype;        /* ia_dtype of q, pools, k_max/k_min/v_bar */
+  int32_t reserved;
+  int64_t pool_page_stride; /* in elements */
+  int64_t pool_head_stride; /* in elements */
+} ia_geom;
+
+/* Block summaries, "mixed" storage of the reference (IMPL/core.py:411-446):
+ * means accumulated in fp32, k_bar kept in fp32, the rest in the KV dtype
+ * (the coordinate bounds are copies of K values, so that is lossless). */
+typedef struct ia_summaries {
+  float* k_bar;      /* [batch, n_kv_heads, max_blocks, head_dim] f32 */
+  void* k_max;       /* same shape, dtype */
+  void* k_min;       /* same shape, dtype */
+  void* v_bar;       /* same shape, dtype */
+  float* v_norm_max; /* [batch, n_kv_heads, max_blocks] f32: max token |v|_2 in the block */
+} ia_summaries;
+
+/* Optional diagnostics of ia_select; any pointer may be null. */
+typedef struct ia_select_aux {
+  float* score;   /* [batch, n_kv_heads, max_blocks]  GQA-mean condition score */
+  float* z;       /* [batch, rows, max_blocks]  s + log(count); needed by IA_REP_HYBRID */
+  float* s;       /* [batch, rows, max_blocks]  q.k_bar / sqrt(D) */
+  float* delta;   /* [batch, rows, max_blocks]  range bound */
+  float* globals; /* [batch, 4, rows]  z_m, z_l, c_m, c_l (online-softmax normalisers) */
+} ia_select_aux;
+
+/* Version of this ABI; bumped on any incompatible change. */
+int ia_abi_version(void);
+
+/* Message for the last non-OK status returned on the calling thread. */
+const char* ia_last_error_string(void);
+
+/* Reads and clears the device status word: bit 0 is set when a bounded
+ * shared-memory barrier wait inside the selection kernel ran out (its results
+ * are then invalid).  Synchronises the device; a debugging aid. */
+int ia_read_device_status(int* out);
+
+/* Replaces _build_prompt_blocks (IMPL/core.py:449-500): one pass over the K/V
+ * pages of every sequence's prefix through the block table. */
+int ia_build_summaries(const void* k_pool, const void* v_pool, const int32_t* block_table,
+                       const int32_t* prefix_lens, const ia_geom* geom, const ia_summaries* out,
+                       ia_stream_t stream);
+
+/* Replaces the selection stats kernel plus the routing decision
+ * (IMPL/core.py:751-814, IMPL/page_attention.py:84-171): condition score of
+ * every block, then either the top_k best blocks per (sequence, kv head) -
+ * higher score first, lower block index first among equal scores - or every
+ * block whose score exceeds eps (the reference rule, IMPL/core.py:546).
+ * Indices are written in ascending order; entries past sel_count are -1.
+ * The score vector stays on chip unless aux asks for it. */
+int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefix_lens,
+              const ia_geom* geom, int mode, int top_k, float eps, int max_sel,
+              int32_t* sel_idx, int32_t* sel_count, const ia_select_aux* aux, ia_stream_t stream);
+
+/* Replaces the attention half of the fused finalize kernel
+ * (IMPL/page_attention.py:173-309): online-softmax attention of the G query
+ * rows of each kv head over the tokens of the selected blocks (gathered page
+ * by page through the block table), the generated suffix
+ * [prefix_len, seq_len) and, in IA_REP_HYBRID, the representatives of the
+ * unselected blocks (logit z from ia_select, value v_bar).  The work of one
+ * (sequence, kv head) is cut into n_splits parts; part s writes a normalised
+ * partial output and its log-sum-exp:
+ *   o_partial   f32 [batch, rows, n_splits, head_dim]
+ *   lse_partial f32 [batch, rows, n_splits]       (-inf for an empty part)
+ * block_lo/block_hi (blocks, hi exclusive; pass 0 / max_blocks for all) and
+ * with_suffix restrict the call to one rank's share in multi-GPU split-KV. */
+int ia_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
+                     const int32_t* block_table, const int32_t* prefix_lens,
+                     const int32_t* seq_lens, const int32_t* sel_idx, const int32_t* sel_count,
+                     int max_sel, const ia_summaries* summaries, const float* z,
+                     const ia_geom* geom, int rep_mode, int n_splits, int block_lo, int block_hi,
+                     int with_suffix, float* o_partial, float* lse_partial, ia_stream_t stream);
+
+/* Replaces _condition_block_stage2_reduce_kernel (IMPL/legacy.py:765-794),
+ * written for (o, lse) partials: out = sum_s o_s e^{lse_s - M} / sum_s
+ * e^{lse_s - M}.  n_rows = batch * rows.  out_dtype is an ia_dtype; out_lse
+ * (f32 [n_rows], may be null) receives the merged log-sum-exp so that the
+ * result can itself be merged again (across GPUs). */
+int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts,
+                int head_dim, void* out, int out_dtype, float* out_lse, ia_stream_t stream);
+
+/* Scratch needed by ia_decode_attention, in bytes. */
+int64_t ia_workspace_bytes(const ia_geom* geom, int max_sel, int n_splits, int rep_mode);
+
+/* One decode-attention layer-step: ia_select, ia_sparse_decode and
+ * ia_finalize on one stream, replacing _condition_block_decode_output_fused_triton
+ * (IMPL/core.py:1035-1155).  workspace: ia_workspace_bytes() bytes, 256-byte
+ * aligned.  out [batch, rows, head_dim] in geom->dtype.  sel_idx/sel_count
+ * may be null (the selection then lives in the workspace). */
+int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool,
+                        const int32_t* block_table, const int32_t* prefix_lens,
+                        const int32_t* seq_lens, const ia_summaries* summaries,
+                        const ia_geom* geom, int mode, int top_k, float eps, int max_sel,
+                        int rep_mode, int n_splits, void* workspace, int64_t workspace_bytes,
+                        int32_t* sel_idx, int32_t* sel_count, void* out, ia_stream_t stream);
+
+/* The same layer-step with HOST buffers, for callers that keep only the KV
+ * pool and the summaries on the device: copies q_host -> device (async on
+ * stream), runs ia_decode_attention, copies the output back into out_host and
+ * waits for the stream.  q_dev/out_dev are caller-owned device staging
+ * buffers of the same sizes; q_host/out_host should be pinned. */
+int ia_decode_attention_host(const void* q_host, void* q_dev, const void* k_pool,
+                             const void* v_pool, const int32_t* block_table,
+                             const int32_t* prefix_lens, const int32_t* seq_lens,
+                             const ia_summaries* summaries, const ia_geom* geom, int mode,
+                             int top_k, float eps, int max_sel, int rep_mode, int n_splits,
+                             void* workspace, int64_t workspace_bytes, void* out_dev,
+                             void* out_host, ia_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INTERATTN_B200_H_ */

@@ -1,0 +1,236 @@
+// extern "C" surface of libinterattn_b200.so: argument checks, status
+// plumbing and the one-call layer-step.  Declarations and the reference
+// interfaces they replace: include/interattn_b200.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "ia_common.cuh"
+
+namespace ia {
+
+static thread_local char tls_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tls_error, sizeof(tls_error), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tls_error, sizeof(tls_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return IA_OK;
+  return fail(IA_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_geom(const ia_geom* g) {
+  if (g == nullptr) return fail(IA_ERR_BAD_ARG, "geom is null");
+  if (g->batch < 0 || g->n_kv_heads <= 0 || g->group_size <= 0)
+    return fail(IA_ERR_BAD_ARG, "geom: batch %d, n_kv_heads %d, group_size %d", g->batch, g->n_kv_heads, g->group_size);
+  if (g->head_dim != 64 && g->head_dim != 128)
+    return fail(IA_ERR_UNSUPPORTED, "geom: head_dim %d (built: 64, 128)", g->head_dim);
+  if (g->page_size != 16) return fail(IA_ERR_UNSUPPORTED, "geom: page_size %d (built: 16)", g->page_size);
+  if (g->block_size <= 0 || g->block_size % g->page_size != 0 || g->block_size > 128)
+    return fail(IA_ERR_BAD_ARG, "geom: block_size %d must be a multiple of page_size %d, at most 128", g->block_size,
+                g->page_size);
+  if (g->group_size > 16) return fail(IA_ERR_UNSUPPORTED, "geom: group_size %d (built: up to 16)", g->group_size);
+  if (g->max_pages <= 0 || g->max_blocks <= 0)
+    return fail(IA_ERR_BAD_ARG, "geom: max_pages %d, max_blocks %d", g->max_pages, g->max_blocks);
+  if (g->dtype != IA_F32 && g->dtype != IA_BF16) return fail(IA_ERR_BAD_ARG, "geom: dtype %d", g->dtype);
+  const int64_t run = (int64_t)g->page_size * g->head_dim;
+  if (g->pool_head_stride < run || g->pool_page_stride < run)
+    return fail(IA_ERR_BAD_ARG, "geom: pool strides (%lld, %lld) smaller than one page run %lld",
+                (long long)g->pool_page_stride, (long long)g->pool_head_stride, (long long)run);
+  const int64_t esz = g->dtype == IA_BF16 ? 2 : 4;
+  if ((g->pool_head_stride * esz) % 16 != 0 || (g->pool_page_stride * esz) % 16 != 0)
+    return fail(IA_ERR_BAD_ARG, "geom: pool strides must be multiples of 16 bytes");
+  return IA_OK;
+}
+
+static int check_summaries(const ia_summaries* s) {
+  if (s == nullptr) return fail(IA_ERR_BAD_ARG, "summaries is null");
+  if (!s->k_bar || !s->k_max || !s->k_min || !s->v_bar || !s->v_norm_max)
+    return fail(IA_ERR_BAD_ARG, "summaries: null member");
+  if (!aligned16(s->k_bar) || !aligned16(s->k_max) || !aligned16(s->k_min) || !aligned16(s->v_bar))
+    return fail(IA_ERR_BAD_ARG, "summaries: arrays must be 16-byte aligned");
+  return IA_OK;
+}
+
+struct Workspace {
+  int32_t* sel_idx;
+  int32_t* sel_count;
+  float* z;
+  float* o_partial;
+  float* lse_partial;
+  int64_t bytes;
+};
+
+static int64_t align256(int64_t x) { return (x + 255) & ~int64_t(255); }
+
+static Workspace carve(const ia_geom& g, int max_sel, int n_splits, int rep_mode, void* base) {
+  Workspace w{};
+  const int64_t pairs = (int64_t)g.batch * g.n_kv_heads;
+  const int64_t rows = pairs * g.group_size;
+  char* p = static_cast<char*>(base);
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) {
+    char* r = p ? p + off : nullptr;
+    off += align256(bytes);
+    return r;
+  };
+  w.sel_idx = reinterpret_cast<int32_t*>(take(pairs * max_sel * 4));
+  w.sel_count = reinterpret_cast<int32_t*>(take(pairs * 4));
+  w.z = reinterpret_cast<float*>(take(rep_mode == IA_REP_HYBRID ? rows * g.max_blocks * 4 : 0));
+  w.o_partial = reinterpret_cast<float*>(take(rows * n_splits * g.head_dim * 4));
+  w.lse_partial = reinterpret_cast<float*>(take(rows * n_splits * 4));
+  w.bytes = off;
+  return w;
+}
+
+}  // namespace ia
+
+using namespace ia;
+
+extern "C" {
+
+int ia_abi_version(void) { return 1; }
+
+const char* ia_last_error_string(void) { return tls_error; }
+
+// Reads and clears the device status word (bit 0: a bounded mbarrier wait in
+// the selection kernel ran out).  Synchronises the device; a debugging aid,
+// not part of the step.
+int ia_read_device_status(int* out) {
+  if (out == nullptr) return fail(IA_ERR_BAD_ARG, "out is null");
+  return read_and_clear_device_status(out);
+}
+
+int ia_build_summaries(const void* k_pool, const void* v_pool, const int32_t* block_table,
+                       const int32_t* prefix_lens, const ia_geom* geom, const ia_summaries* out,
+                       ia_stream_t stream) {
+  if (int s = check_geom(geom)) return s;
+  if (int s = check_summaries(out)) return s;
+  if (!k_pool || !v_pool || !block_table || !prefix_lens) return fail(IA_ERR_BAD_ARG, "build_summaries: null argument");
+  if (!aligned16(k_pool) || !aligned16(v_pool)) return fail(IA_ERR_BAD_ARG, "build_summaries: pools must be 16-byte aligned");
+  return launch_build_summaries(k_pool, v_pool, block_table, prefix_lens, *geom, *out, (cudaStream_t)stream);
+}
+
+int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefix_lens,
+              const ia_geom* geom, int mode, int top_k, float eps, int max_sel, int32_t* sel_idx,
+              int32_t* sel_count, const ia_select_aux* aux, ia_stream_t stream) {
+  if (int s = check_geom(geom)) return s;
+  if (int s = check_summaries(summaries)) return s;
+  if (!q || !prefix_lens || !sel_idx || !sel_count) return fail(IA_ERR_BAD_ARG, "select: null argument");
+  if (mode != IA_SELECT_TOPK && mode != IA_SELECT_EPS) return fail(IA_ERR_BAD_ARG, "select: mode %d", mode);
+  if (max_sel <= 0) return fail(IA_ERR_BAD_ARG, "select: max_sel %d", max_sel);
+  if (mode == IA_SELECT_TOPK && (top_k < 0 || top_k > max_sel))
+    return fail(IA_ERR_BAD_ARG, "select: top_k %d outside [0, max_sel %d]", top_k, max_sel);
+  if (mode == IA_SELECT_EPS && max_sel < geom->max_blocks)
+    return fail(IA_ERR_BAD_ARG, "select: epsilon mode may keep every block: max_sel %d < max_blocks %d", max_sel,
+                geom->max_blocks);
+  ia_select_aux none{};
+  return launch_select(q, *summaries, prefix_lens, *geom, mode, top_k, eps, max_sel, sel_idx, sel_count,
+                       aux ? *aux : none, (cudaStream_t)stream);
+}
+
+int ia_sparse_decode(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                     const int32_t* prefix_lens, const int32_t* seq_lens, const int32_t* sel_idx,
+                     const int32_t* sel_count, int max_sel, const ia_summaries* summaries, const float* z,
+                     const ia_geom* geom, int rep_mode, int n_splits, int block_lo, int block_hi,
+                     int with_suffix, float* o_partial, float* lse_partial, ia_stream_t stream) {
+  if (int s = check_geom(geom)) return s;
+  if (!q || !k_pool || !v_pool || !block_table || !prefix_lens || !seq_lens || !sel_idx || !sel_count ||
+      !o_partial || !lse_partial)
+    return fail(IA_ERR_BAD_ARG, "sparse_decode: null argument");
+  if (!aligned16(k_pool) || !aligned16(v_pool) || !aligned16(q))
+    return fail(IA_ERR_BAD_ARG, "sparse_decode: q and pools must be 16-byte aligned");
+  if (rep_mode != IA_REP_SPARSE_ONLY && rep_mode != IA_REP_HYBRID)
+    return fail(IA_ERR_BAD_ARG, "sparse_decode: rep_mode %d", rep_mode);
+  if (rep_mode == IA_REP_HYBRID) {
+    if (!summaries || !summaries->v_bar || !z)
+      return fail(IA_ERR_BAD_ARG, "sparse_decode: hybrid mode needs summaries->v_bar and z");
+    if (!aligned16(summaries->v_bar)) return fail(IA_ERR_BAD_ARG, "sparse_decode: v_bar must be 16-byte aligned");
+  }
+  if (n_splits <= 0 || n_splits > 64) return fail(IA_ERR_BAD_ARG, "sparse_decode: n_splits %d outside [1, 64]", n_splits);
+  if (max_sel <= 0) return fail(IA_ERR_BAD_ARG, "sparse_decode: max_sel %d", max_sel);
+  if (block_lo < 0 || block_hi < block_lo) return fail(IA_ERR_BAD_ARG, "sparse_decode: block range [%d, %d)", block_lo, block_hi);
+  return launch_sparse_decode(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, sel_idx, sel_count, max_sel,
+                              summaries, z, *geom, rep_mode, n_splits, block_lo, block_hi, with_suffix, o_partial,
+                              lse_partial, (cudaStream_t)stream);
+}
+
+int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts, int head_dim,
+                void* out, int out_dtype, float* out_lse, ia_stream_t stream) {
+  if (!o_partial || !lse_partial || !out) return fail(IA_ERR_BAD_ARG, "finalize: null argument");
+  if (n_rows < 0 || n_parts <= 0) return fail(IA_ERR_BAD_ARG, "finalize: n_rows %d, n_parts %d", n_rows, n_parts);
+  return launch_finalize(o_partial, lse_partial, n_rows, n_parts, head_dim, out, out_dtype, out_lse,
+                         (cudaStream_t)stream);
+}
+
+int64_t ia_workspace_bytes(const ia_geom* geom, int max_sel, int n_splits, int rep_mode) {
+  if (check_geom(geom) != IA_OK || max_sel <= 0 || n_splits <= 0) return -1;
+  return carve(*geom, max_sel, n_splits, rep_mode, nullptr).bytes;
+}
+
+int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                        const int32_t* prefix_lens, const int32_t* seq_lens, const ia_summaries* summaries,
+                        const ia_geom* geom, int mode, int top_k, float eps, int max_sel, int rep_mode,
+                        int n_splits, void* workspace, int64_t workspace_bytes, int32_t* sel_idx,
+                        int32_t* sel_count, void* out, ia_stream_t stream) {
+  if (int s = check_geom(geom)) return s;
+  if (!workspace || !out) return fail(IA_ERR_BAD_ARG, "decode_attention: null workspace or out");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    return fail(IA_ERR_BAD_ARG, "decode_attention: workspace must be 256-byte aligned");
+  if (max_sel <= 0 || n_splits <= 0) return fail(IA_ERR_BAD_ARG, "decode_attention: max_sel %d, n_splits %d", max_sel, n_splits);
+  Workspace w = carve(*geom, max_sel, n_splits, rep_mode, workspace);
+  if (workspace_bytes < w.bytes)
+    return fail(IA_ERR_BAD_ARG, "decode_attention: workspace %lld bytes, need %lld", (long long)workspace_bytes,
+                (long long)w.bytes);
+  int32_t* idx = sel_idx ? sel_idx : w.sel_idx;
+  int32_t* cnt = sel_count ? sel_count : w.sel_count;
+  ia_select_aux aux{};
+  if (rep_mode == IA_REP_HYBRID) aux.z = w.z;
+  if (int s = ia_select(q, summaries, prefix_lens, geom, mode, top_k, eps, max_sel, idx, cnt, &aux, stream)) return s;
+  if (int s = ia_sparse_decode(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, idx, cnt, max_sel, summaries,
+                               w.z, geom, rep_mode, n_splits, 0, geom->max_blocks, 1, w.o_partial, w.lse_partial,
+                               stream))
+    return s;
+  const int n_rows = geom->batch * geom->n_kv_heads * geom->group_size;
+  return ia_finalize(w.o_partial, w.lse_partial, n_rows, n_splits, geom->head_dim, out, geom->dtype, nullptr, stream);
+}
+
+int ia_decode_attention_host(const void* q_host, void* q_dev, const void* k_pool, const void* v_pool,
+                             const int32_t* block_table, const int32_t* prefix_lens, const int32_t* seq_lens,
+                             const ia_summaries* summaries, const ia_geom* geom, int mode, int top_k, float eps,
+                             int max_sel, int rep_mode, int n_splits, void* workspace, int64_t workspace_bytes,
+                             void* out_dev, void* out_host, ia_stream_t stream) {
+  if (int s = check_geom(geom)) return s;
+  if (!q_host || !q_dev || !out_dev || !out_host) return fail(IA_ERR_BAD_ARG, "decode_attention_host: null buffer");
+  const size_t esz = geom->dtype == IA_BF16 ? 2 : 4;
+  const size_t bytes = (size_t)geom->batch * geom->n_kv_heads * geom->group_size * geom->head_dim * esz;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemcpyAsync(q_dev, q_host, bytes, cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "decode_attention_host: h2d: %s", cudaGetErrorString(e));
+  if (int s = ia_decode_attention(q_dev, k_pool, v_pool, block_table, prefix_lens, seq_lens, summaries, geom, mode,
+                                  top_k, eps, max_sel, rep_mode, n_splits, workspace, workspace_bytes, nullptr,
+                                  nullptr, out_dev, stream))
+    return s;
+  e = cudaMemcpyAsync(out_host, out_dev, bytes, cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "decode_attention_host: d2h: %s", cudaGetErrorString(e));
+  return IA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,124 @@
+// Work list of one (sequence, kv head, split) of the sparse decode-attention
+// kernels.  The list is the concatenation of
+//   * the physical pages of the selected blocks that fall into the block range,
+//   * (hybrid mode) tiles of 16 consecutive blocks whose unselected members
+//     contribute their representative (z, v_bar),
+//   * the pages of the generated suffix [prefix_len, seq_len).
+// Split s of n owns the items [N s / n, N (s + 1) / n).  Descriptors are
+// resolved (selection list -> block table -> physical page) by all threads at
+// once and parked in shared memory, so that the load pipeline never waits on a
+// dependent global load.
+#pragma once
+
+#include "ia_common.cuh"
+
+namespace ia {
+
+struct DecodeParams {
+  const void* q;
+  const void* k_pool;
+  const void* v_pool;
+  const int32_t* block_table;
+  const int32_t* prefix_lens;
+  const int32_t* seq_lens;
+  const int32_t* sel_idx;
+  const int32_t* sel_count;
+  const void* v_bar;  // hybrid only
+  const float* z;     // hybrid only: [batch, rows, max_blocks]
+  float* o_partial;
+  float* lse_partial;
+  int64_t page_stride, head_stride;
+  int n_kv_heads, group_size, page_size, block_size, max_pages, max_blocks, max_sel;
+  int rep_mode, n_splits, block_lo, block_hi, with_suffix;
+};
+
+enum : int { ITEM_PAGE = 0, ITEM_REP_TILE = 1 };
+constexpr int kRepTile = 16;     // blocks per representative tile (= page_size rows of v_bar)
+constexpr int kItemChunk = 512;  // descriptors resident in shared memory at a time
+
+// kind, first: physical page (ITEM_PAGE) or first block (ITEM_REP_TILE),
+// lo/hi: valid rows [lo, hi) of the page / tile
+struct __align__(16) Item { int kind, first, lo, hi; };
+
+struct ItemRange {
+  int prefix, seq_len, nb_eff, lo_b, hi_b;
+  int sel_first, n_sel_items, n_rep, n_suf, suf_first_page;
+  int begin, end;  // this split's items
+};
+
+// Called by every thread of the CTA.  scratch: 2 ints of shared memory.
+__device__ __forceinline__ ItemRange item_range(const DecodeParams& p, int seq, int head, int split,
+                                                int* scratch) {
+  ItemRange r;
+  r.prefix = p.prefix_lens[seq];
+  r.seq_len = p.seq_lens[seq];
+  r.nb_eff = min((r.prefix + p.block_size - 1) / p.block_size, p.max_blocks);
+  r.lo_b = max(p.block_lo, 0);
+  r.hi_b = min(p.block_hi, r.nb_eff);
+  const int pair = seq * p.n_kv_heads + head;
+  const int count = min(p.sel_count[pair], p.max_sel);
+  const int32_t* idx = p.sel_idx + (int64_t)pair * p.max_sel;
+  if (threadIdx.x < 2) scratch[threadIdx.x] = 0;
+  __syncthreads();
+  int below_lo = 0, below_hi = 0;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    const int b = idx[i];
+    below_lo += (b < r.lo_b);
+    below_hi += (b < r.hi_b);
+  }
+  if (below_lo) atomicAdd(&scratch[0], below_lo);
+  if (below_hi) atomicAdd(&scratch[1], below_hi);
+  __syncthreads();
+  r.sel_first = scratch[0];
+  const int n_sel = max(scratch[1] - scratch[0], 0);
+  __syncthreads();
+  const int ppb = p.block_size / p.page_size;
+  r.n_sel_items = n_sel * ppb;
+  r.n_rep = (p.rep_mode == IA_REP_HYBRID && r.hi_b > r.lo_b) ? (r.hi_b - r.lo_b + kRepTile - 1) / kRepTile : 0;
+  r.n_suf = 0;
+  r.suf_first_page = r.prefix / p.page_size;
+  if (p.with_suffix && r.seq_len > r.prefix)
+    r.n_suf = (r.seq_len - 1) / p.page_size - r.suf_first_page + 1;
+  const int64_t n = (int64_t)r.n_sel_items + r.n_rep + r.n_suf;
+  r.begin = (int)(n * split / p.n_splits);
+  r.end = (int)(n * (split + 1) / p.n_splits);
+  return r;
+}
+
+// Resolve items [chunk_begin, chunk_end) into items_s[0 ..).  All threads; ends with a barrier.
+__device__ __forceinline__ void resolve_items(const DecodeParams& p, const ItemRange& r, int seq, int head,
+                                              int chunk_begin, int chunk_end, Item* items_s) {
+  const int pair = seq * p.n_kv_heads + head;
+  const int32_t* idx = p.sel_idx + (int64_t)pair * p.max_sel;
+  const int32_t* table = p.block_table + (int64_t)seq * p.max_pages;
+  const int ppb = p.block_size / p.page_size;
+  for (int i = chunk_begin + threadIdx.x; i < chunk_end; i += blockDim.x) {
+    Item it;
+    if (i < r.n_sel_items) {
+      const int blk = idx[r.sel_first + i / ppb];
+      const int lpage = blk * ppb + i % ppb;
+      const int tok0 = lpage * p.page_size;
+      it.kind = ITEM_PAGE;
+      it.lo = 0;
+      it.hi = max(min(p.page_size, r.prefix - tok0), 0);
+      it.first = it.hi > 0 ? table[lpage] : 0;
+    } else if (i < r.n_sel_items + r.n_rep) {
+      const int b0 = r.lo_b + (i - r.n_sel_items) * kRepTile;
+      it.kind = ITEM_REP_TILE;
+      it.first = b0;
+      it.lo = 0;
+      it.hi = min(kRepTile, r.hi_b - b0);
+    } else {
+      const int lpage = r.suf_first_page + (i - r.n_sel_items - r.n_rep);
+      const int tok0 = lpage * p.page_size;
+      it.kind = ITEM_PAGE;
+      it.lo = max(r.prefix - tok0, 0);
+      it.hi = min(p.page_size, r.seq_len - tok0);
+      it.first = table[lpage];
+    }
+    items_s[i - chunk_begin] = it;
+  }
+  __syncthreads();
+}
+
+}  // namespace ia

@@ -1,0 +1,123 @@
+// Shared helpers of the interattn_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/interattn_b200.h"
+
+namespace ia {
+
+// ---- host-side status plumbing -------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int status, const char* fmt, ...);
+int check_launch(const char* what);
+int check_geom(const ia_geom* g);
+
+inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- device status word --------------------------------------------------------
+// Bit set by a kernel whose bounded wait (mbarrier) ran out; read with
+// ia_read_device_status().  Waiting is always bounded so that a programming
+// error shows up as a status bit instead of a hung GPU.
+enum : int { DEV_STATUS_SELECT_WAIT_TIMEOUT = 1 };
+int read_and_clear_device_status(int* out);  // defined next to the kernel that owns the word
+
+// ---- dtype traits ---------------------------------------------------------------
+template <typename T> struct DType;
+template <> struct DType<float> { static constexpr int id = IA_F32; };
+template <> struct DType<__nv_bfloat16> { static constexpr int id = IA_BF16; };
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ void from_f32(float& dst, float x) { dst = x; }
+__device__ __forceinline__ void from_f32(__nv_bfloat16& dst, float x) { dst = __float2bfloat16_rn(x); }
+
+// bf16 pair packed in a 32-bit word -> two floats (exact: a shift and a mask)
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// Load N consecutive elements (N * sizeof(T) in {4, 8, 16} bytes, aligned) as floats.
+template <int N> __device__ __forceinline__ void load_vec(const float* p, float (&out)[N]) {
+  if constexpr (N == 4) {
+    float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  } else if constexpr (N == 2) {
+    float2 v = *reinterpret_cast<const float2*>(p);
+    out[0] = v.x; out[1] = v.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = p[i];
+  }
+}
+template <int N> __device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&out)[N]) {
+  if constexpr (N == 4) {
+    uint2 v = *reinterpret_cast<const uint2*>(p);
+    out[0] = bf16lo(v.x); out[1] = bf16hi(v.x); out[2] = bf16lo(v.y); out[3] = bf16hi(v.y);
+  } else if constexpr (N == 2) {
+    uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+    out[0] = bf16lo(v); out[1] = bf16hi(v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = __bfloat162float(p[i]);
+  }
+}
+template <int N> __device__ __forceinline__ void store_vec(float* p, const float (&v)[N]) {
+  if constexpr (N == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  } else if constexpr (N == 2) {
+    *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) p[i] = v[i];
+  }
+}
+template <int N> __device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&v)[N]) {
+  if constexpr (N == 4) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+    __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 w;
+    w.x = *reinterpret_cast<uint32_t*>(&a);
+    w.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = w;
+  } else if constexpr (N == 2) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(p) = a;
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) p[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// ---- kernel launchers (one per translation unit) -------------------------------
+int launch_build_summaries(const void* k_pool, const void* v_pool, const int32_t* block_table,
+                           const int32_t* prefix_lens, const ia_geom& g, const ia_summaries& out,
+                           cudaStream_t stream);
+int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_lens, const ia_geom& g,
+                  int mode, int top_k, float eps, int max_sel, int32_t* sel_idx, int32_t* sel_count,
+                  const ia_select_aux& aux, cudaStream_t stream);
+int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_table, const int32_t* prefix_lens,
+                         const int32_t* seq_lens, const int32_t* sel_idx, const int32_t* sel_count,
+                         int max_sel, const ia_summaries* summaries, const float* z, const ia_geom& g,
+                         int rep_mode, int n_splits, int block_lo, int block_hi, int with_suffix,
+                         float* o_partial, float* lse_partial, cudaStream_t stream);
+int launch_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts,
+                    int head_dim, void* out, int out_dtype, float* out_lse, cudaStream_t stream);
+
+}  // namespace ia

@@ -1,0 +1,347 @@
+"""Batched, paged operators of the condition-block decode path (CUDA only).
+
+Thin host code over the C ABI (``include/interattn_b200.h``): tensors become
+raw device pointers, the current torch stream becomes the CUDA stream, status
+codes become exceptions.  PyTorch is used for device memory and streams only;
+none of these functions computes anything in PyTorch and none has a CPU path.
+
+Shapes (B sequences, Hkv kv heads, G query heads per kv head, D head_dim,
+P = 16 tokens per physical page, block = selection block, nb = blocks):
+
+    q            [B, Hkv * G, D]              query head = kv * G + g
+    k_pool       [n_pages, Hkv, P, D]         any page / head strides, inner [P, D] contiguous
+    block_table  int32 [B, max_pages]
+    prefix_lens  int32 [B]   tokens covered by summaries (the prompt)
+    seq_lens     int32 [B]   prefix + generated suffix
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Dict, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import (Geom, IA_BF16, IA_F32, IA_REP_HYBRID, IA_REP_SPARSE_ONLY, IA_SELECT_EPS,
+                   IA_SELECT_TOPK, SelectAux, Summaries, check)
+
+_DTYPES = {torch.float32: IA_F32, torch.bfloat16: IA_BF16}
+_REP = {"sparse_only": IA_REP_SPARSE_ONLY, "hybrid": IA_REP_HYBRID}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("interattn_b200 operators take CUDA tensors only (there is no CPU path)")
+
+
+@dataclass
+class PagedKV:
+    """A paged KV cache: physical pools + per-sequence page lists + lengths."""
+
+    k_pool: torch.Tensor
+    v_pool: torch.Tensor
+    block_table: torch.Tensor
+    prefix_lens: torch.Tensor
+    seq_lens: torch.Tensor
+
+    def __post_init__(self):
+        _need_cuda(self.k_pool, self.v_pool, self.block_table, self.prefix_lens, self.seq_lens)
+        k, v = self.k_pool, self.v_pool
+        if k.dim() != 4 or k.shape != v.shape or k.dtype != v.dtype or k.stride() != v.stride():
+            raise ValueError("k_pool / v_pool must be [n_pages, Hkv, P, D] tensors of equal shape, dtype and strides")
+        if k.dtype not in _DTYPES:
+            raise ValueError(f"KV dtype {k.dtype} not supported (float32, bfloat16)")
+        if k.stride(3) != 1 or k.stride(2) != k.shape[3]:
+            raise ValueError("the [P, D] run of one (page, kv head) must be contiguous")
+        for name in ("block_table", "prefix_lens", "seq_lens"):
+            t = getattr(self, name)
+            if t.dtype != torch.int32 or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous int32 tensor")
+        if self.block_table.dim() != 2:
+            raise ValueError("block_table must be [B, max_pages]")
+
+    @property
+    def batch(self) -> int:
+        return int(self.block_table.shape[0])
+
+    @property
+    def n_kv_heads(self) -> int:
+        return int(self.k_pool.shape[1])
+
+    @property
+    def page_size(self) -> int:
+        return int(self.k_pool.shape[2])
+
+    @property
+    def head_dim(self) -> int:
+        return int(self.k_pool.shape[3])
+
+    def geom(self, group_size: int, block_size: int, max_blocks: int) -> Geom:
+        return Geom(
+            batch=self.batch, n_kv_heads=self.n_kv_heads, group_size=int(group_size), head_dim=self.head_dim,
+            page_size=self.page_size, block_size=int(block_size), max_pages=int(self.block_table.shape[1]),
+            max_blocks=int(max_blocks), dtype=_DTYPES[self.k_pool.dtype], reserved=0,
+            pool_page_stride=int(self.k_pool.stride(0)), pool_head_stride=int(self.k_pool.stride(1)))
+
+
+@dataclass
+class BlockSummaries:
+    """Per (sequence, kv head, block) statistics: k_bar f32, the rest in the KV dtype."""
+
+    k_bar: torch.Tensor       # [B, Hkv, nb, D] f32
+    k_max: torch.Tensor       # [B, Hkv, nb, D]
+    k_min: torch.Tensor
+    v_bar: torch.Tensor
+    v_norm_max: torch.Tensor  # [B, Hkv, nb] f32
+    block_size: int
+
+    @property
+    def max_blocks(self) -> int:
+        return int(self.k_bar.shape[2])
+
+    def c_struct(self) -> Summaries:
+        return Summaries(self.k_bar.data_ptr(), self.k_max.data_ptr(), self.k_min.data_ptr(),
+                         self.v_bar.data_ptr(), self.v_norm_max.data_ptr())
+
+    @staticmethod
+    def empty(batch: int, n_kv_heads: int, max_blocks: int, head_dim: int, dtype: torch.dtype, device,
+              block_size: int) -> "BlockSummaries":
+        shape = (batch, n_kv_heads, max_blocks, head_dim)
+        return BlockSummaries(
+            k_bar=torch.zeros(shape, device=device, dtype=torch.float32),
+            k_max=torch.zeros(shape, device=device, dtype=dtype),
+            k_min=torch.zeros(shape, device=device, dtype=dtype),
+            v_bar=torch.zeros(shape, device=device, dtype=dtype),
+            v_norm_max=torch.zeros(shape[:3], device=device, dtype=torch.float32),
+            block_size=int(block_size))
+
+
+def build_summaries(kv: PagedKV, block_size: int, max_blocks: Optional[int] = None,
+                    out: Optional[BlockSummaries] = None) -> BlockSummaries:
+    """Block summaries of every sequence's prefix (reference: ``_build_prompt_blocks``)."""
+    lib = _lib.load()
+    if max_blocks is None:
+        max_blocks = out.max_blocks if out is not None else max(
+            1, (int(kv.block_table.shape[1]) * kv.page_size + block_size - 1) // block_size)
+    if out is None:
+        out = BlockSummaries.empty(kv.batch, kv.n_kv_heads, max_blocks, kv.head_dim, kv.k_pool.dtype,
+                                   kv.k_pool.device, block_size)
+    g = kv.geom(1, block_size, max_blocks)
+    s = out.c_struct()
+    check(lib.ia_build_summaries(_ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),
+                                 ctypes.byref(g), ctypes.byref(s), _stream()))
+    return out
+
+
+def _q_geom(q: torch.Tensor, n_kv_heads: int) -> int:
+    if q.dim() != 3 or not q.is_contiguous():
+        raise ValueError("q must be a contiguous [B, Hq, D] tensor")
+    if q.shape[1] % n_kv_heads != 0:
+        raise ValueError("query heads must be a multiple of kv heads (grouped-query attention)")
+    return int(q.shape[1]) // n_kv_heads
+
+
+def select_blocks(
+    q: torch.Tensor, summ: BlockSummaries, prefix_lens: torch.Tensor, *,
+    top_k: Optional[int] = None, eps: Optional[float] = None, max_sel: Optional[int] = None,
+    want: Sequence[str] = (), out_idx: Optional[torch.Tensor] = None, out_count: Optional[torch.Tensor] = None,
+    aux_buffers: Optional[Dict[str, torch.Tensor]] = None,
+) -> Tuple[torch.Tensor, torch.Tensor, Dict[str, torch.Tensor]]:
+    """Score every block and route.
+
+    Exactly one of ``top_k`` (k best blocks per (sequence, kv head); ties go to
+    the lower block index) and ``eps`` (the reference rule ``score > eps``) is
+    given.  Returns ``(idx int32 [B, Hkv, max_sel] ascending, -1 padded,
+    count int32 [B, Hkv], aux)`` where ``aux`` holds the tensors named in
+    ``want`` out of: score [B,Hkv,nb], z / s / delta [B,rows,nb], globals [B,4,rows].
+    """
+    lib = _lib.load()
+    _need_cuda(q, prefix_lens, summ.k_bar)
+    if (top_k is None) == (eps is None):
+        raise ValueError("give exactly one of top_k and eps")
+    b, hkv, nb, d = summ.k_bar.shape
+    group = _q_geom(q, hkv)
+    if q.dtype != summ.k_max.dtype:
+        raise ValueError("q and the summaries must share the KV dtype")
+    mode = IA_SELECT_TOPK if top_k is not None else IA_SELECT_EPS
+    if max_sel is None:
+        max_sel = int(top_k) if mode == IA_SELECT_TOPK else nb
+        max_sel = max(max_sel, 1)
+    rows = hkv * group
+    dev = q.device
+    idx = out_idx if out_idx is not None else torch.empty((b, hkv, max_sel), device=dev, dtype=torch.int32)
+    cnt = out_count if out_count is not None else torch.empty((b, hkv), device=dev, dtype=torch.int32)
+    shapes = {"score": (b, hkv, nb), "z": (b, rows, nb), "s": (b, rows, nb), "delta": (b, rows, nb),
+              "globals": (b, 4, rows)}
+    aux: Dict[str, torch.Tensor] = {}
+    for name in want:
+        if name not in shapes:
+            raise ValueError(f"unknown diagnostic {name!r}")
+        buf = None if aux_buffers is None else aux_buffers.get(name)
+        if buf is None:  # blocks past a sequence's prefix are never written: give them neutral values
+            buf = torch.full(shapes[name], float("-inf") if name == "z" else 0.0, device=dev, dtype=torch.float32)
+        aux[name] = buf
+    c_aux = SelectAux(*[aux[n].data_ptr() if n in aux else None for n in ("score", "z", "s", "delta", "globals")])
+    g = Geom(batch=b, n_kv_heads=hkv, group_size=group, head_dim=d, page_size=16, block_size=summ.block_size,
+             max_pages=1, max_blocks=nb, dtype=_DTYPES[q.dtype], reserved=0,
+             pool_page_stride=16 * d, pool_head_stride=16 * d)
+    s = summ.c_struct()
+    check(lib.ia_select(_ptr(q), ctypes.byref(s), _ptr(prefix_lens), ctypes.byref(g), mode,
+                        int(top_k or 0), float(eps or 0.0), int(max_sel), _ptr(idx), _ptr(cnt),
+                        ctypes.byref(c_aux), _stream()))
+    return idx, cnt, aux
+
+
+def sparse_decode(
+    q: torch.Tensor, kv: PagedKV, idx: torch.Tensor, count: torch.Tensor, *, block_size: int,
+    max_blocks: int, rep_mode: str = "sparse_only", summ: Optional[BlockSummaries] = None,
+    z: Optional[torch.Tensor] = None, n_splits: int = 1, block_range: Optional[Tuple[int, int]] = None,
+    with_suffix: bool = True, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Attention over the selected blocks (+ representatives, + suffix).
+
+    Returns normalised partials ``(o f32 [B, rows, n_splits, D], lse f32 [B, rows, n_splits])``."""
+    lib = _lib.load()
+    _need_cuda(q, idx, count)
+    group = _q_geom(q, kv.n_kv_heads)
+    if q.dtype != kv.k_pool.dtype:
+        raise ValueError("q and the KV pools must share a dtype")
+    if rep_mode not in _REP:
+        raise ValueError(f"rep_mode must be one of {sorted(_REP)}")
+    if rep_mode == "hybrid" and (summ is None or z is None):
+        raise ValueError("hybrid mode needs the block summaries (v_bar) and z from select_blocks(want=('z',))")
+    rows = kv.n_kv_heads * group
+    b = kv.batch
+    if out is None:
+        o = torch.empty((b, rows, n_splits, kv.head_dim), device=q.device, dtype=torch.float32)
+        lse = torch.empty((b, rows, n_splits), device=q.device, dtype=torch.float32)
+    else:
+        o, lse = out
+    lo, hi = (0, max_blocks) if block_range is None else block_range
+    g = kv.geom(group, block_size, max_blocks)
+    s = summ.c_struct() if summ is not None else None
+    check(lib.ia_sparse_decode(
+        _ptr(q), _ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens), _ptr(kv.seq_lens),
+        _ptr(idx), _ptr(count), int(idx.shape[-1]), ctypes.byref(s) if s is not None else None, _ptr(z),
+        ctypes.byref(g), _REP[rep_mode], int(n_splits), int(lo), int(hi), int(bool(with_suffix)),
+        _ptr(o), _ptr(lse), _stream()))
+    return o, lse
+
+
+def finalize(o_partial: torch.Tensor, lse_partial: torch.Tensor, out_dtype: torch.dtype,
+             return_lse: bool = False, out: Optional[torch.Tensor] = None):
+    """Log-sum-exp merge of partials along their second-to-last axis.
+
+    o_partial [..., n_parts, D], lse_partial [..., n_parts] -> out [..., D]."""
+    lib = _lib.load()
+    _need_cuda(o_partial, lse_partial)
+    if o_partial.dtype != torch.float32 or lse_partial.dtype != torch.float32:
+        raise ValueError("partials are float32")
+    if not (o_partial.is_contiguous() and lse_partial.is_contiguous()):
+        raise ValueError("partials must be contiguous")
+    *lead, parts, d = o_partial.shape
+    if tuple(lse_partial.shape) != (*lead, parts):
+        raise ValueError("lse_partial must be o_partial without its last axis")
+    n_rows = 1
+    for x in lead:
+        n_rows *= int(x)
+    if out is None:
+        out = torch.empty((*lead, d), device=o_partial.device, dtype=out_dtype)
+    lse = torch.empty(lead, device=o_partial.device, dtype=torch.float32) if return_lse else None
+    check(lib.ia_finalize(_ptr(o_partial), _ptr(lse_partial), n_rows, int(parts), int(d), _ptr(out),
+                          _DTYPES[out_dtype], _ptr(lse), _stream()))
+    return (out, lse) if return_lse else out
+
+
+class DecodeAttention:
+    """One decode-attention layer-step behind a single call, with all scratch
+    preallocated: selection -> sparse attention -> finalize.
+
+    ``step(q)`` enqueues the three kernels on the current stream and returns
+    the output tensor it owns (overwritten by the next call); it allocates
+    nothing and does not synchronise, so it can be captured in a CUDA graph.
+    ``step_host(q_host, out_host)`` is the same step for callers holding the
+    query on the host: pinned q -> device, the step, output -> pinned host,
+    then a stream synchronise.
+    """
+
+    def __init__(self, kv: PagedKV, summ: BlockSummaries, n_q_heads: int, *, top_k: Optional[int] = None,
+                 eps: Optional[float] = None, rep_mode: str = "sparse_only", n_splits: int = 1,
+                 max_sel: Optional[int] = None):
+        self.lib = _lib.load()
+        if (top_k is None) == (eps is None):
+            raise ValueError("give exactly one of top_k and eps")
+        if n_q_heads % kv.n_kv_heads != 0:
+            raise ValueError("query heads must be a multiple of kv heads")
+        if rep_mode not in _REP:
+            raise ValueError(f"rep_mode must be one of {sorted(_REP)}")
+        self.kv, self.summ = kv, summ
+        self.group = n_q_heads // kv.n_kv_heads
+        self.mode = IA_SELECT_TOPK if top_k is not None else IA_SELECT_EPS
+        self.top_k, self.eps = int(top_k or 0), float(eps or 0.0)
+        self.rep_mode, self.n_splits = rep_mode, int(n_splits)
+        nb = summ.max_blocks
+        self.max_sel = int(max_sel) if max_sel is not None else (max(self.top_k, 1) if top_k is not None else nb)
+        self.geom = kv.geom(self.group, summ.block_size, nb)
+        self.c_summ = summ.c_struct()
+        need = self.lib.ia_workspace_bytes(ctypes.byref(self.geom), self.max_sel, self.n_splits, _REP[rep_mode])
+        if need < 0:
+            check(_lib.IA_ERR_BAD_ARG)
+        dev = kv.k_pool.device
+        self.workspace = torch.empty((int(need) + 256,), device=dev, dtype=torch.uint8)
+        self._ws_off = (-self.workspace.data_ptr()) % 256
+        self.ws_bytes = int(need)
+        b, rows = kv.batch, kv.n_kv_heads * self.group
+        self.sel_idx = torch.empty((b, kv.n_kv_heads, self.max_sel), device=dev, dtype=torch.int32)
+        self.sel_count = torch.empty((b, kv.n_kv_heads), device=dev, dtype=torch.int32)
+        self.out = torch.empty((b, rows, kv.head_dim), device=dev, dtype=kv.k_pool.dtype)
+        self.q_dev = torch.empty((b, rows, kv.head_dim), device=dev, dtype=kv.k_pool.dtype)
+
+    def _ws_ptr(self):
+        return ctypes.c_void_p(self.workspace.data_ptr() + self._ws_off)
+
+    def step(self, q: torch.Tensor) -> torch.Tensor:
+        _need_cuda(q)
+        if q.shape != self.out.shape or q.dtype != self.out.dtype or not q.is_contiguous():
+            raise ValueError(f"q must be a contiguous {tuple(self.out.shape)} {self.out.dtype} tensor")
+        kv = self.kv
+        check(self.lib.ia_decode_attention(
+            _ptr(q), _ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),
+            _ptr(kv.seq_lens), ctypes.byref(self.c_summ), ctypes.byref(self.geom), self.mode, self.top_k,
+            self.eps, self.max_sel, _REP[self.rep_mode], self.n_splits, self._ws_ptr(), self.ws_bytes,
+            _ptr(self.sel_idx), _ptr(self.sel_count), _ptr(self.out), _stream()))
+        return self.out
+
+    def step_host(self, q_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
+        if q_host.is_cuda or out_host.is_cuda:
+            raise ValueError("step_host takes host tensors (pinned for full speed)")
+        if q_host.shape != self.out.shape or q_host.dtype != self.out.dtype or not q_host.is_contiguous():
+            raise ValueError(f"q_host must be a contiguous {tuple(self.out.shape)} {self.out.dtype} tensor")
+        if out_host.shape != self.out.shape or out_host.dtype != self.out.dtype or not out_host.is_contiguous():
+            raise ValueError("out_host must match q_host")
+        kv = self.kv
+        check(self.lib.ia_decode_attention_host(
+            _ptr(q_host), _ptr(self.q_dev), _ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table),
+            _ptr(kv.prefix_lens), _ptr(kv.seq_lens), ctypes.byref(self.c_summ), ctypes.byref(self.geom),
+            self.mode, self.top_k, self.eps, self.max_sel, _REP[self.rep_mode], self.n_splits, self._ws_ptr(),
+            self.ws_bytes, _ptr(self.out), _ptr(out_host), _stream()))
+        return out_host
+
+
+def device_status() -> int:
+    """Read and clear the device status word (non-zero: a bounded wait inside a kernel ran out)."""
+    lib = _lib.load()
+    v = ctypes.c_int(0)
+    check(lib.ia_read_device_status(ctypes.byref(v)))
+    return int(v.value)
