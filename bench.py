@@ -1,0 +1,372 @@
+"""Benchmark of the condition-block sparse decode-attention layer-step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (N = 1): the Llama-3-8B attention geometry - bf16, 32 query / 8 kv
+heads, head_dim 128, batch 16, context 32768 per sequence, 16-token pages
+behind a randomly permuted block table, selection block 64, top-k 64 - one
+decode step of one attention layer: block scoring + top-k routing, paged
+sparse attention over the selected pages, split-KV finalize.  Synthetic
+N(0,1) tensors (K channels scaled by a log-normal factor) stand in for real
+prompts.  A "step" is one such layer-step over the batch.  With N GPUs every
+rank owns its own 16 sequences (batch x kv-head sharding: the units share
+nothing, so there is no collective on the data path) - weak scaling.
+
+One JSON line on rank 0:
+  value      decode tokens advanced through one attention layer per second,
+             whole job, inputs resident in HBM (one C-ABI call per step)
+  e2e        the same through the host-buffer entry point: pinned q -> device,
+             the step, output -> pinned host, every step
+  roofline   the paged sparse-attention kernel: K/V bytes of the selected
+             tokens / its CUDA-event duration, against the measured HBM peak
+  cpu_baseline  the CPU oracle (a port of the reference's PyTorch path) timed
+             on this box's host cores on a bounded sample
+`--impl reference` times that CPU path alone, with every host thread.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "sparse_decode_attn_layer_tokens_per_s"
+UNIT = "tok*layer/s"
+WORKLOAD = "cfg2_llama8b_32k"
+N_LAYER_POOLS = 4       # KV pools rotated between steps: 4 x 320 MiB touched > 126 MB of L2
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--n-splits", type=int, default=0, help="split-KV parts per (sequence, kv head); 0 = auto")
+    ap.add_argument("--rep-mode", default="sparse_only", choices=["sparse_only", "hybrid"])
+    ap.add_argument("--workload", default=WORKLOAD)
+    ap.add_argument("--cpu-sample-seqs", type=int, default=4)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's PyTorch path
+# ----------------------------------------------------------------------------
+
+def cpu_prepare(cfg, n_seqs, seed_offset=0):
+    """Inputs of ``n_seqs`` sequences of the workload on the host, with their
+    block summaries (built once per prompt, hence outside the timed part)."""
+    from dataclasses import replace
+    from oracle import condition_block_oracle as orc
+    from oracle.configs import make_case
+
+    small = replace(cfg, batch=n_seqs, prefix_lens=cfg.prefix_lens[:n_seqs], suffix_lens=cfg.suffix_lens[:n_seqs],
+                    seed=cfg.seed + seed_offset)
+    case = make_case(small)
+    hkv, g = small.n_kv_heads, small.group_size
+    prepared = []
+    for b in range(n_seqs):
+        plen, slen = int(case["prefix_lens"][b]), int(case["seq_lens"][b])
+        k = orc.gather_logical(case["k_pool"], case["block_table"][b], slen)
+        v = orc.gather_logical(case["v_pool"], case["block_table"][b], slen)
+        summ = orc.block_summaries(k[:, :plen], v[:, :plen], small.block_size, storage="mixed")
+        prepared.append((plen, k, v, summ, case["q"][b].reshape(hkv, g, -1)))
+    return small, prepared
+
+
+def cpu_layer_step(small, prepared):
+    """One layer-step on the host: score + top-k + sparse attention per sequence.  Returns seconds."""
+    from oracle import condition_block_oracle as orc
+    t0 = time.perf_counter()
+    for plen, k, v, summ, qg in prepared:
+        terms = orc.condition_terms(qg, summ)
+        _, mask = orc.select_topk(terms["score"], summ.counts, small.top_k)
+        orc.decode_attention(qg, k, v, plen, small.block_size, mask, rep_mode="sparse_only")
+    return time.perf_counter() - t0
+
+
+def run_reference_arm(args):
+    """The reference's CPU implementation of the path (oracle port), all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from oracle.configs import CONFIGS
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = CONFIGS[args.workload]
+    n = 1 if args.steps > 20 else max(1, min(args.cpu_sample_seqs, 4))
+    small, prepared = cpu_prepare(cfg, n)
+    for _ in range(args.warmup):
+        cpu_layer_step(small, prepared)
+    total = 0.0
+    for _ in range(args.steps):
+        total += cpu_layer_step(small, prepared)
+    value = n * args.steps / total
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": f"{n} of {cfg.batch} sequences per step"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{n} sequence(s) x {args.steps} steps: score + top-k + sparse attention, "
+                                   "summaries excluded"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in out.strip().splitlines():
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------
+
+def make_device_layer(cfg, device, seed):
+    """One layer's paged KV cache for the whole batch, generated on the device:
+    N(0,1) K/V (K channels scaled by a log-normal factor), a random permutation
+    as the block table."""
+    import torch
+    from interattn_b200 import ops
+    g = torch.Generator(device=device).manual_seed(seed)
+    P, D, hkv = cfg.page_size, cfg.head_dim, cfg.n_kv_heads
+    pages_per_seq = [(n + s + P - 1) // P for n, s in zip(cfg.prefix_lens, cfg.suffix_lens)]
+    n_pages, max_pages = sum(pages_per_seq), max(pages_per_seq)
+    dt = cfg.torch_dtype
+    k_pool = torch.randn((n_pages, hkv, P, D), generator=g, device=device, dtype=torch.float32)
+    if cfg.k_channel_sigma > 0:
+        k_pool *= torch.exp(cfg.k_channel_sigma * torch.randn((D,), generator=g, device=device))
+    k_pool = k_pool.to(dt)
+    v_pool = torch.randn((n_pages, hkv, P, D), generator=g, device=device, dtype=torch.float32).to(dt)
+    perm = torch.randperm(n_pages, generator=g, device=device).to(torch.int32)
+    table = torch.zeros((cfg.batch, max_pages), dtype=torch.int32, device=device)
+    at = 0
+    for b, n in enumerate(pages_per_seq):
+        table[b, :n] = perm[at: at + n]
+        at += n
+    prefix = torch.tensor(cfg.prefix_lens, dtype=torch.int32, device=device)
+    seq = torch.tensor([p + s for p, s in zip(cfg.prefix_lens, cfg.suffix_lens)], dtype=torch.int32, device=device)
+    return ops.PagedKV(k_pool, v_pool, table, prefix, seq)
+
+
+def auto_splits(cfg, n_sms):
+    """Split-KV parts so that the grid covers the SMs at two CTAs each."""
+    pairs = cfg.batch * cfg.n_kv_heads
+    want = max(1, (2 * n_sms + pairs - 1) // pairs)
+    return min(want, 8)
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from interattn_b200 import ops
+    from oracle.configs import CONFIGS
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the operators have no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    cfg = CONFIGS[args.workload]
+    props = torch.cuda.get_device_properties(device)
+    n_splits = args.n_splits or auto_splits(cfg, props.multi_processor_count)
+    nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
+    rows = cfg.n_q_heads
+
+    layers, steppers, qs = [], [], []
+    for l in range(N_LAYER_POOLS):
+        kv = make_device_layer(cfg, device, seed=1000 * rank + l)
+        summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb)
+        layers.append((kv, summ))
+        steppers.append(ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=args.rep_mode,
+                                            n_splits=n_splits))
+        g = torch.Generator(device=device).manual_seed(77 + 1000 * rank + l)
+        qs.append(torch.randn((cfg.batch, rows, cfg.head_dim), generator=g, device=device).to(cfg.torch_dtype))
+    torch.cuda.synchronize()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident arm: K steps, per-kernel events inside the same region -------------
+    K, W = args.steps, args.warmup
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
+    for row in ev:
+        for e in row:
+            e.record()
+    sampler = ClockSampler(local_rank)   # samples from the warm-up to the end of the second timed region
+    sampler.start()
+    for i in range(W):
+        steppers[i % N_LAYER_POOLS].step(qs[i % N_LAYER_POOLS])
+    sync_all()
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin.record()
+    for i in range(K):
+        steppers[i % N_LAYER_POOLS].step_timed(qs[i % N_LAYER_POOLS], ev[i])
+    t_end.record()
+    sync_all()
+    elapsed_ms = t_begin.elapsed_time(t_end)
+    sel_ms = sum(r[0].elapsed_time(r[1]) for r in ev) / K
+    att_ms = sum(r[1].elapsed_time(r[2]) for r in ev) / K
+    fin_ms = sum(r[2].elapsed_time(r[3]) for r in ev) / K
+    status = ops.device_status()
+
+    # ---- end-to-end arm: host q in, host output back, every step ---------------------------------
+    q_host = [q.cpu().pin_memory() for q in qs]
+    out_host = [torch.empty_like(q).pin_memory() for q in q_host]
+    for i in range(min(W, 5)):
+        steppers[i % N_LAYER_POOLS].step_host(q_host[i % N_LAYER_POOLS], out_host[i % N_LAYER_POOLS])
+    sync_all()
+    e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_begin.record()
+    for i in range(K):
+        steppers[i % N_LAYER_POOLS].step_host(q_host[i % N_LAYER_POOLS], out_host[i % N_LAYER_POOLS])
+    e_end.record()
+    sync_all()
+    clocks = sampler.stop()
+    e2e_ms = e_begin.elapsed_time(e_end)
+
+    times = torch.tensor([elapsed_ms, e2e_ms, att_ms, sel_ms, fin_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms, att_ms, sel_ms, fin_ms = [float(x) for x in times.cpu()]
+
+    if rank == 0:
+        esz = 2 if cfg.dtype == "bfloat16" else 4
+        tokens_sel = sum(min(cfg.top_k * cfg.block_size, n) for n in cfg.prefix_lens) * cfg.n_kv_heads
+        suffix_tok = sum(cfg.suffix_lens) * cfg.n_kv_heads
+        kv_bytes = (tokens_sel + suffix_tok) * cfg.head_dim * 2 * esz
+        sel_bytes = sum((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens) * cfg.n_kv_heads * (
+            cfg.head_dim * 4 + 2 * cfg.head_dim * esz + 4)
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured"
+        except (OSError, KeyError, ValueError):
+            pass
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+                traffic = json.load(f).get(args.workload, {}).get("sparse_decode_bytes_per_launch")
+        except (OSError, ValueError):
+            pass
+        att_gbs = kv_bytes / (att_ms * 1e-3) / 1e9
+        sel_gbs = sel_bytes / (sel_ms * 1e-3) / 1e9
+        q_bytes = cfg.batch * rows * cfg.head_dim * esz
+        line = {
+            "metric": METRIC, "value": world * cfg.batch * K / (elapsed_ms * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": elapsed_ms / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if cfg.dtype == "bfloat16" else "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": cfg.batch, "n_q_heads": cfg.n_q_heads,
+                       "n_kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim, "context": max(cfg.prefix_lens),
+                       "page": cfg.page_size, "block": cfg.block_size, "top_k": cfg.top_k,
+                       "rep_mode": args.rep_mode, "n_splits": n_splits, "parallelism": f"batch-shard x{world}",
+                       "l2": f"{N_LAYER_POOLS} layer pools rotated, {(kv_bytes + sel_bytes) >> 20} MiB read per step "
+                             "(> 126 MB L2), no flush"},
+            "us_per_layer": 1e3 * elapsed_ms / K,
+            "kernel_us": {"select": 1e3 * sel_ms, "sparse_decode": 1e3 * att_ms, "finalize": 1e3 * fin_ms},
+            "roofline": {"bound": "hbm", "kernel": "condition_block_finalize_attention_kernel",
+                         "achieved": att_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                         "frac": att_gbs / peak, "traffic": traffic, "bytes_per_launch": kv_bytes},
+            "roofline_select": {"bound": "hbm", "kernel": "condition_block_select_kernel", "achieved": sel_gbs,
+                                "peak": peak, "unit": "GB/s", "frac": sel_gbs / peak,
+                                "bytes_per_launch": sel_bytes},
+            "e2e": {"value": world * cfg.batch * K / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": q_bytes, "d2h_bytes_per_step": q_bytes,
+                    "us_per_layer": 1e3 * e2e_ms / K,
+                    "note": "KV pool and block summaries are cache state resident on the device; the step's "
+                            "inputs (q) and outputs cross PCIe every step"},
+            "gpu_launches": 3 * K,
+            "clocks": clocks,
+            "device_status": status,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            n = max(1, args.cpu_sample_seqs)
+            small, prepared = cpu_prepare(cfg, n)
+            cpu_layer_step(small, prepared)  # warm-up
+            reps = 5
+            dt = sum(cpu_layer_step(small, prepared) for _ in range(reps)) / reps
+            line["cpu_baseline"] = {
+                "value": n / dt, "unit": UNIT, "cores": cores, "kind": "port",
+                "sample": f"{n} of {cfg.batch} sequences, one layer-step x {reps}: score + top-k + sparse "
+                          f"attention ({dt:.2f} s per step), summaries excluded"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

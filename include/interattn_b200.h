@@ -168,6 +168,19 @@ int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool,
                         int rep_mode, int n_splits, void* workspace, int64_t workspace_bytes,
                         int32_t* sel_idx, int32_t* sel_count, void* out, ia_stream_t stream);
 
+/* ia_decode_attention that also records four caller-created CUDA events
+ * (cudaEvent_t, timing enabled) on the stream: events[0] before the selection
+ * kernel, [1] between selection and attention, [2] between attention and
+ * finalize, [3] after finalize - per-kernel device times of a live step
+ * without a profiler.  A null entry is skipped. */
+int ia_decode_attention_timed(const void* q, const void* k_pool, const void* v_pool,
+                              const int32_t* block_table, const int32_t* prefix_lens,
+                              const int32_t* seq_lens, const ia_summaries* summaries,
+                              const ia_geom* geom, int mode, int top_k, float eps, int max_sel,
+                              int rep_mode, int n_splits, void* workspace, int64_t workspace_bytes,
+                              int32_t* sel_idx, int32_t* sel_count, void* out, void* const* events,
+                              ia_stream_t stream);
+
 /* The same layer-step with HOST buffers, for callers that keep only the KV
  * pool and the summaries on the device: copies q_host -> device (async on
  * stream), runs ia_decode_attention, copies the output back into out_host and

@@ -60,6 +60,10 @@ SIGNATURES = {
     "ia_decode_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Summaries),
                                     POINTER(Geom), c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int64,
                                     c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ia_decode_attention_timed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          POINTER(Summaries), POINTER(Geom), c_int, c_int, c_float, c_int, c_int,
+                                          c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                          POINTER(c_void_p), c_void_p]),
     "ia_decode_attention_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          POINTER(Summaries), POINTER(Geom), c_int, c_int, c_float, c_int, c_int,
                                          c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),

@@ -184,11 +184,12 @@ int64_t ia_workspace_bytes(const ia_geom* geom, int max_sel, int n_splits, int r
   return carve(*geom, max_sel, n_splits, rep_mode, nullptr).bytes;
 }
 
-int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
-                        const int32_t* prefix_lens, const int32_t* seq_lens, const ia_summaries* summaries,
-                        const ia_geom* geom, int mode, int top_k, float eps, int max_sel, int rep_mode,
-                        int n_splits, void* workspace, int64_t workspace_bytes, int32_t* sel_idx,
-                        int32_t* sel_count, void* out, ia_stream_t stream) {
+static int decode_attention_impl(const void* q, const void* k_pool, const void* v_pool,
+                                 const int32_t* block_table, const int32_t* prefix_lens,
+                                 const int32_t* seq_lens, const ia_summaries* summaries, const ia_geom* geom,
+                                 int mode, int top_k, float eps, int max_sel, int rep_mode, int n_splits,
+                                 void* workspace, int64_t workspace_bytes, int32_t* sel_idx, int32_t* sel_count,
+                                 void* out, void* const* events, ia_stream_t stream) {
   if (int s = check_geom(geom)) return s;
   if (!workspace || !out) return fail(IA_ERR_BAD_ARG, "decode_attention: null workspace or out");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
@@ -198,17 +199,48 @@ int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool, c
   if (workspace_bytes < w.bytes)
     return fail(IA_ERR_BAD_ARG, "decode_attention: workspace %lld bytes, need %lld", (long long)workspace_bytes,
                 (long long)w.bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  auto mark = [&](int i) {
+    if (events != nullptr && events[i] != nullptr) cudaEventRecord((cudaEvent_t)events[i], st);
+  };
   int32_t* idx = sel_idx ? sel_idx : w.sel_idx;
   int32_t* cnt = sel_count ? sel_count : w.sel_count;
   ia_select_aux aux{};
   if (rep_mode == IA_REP_HYBRID) aux.z = w.z;
+  mark(0);
   if (int s = ia_select(q, summaries, prefix_lens, geom, mode, top_k, eps, max_sel, idx, cnt, &aux, stream)) return s;
+  mark(1);
   if (int s = ia_sparse_decode(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, idx, cnt, max_sel, summaries,
                                w.z, geom, rep_mode, n_splits, 0, geom->max_blocks, 1, w.o_partial, w.lse_partial,
                                stream))
     return s;
+  mark(2);
   const int n_rows = geom->batch * geom->n_kv_heads * geom->group_size;
-  return ia_finalize(w.o_partial, w.lse_partial, n_rows, n_splits, geom->head_dim, out, geom->dtype, nullptr, stream);
+  const int s = ia_finalize(w.o_partial, w.lse_partial, n_rows, n_splits, geom->head_dim, out, geom->dtype, nullptr,
+                            stream);
+  mark(3);
+  return s;
+}
+
+int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                        const int32_t* prefix_lens, const int32_t* seq_lens, const ia_summaries* summaries,
+                        const ia_geom* geom, int mode, int top_k, float eps, int max_sel, int rep_mode,
+                        int n_splits, void* workspace, int64_t workspace_bytes, int32_t* sel_idx,
+                        int32_t* sel_count, void* out, ia_stream_t stream) {
+  return decode_attention_impl(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, summaries, geom, mode, top_k,
+                               eps, max_sel, rep_mode, n_splits, workspace, workspace_bytes, sel_idx, sel_count, out,
+                               nullptr, stream);
+}
+
+int ia_decode_attention_timed(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                              const int32_t* prefix_lens, const int32_t* seq_lens, const ia_summaries* summaries,
+                              const ia_geom* geom, int mode, int top_k, float eps, int max_sel, int rep_mode,
+                              int n_splits, void* workspace, int64_t workspace_bytes, int32_t* sel_idx,
+                              int32_t* sel_count, void* out, void* const* events, ia_stream_t stream) {
+  if (events == nullptr) return fail(IA_ERR_BAD_ARG, "decode_attention_timed: events is null");
+  return decode_attention_impl(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, summaries, geom, mode, top_k,
+                               eps, max_sel, rep_mode, n_splits, workspace, workspace_bytes, sel_idx, sel_count, out,
+                               events, stream);
 }
 
 int ia_decode_attention_host(const void* q_host, void* q_dev, const void* k_pool, const void* v_pool,

@@ -323,6 +323,23 @@ class DecodeAttention:
             _ptr(self.sel_idx), _ptr(self.sel_count), _ptr(self.out), _stream()))
         return self.out
 
+    def step_timed(self, q: torch.Tensor, events: Sequence[torch.cuda.Event]) -> torch.Tensor:
+        """``step`` that also records four timing events (before selection, after
+        selection, after attention, after finalize) on the current stream.  The
+        events must have been recorded once before (torch creates the CUDA event
+        lazily on first use)."""
+        _need_cuda(q)
+        if len(events) != 4:
+            raise ValueError("four events are needed")
+        handles = (ctypes.c_void_p * 4)(*[ctypes.c_void_p(e.cuda_event) for e in events])
+        kv = self.kv
+        check(self.lib.ia_decode_attention_timed(
+            _ptr(q), _ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),
+            _ptr(kv.seq_lens), ctypes.byref(self.c_summ), ctypes.byref(self.geom), self.mode, self.top_k,
+            self.eps, self.max_sel, _REP[self.rep_mode], self.n_splits, self._ws_ptr(), self.ws_bytes,
+            _ptr(self.sel_idx), _ptr(self.sel_count), _ptr(self.out), handles, _stream()))
+        return self.out
+
     def step_host(self, q_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
         if q_host.is_cuda or out_host.is_cuda:
             raise ValueError("step_host takes host tensors (pinned for full speed)")

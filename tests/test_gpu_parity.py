@@ -91,7 +91,8 @@ def test_topk_indices_bit_exact(bundle):
         osum, terms, ranked, mask = _oracle_selection(cfg, case, summ, b, cfg.top_k)
         nb = osum.n_blocks
         score = aux["score"][b, :, :nb].cpu()
-        assert torch.allclose(score, terms["score"], rtol=2e-4, atol=1e-12), "condition score"
+        # a one-token block has delta = 0 exactly, hence score 0; the CPU float noise there is ~1e-9
+        assert torch.allclose(score, terms["score"], rtol=2e-4, atol=1e-8), "condition score"
         assert torch.allclose(aux["z"][b, :, :nb].cpu().reshape(cfg.n_kv_heads, cfg.group_size, nb),
                               terms["z"], rtol=1e-5, atol=1e-5)
         assert torch.allclose(aux["delta"][b, :, :nb].cpu().reshape(cfg.n_kv_heads, cfg.group_size, nb),
@@ -124,12 +125,14 @@ def test_eps_selection(bundle):
                 want = want_mask[h].nonzero().flatten().tolist()
                 got = idx[b, h, : int(cnt[b, h])].tolist()
                 if eps == 0.0:
-                    assert got == list(range(osum.n_blocks))      # every block that holds a token
+                    # every block that holds a token, except a one-token block (zero width: score 0)
+                    everyone = list(range(osum.n_blocks))
+                    assert got == everyone or (int(osum.counts[-1]) == 1 and got == everyone[:-1])
                 elif eps == 1e9:
                     assert got == []
                 else:
                     sc = terms["score"][h]
-                    near = ((sc - eps).abs() <= 2e-4 * sc.abs()).nonzero().flatten().tolist()
+                    near = ((sc - eps).abs() <= 2e-4 * sc.abs() + 1e-8).nonzero().flatten().tolist()
                     assert set(got) ^ set(want) <= set(near)
 
 
@@ -203,7 +206,10 @@ def test_block_range_shares_merge_to_the_whole(bundle):
         glse = torch.stack([p[1] for p in parts], dim=2).contiguous()
         merged, merged_lse = ops.finalize(go, glse, torch.float32, return_lse=True)
         torch.cuda.synchronize()
-        torch.testing.assert_close(merged, whole, rtol=2e-5, atol=2e-5)
+        # fp32 pools: only the summation order differs.  bf16 pools: the probabilities are
+        # rounded to bf16 relative to the running maximum, which depends on the partition.
+        tol = dict(rtol=2e-5, atol=2e-5) if cfg.dtype == "float32" else dict(rtol=1e-2, atol=3e-3)
+        torch.testing.assert_close(merged, whole, **tol)
         finite = torch.isfinite(whole_lse)
         torch.testing.assert_close(merged_lse[finite], whole_lse[finite], rtol=1e-5, atol=1e-5)
 
@@ -352,7 +358,7 @@ def test_argument_errors_are_value_errors():
     with pytest.raises(ValueError):
         ops.select_blocks(case["q"], summ, kv.prefix_lens, top_k=1)             # CPU tensor
     with pytest.raises(ValueError):
-        ops.build_summaries(kv, 48)                                             # block not a page multiple
+        ops.build_summaries(kv, 40)                                             # block not a page multiple
     idx, cnt, _ = ops.select_blocks(q, summ, kv.prefix_lens, top_k=1)
     with pytest.raises(ValueError):
         ops.sparse_decode(q, kv, idx, cnt, block_size=64, max_blocks=2, rep_mode="hybrid")   # no z / summaries
