@@ -194,6 +194,36 @@ int ia_decode_attention_host(const void* q_host, void* q_dev, const void* k_pool
                              void* workspace, int64_t workspace_bytes, void* out_dev,
                              void* out_host, ia_stream_t stream);
 
+/* ia_decode_attention for callers that cannot allocate device memory at all -
+ * for example a plug-in inside an inference server that gave all of HBM to its
+ * KV-cache pool at start-up, where a cudaMalloc made afterwards fails or
+ * fragments that pool.  No counterpart in the reference (its scratch is a dict
+ * of torch tensors, IMPL/core.py:558-570).
+ *
+ * Same step, same results, but the scratch (selection list, split-KV partials,
+ * hybrid-mode logits) is a fixed IA_NOALLOC_SCRATCH_BYTES array inside the
+ * library image instead of a caller workspace; every GPU that loads the
+ * library holds that array until the process exits.  The caller still passes q,
+ * the KV pool, the summaries and out [batch, rows, head_dim] (geom->dtype).
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *  - A step whose ia_workspace_bytes() exceeds IA_NOALLOC_SCRATCH_BYTES is
+ *    refused with IA_ERR_UNSUPPORTED (at the Llama-3-8B geometry, batch 16,
+ *    top-64, 3 splits the step needs about 0.8 MB; hybrid mode at 32k context
+ *    about 1.9 MB).
+ *  - The first call on each device looks up the array's device address (with
+ *    that device current); make that first call before any stream capture.
+ *  - All calls share the one array and it keeps the previous call's contents.
+ *    Nothing in it needs clearing between calls, but two calls that overlap on
+ *    the GPU (different streams, or different host threads) race on it: keep
+ *    the calls of one device on one stream, or order them with events. */
+#define IA_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024)
+int64_t ia_noalloc_scratch_bytes(void);
+int ia_decode_attention_noalloc(const void* q, const void* k_pool, const void* v_pool,
+                                const int32_t* block_table, const int32_t* prefix_lens,
+                                const int32_t* seq_lens, const ia_summaries* summaries,
+                                const ia_geom* geom, int mode, int top_k, float eps, int max_sel,
+                                int rep_mode, int n_splits, void* out, ia_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -67,6 +67,10 @@ SIGNATURES = {
     "ia_decode_attention_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          POINTER(Summaries), POINTER(Geom), c_int, c_int, c_float, c_int, c_int,
                                          c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "ia_noalloc_scratch_bytes": (c_int64, []),
+    "ia_decode_attention_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            POINTER(Summaries), POINTER(Geom), c_int, c_int, c_float, c_int, c_int,
+                                            c_int, c_void_p, c_void_p]),
 }
 
 _lib = None

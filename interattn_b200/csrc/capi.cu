@@ -266,3 +266,70 @@ int ia_decode_attention_host(const void* q_host, void* q_dev, const void* k_pool
 }
 
 }  // extern "C"
+
+// ---- the layer-step for callers that cannot allocate device memory ---------------------
+//
+// Some hosts of this library never get to call cudaMalloc: an inference server
+// that hands (nearly) all of HBM to its KV-cache pool at start-up, so that a
+// later allocation by a plug-in fails or fragments the pool; a runtime whose
+// hot loop is audited to be allocation-free.  For them the scratch of the
+// layer-step (selection list, split-KV partials, hybrid-mode logits) lives in
+// the array below, which is part of the library image: every GPU that loads
+// the library holds these IA_NOALLOC_SCRATCH_BYTES until the process exits.
+namespace ia {
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[IA_NOALLOC_SCRATCH_BYTES];
+
+// In host code `g_noalloc_scratch` only names the symbol; it is not a device
+// address and must never be handed to a kernel.  The device address is looked
+// up once per device (with that device current) and cached here.
+constexpr int kMaxDevices = 64;
+static void* g_noalloc_addr[kMaxDevices] = {};
+
+static int noalloc_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(IA_ERR_NO_DEVICE, "decode_attention_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(IA_ERR_UNSUPPORTED, "decode_attention_noalloc: device ordinal %d", dev);
+  void* p = __atomic_load_n(&g_noalloc_addr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(IA_ERR_LAUNCH, "decode_attention_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    __atomic_store_n(&g_noalloc_addr[dev], p, __ATOMIC_RELEASE);  // every thread would store the same address
+  }
+  *out = p;
+  return IA_OK;
+}
+
+}  // namespace ia
+
+extern "C" {
+
+int64_t ia_noalloc_scratch_bytes(void) { return (int64_t)IA_NOALLOC_SCRATCH_BYTES; }
+
+int ia_decode_attention_noalloc(const void* q, const void* k_pool, const void* v_pool,
+                                const int32_t* block_table, const int32_t* prefix_lens,
+                                const int32_t* seq_lens, const ia_summaries* summaries, const ia_geom* geom,
+                                int mode, int top_k, float eps, int max_sel, int rep_mode, int n_splits, void* out,
+                                ia_stream_t stream) {
+  if (int s = check_geom(geom)) return s;
+  if (max_sel <= 0 || n_splits <= 0)
+    return fail(IA_ERR_BAD_ARG, "decode_attention_noalloc: max_sel %d, n_splits %d", max_sel, n_splits);
+  const int64_t need = carve(*geom, max_sel, n_splits, rep_mode, nullptr).bytes;
+  if (need > (int64_t)IA_NOALLOC_SCRATCH_BYTES)
+    return fail(IA_ERR_UNSUPPORTED,
+                "decode_attention_noalloc: this step needs %lld bytes of scratch, the built-in array holds %lld; "
+                "use ia_decode_attention with a caller-owned workspace, or fewer sequences / splits per call",
+                (long long)need, (long long)IA_NOALLOC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  if (int s = noalloc_scratch(&scratch)) return s;
+  // Nothing in the scratch has to start at zero: the selection kernel writes the
+  // whole index list and every count, the attention kernel every (row, split)
+  // partial, and hybrid-mode logits are read only where the selection wrote them.
+  return decode_attention_impl(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, summaries, geom, mode, top_k,
+                               eps, max_sel, rep_mode, n_splits, scratch, need, nullptr, nullptr, out, nullptr,
+                               stream);
+}
+
+}  // extern "C"

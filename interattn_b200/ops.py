@@ -356,6 +356,44 @@ class DecodeAttention:
         return out_host
 
 
+def decode_attention_noalloc(
+    q: torch.Tensor, kv: PagedKV, summ: BlockSummaries, out: torch.Tensor, *, top_k: Optional[int] = None,
+    eps: Optional[float] = None, rep_mode: str = "sparse_only", n_splits: int = 1,
+    max_sel: Optional[int] = None,
+) -> torch.Tensor:
+    """One decode-attention layer-step with no device allocation anywhere.
+
+    For hosts that cannot allocate device memory once they are running (an
+    inference server that reserved all of HBM for its KV pool; a loop that must
+    stay allocation-free).  The caller passes ``q`` and ``out`` (same shape and
+    dtype); the step's scratch is a fixed array inside the shared library
+    instead of a workspace tensor, so neither this function nor the library
+    calls an allocator.  Limits and caveats: the step must fit in
+    ``ia_noalloc_scratch_bytes()`` (else ValueError); the first call on a
+    device should come before any stream capture; calls share the array, so
+    calls that overlap on the GPU race - keep them on one stream.
+    """
+    lib = _lib.load()
+    _need_cuda(q, out)
+    if (top_k is None) == (eps is None):
+        raise ValueError("give exactly one of top_k and eps")
+    if rep_mode not in _REP:
+        raise ValueError(f"rep_mode must be one of {sorted(_REP)}")
+    group = _q_geom(q, kv.n_kv_heads)
+    if out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous() or q.dtype != kv.k_pool.dtype:
+        raise ValueError("out must be a contiguous tensor of q's shape and dtype (the KV dtype)")
+    mode = IA_SELECT_TOPK if top_k is not None else IA_SELECT_EPS
+    if max_sel is None:
+        max_sel = max(int(top_k), 1) if top_k is not None else summ.max_blocks
+    g = kv.geom(group, summ.block_size, summ.max_blocks)
+    s = summ.c_struct()
+    check(lib.ia_decode_attention_noalloc(
+        _ptr(q), _ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens), _ptr(kv.seq_lens),
+        ctypes.byref(s), ctypes.byref(g), mode, int(top_k or 0), float(eps or 0.0), int(max_sel), _REP[rep_mode],
+        int(n_splits), _ptr(out), _stream()))
+    return out
+
+
 def device_status() -> int:
     """Read and clear the device status word (non-zero: a bounded wait inside a kernel ran out)."""
     lib = _lib.load()
