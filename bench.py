@@ -42,7 +42,7 @@ if ROOT not in sys.path:
 METRIC = "sparse_decode_attn_layer_tokens_per_s"
 UNIT = "tok*layer/s"
 WORKLOAD = "cfg2_llama8b_32k"
-N_LAYER_POOLS = 4       # KV pools rotated between steps: 4 x 320 MiB touched > 126 MB of L2
+N_LAYER_POOLS = 4       # default number of KV pools rotated between steps (4 x 320 MiB touched > 126 MB of L2)
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -57,6 +57,8 @@ def parse_args():
     ap.add_argument("--workload", default=WORKLOAD)
     ap.add_argument("--cpu-sample-seqs", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer-pools", type=int, default=N_LAYER_POOLS,
+                    help="KV pools rotated between steps (1 keeps a profiler capture small)")
     return ap.parse_args()
 
 
@@ -234,7 +236,8 @@ def run_gpu_arm(args):
     rows = cfg.n_q_heads
 
     layers, steppers, qs = [], [], []
-    for l in range(N_LAYER_POOLS):
+    n_pools = max(1, args.layer_pools)
+    for l in range(n_pools):
         kv = make_device_layer(cfg, device, seed=1000 * rank + l)
         summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb)
         layers.append((kv, summ))
@@ -259,12 +262,12 @@ def run_gpu_arm(args):
     sampler = ClockSampler(local_rank)   # samples from the warm-up to the end of the second timed region
     sampler.start()
     for i in range(W):
-        steppers[i % N_LAYER_POOLS].step(qs[i % N_LAYER_POOLS])
+        steppers[i % n_pools].step(qs[i % n_pools])
     sync_all()
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_begin.record()
     for i in range(K):
-        steppers[i % N_LAYER_POOLS].step_timed(qs[i % N_LAYER_POOLS], ev[i])
+        steppers[i % n_pools].step_timed(qs[i % n_pools], ev[i])
     t_end.record()
     sync_all()
     elapsed_ms = t_begin.elapsed_time(t_end)
@@ -277,12 +280,12 @@ def run_gpu_arm(args):
     q_host = [q.cpu().pin_memory() for q in qs]
     out_host = [torch.empty_like(q).pin_memory() for q in q_host]
     for i in range(min(W, 5)):
-        steppers[i % N_LAYER_POOLS].step_host(q_host[i % N_LAYER_POOLS], out_host[i % N_LAYER_POOLS])
+        steppers[i % n_pools].step_host(q_host[i % n_pools], out_host[i % n_pools])
     sync_all()
     e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_begin.record()
     for i in range(K):
-        steppers[i % N_LAYER_POOLS].step_host(q_host[i % N_LAYER_POOLS], out_host[i % N_LAYER_POOLS])
+        steppers[i % n_pools].step_host(q_host[i % n_pools], out_host[i % n_pools])
     e_end.record()
     sync_all()
     clocks = sampler.stop()
@@ -324,7 +327,7 @@ def run_gpu_arm(args):
                        "n_kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim, "context": max(cfg.prefix_lens),
                        "page": cfg.page_size, "block": cfg.block_size, "top_k": cfg.top_k,
                        "rep_mode": args.rep_mode, "n_splits": n_splits, "parallelism": f"batch-shard x{world}",
-                       "l2": f"{N_LAYER_POOLS} layer pools rotated, {(kv_bytes + sel_bytes) >> 20} MiB read per step "
+                       "l2": f"{n_pools} layer pools rotated, {(kv_bytes + sel_bytes) >> 20} MiB read per step "
                              "(> 126 MB L2), no flush"},
             "us_per_layer": 1e3 * elapsed_ms / K,
             "kernel_us": {"select": 1e3 * sel_ms, "sparse_decode": 1e3 * att_ms, "finalize": 1e3 * fin_ms},
