@@ -206,13 +206,6 @@ def make_device_layer(cfg, device, seed):
     return ops.PagedKV(k_pool, v_pool, table, prefix, seq)
 
 
-def auto_splits(cfg, n_sms):
-    """Split-KV parts so that the grid covers the SMs at two CTAs each."""
-    pairs = cfg.batch * cfg.n_kv_heads
-    want = max(1, (2 * n_sms + pairs - 1) // pairs)
-    return min(want, 8)
-
-
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -231,7 +224,7 @@ def run_gpu_arm(args):
 
     cfg = CONFIGS[args.workload]
     props = torch.cuda.get_device_properties(device)
-    n_splits = args.n_splits or auto_splits(cfg, props.multi_processor_count)
+    n_splits = args.n_splits or None      # None: the library picks a wave-aware split count
     nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
     rows = cfg.n_q_heads
 
@@ -245,6 +238,7 @@ def run_gpu_arm(args):
                                             n_splits=n_splits))
         g = torch.Generator(device=device).manual_seed(77 + 1000 * rank + l)
         qs.append(torch.randn((cfg.batch, rows, cfg.head_dim), generator=g, device=device).to(cfg.torch_dtype))
+    n_splits = steppers[0].n_splits
     torch.cuda.synchronize()
 
     def sync_all():

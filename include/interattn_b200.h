@@ -156,6 +156,12 @@ int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, in
 /* Scratch needed by ia_decode_attention, in bytes. */
 int64_t ia_workspace_bytes(const ia_geom* geom, int max_sel, int n_splits, int rep_mode);
 
+/* A good n_splits for ia_sparse_decode / ia_decode_attention on the current
+ * device, given how many blocks a (sequence, kv head) is expected to attend
+ * (top_k, or a typical count in epsilon mode): picks the split count whose
+ * grid fills whole waves of resident CTAs.  Host arithmetic only. */
+int ia_suggest_splits(const ia_geom* geom, int expected_blocks);
+
 /* One decode-attention layer-step: ia_select, ia_sparse_decode and
  * ia_finalize on one stream, replacing _condition_block_decode_output_fused_triton
  * (IMPL/core.py:1035-1155).  workspace: ia_workspace_bytes() bytes, 256-byte

@@ -57,6 +57,7 @@ SIGNATURES = {
                                  c_int, c_void_p, c_void_p, c_void_p]),
     "ia_finalize": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "ia_workspace_bytes": (c_int64, [POINTER(Geom), c_int, c_int, c_int]),
+    "ia_suggest_splits": (c_int, [POINTER(Geom), c_int]),
     "ia_decode_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Summaries),
                                     POINTER(Geom), c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int64,
                                     c_void_p, c_void_p, c_void_p, c_void_p]),

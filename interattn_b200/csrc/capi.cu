@@ -184,6 +184,42 @@ int64_t ia_workspace_bytes(const ia_geom* geom, int max_sel, int n_splits, int r
   return carve(*geom, max_sel, n_splits, rep_mode, nullptr).bytes;
 }
 
+// Split-KV parts per (sequence, kv head) for ia_sparse_decode.  The attention
+// kernel keeps two CTAs per SM resident; a grid that is not a whole number of
+// such waves leaves SMs idle in its last wave, and a lone CTA cannot pull much
+// more than its fair share of HBM (its loads in flight are bounded by its
+// shared-memory ring).  The estimate below is that model, fitted on B200:
+//   time(S) = sum over waves of max(bytes per CTA / r_cta, bytes of the wave / B) + c
+// with r_cta = 26 GB/s, B = 5.4 TB/s, c = 3 us.
+int ia_suggest_splits(const ia_geom* geom, int expected_blocks) {
+  if (check_geom(geom) != IA_OK || expected_blocks <= 0) return 1;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 148;
+  const double slots = 2.0 * sms;
+  const double pairs = (double)geom->batch * geom->n_kv_heads;
+  const double esz = geom->dtype == IA_BF16 ? 2.0 : 4.0;
+  const double pair_bytes = (double)expected_blocks * geom->block_size * geom->head_dim * 2.0 * esz;
+  const double r_cta = 26e9, hbm = 5.4e12, fixed = 3e-6;
+  const int pages = expected_blocks * (geom->block_size / geom->page_size);
+  int best = 1;
+  double best_t = 1e30;
+  for (int s = 1; s <= 16; ++s) {
+    if (s > 1 && pages / s < 8) break;  // keep at least two pages per warp
+    const double cta_bytes = pair_bytes / s;
+    double left = pairs * s, t = 0.0;
+    while (left > 0.0) {
+      const double n = left < slots ? left : slots;
+      const double a = cta_bytes / r_cta, b = n * cta_bytes / hbm;
+      t += (a > b ? a : b) + fixed;
+      left -= n;
+    }
+    if (t < best_t * 0.98) { best_t = t; best = s; }
+  }
+  return best;
+}
+
 static int decode_attention_impl(const void* q, const void* k_pool, const void* v_pool,
                                  const int32_t* block_table, const int32_t* prefix_lens,
                                  const int32_t* seq_lens, const ia_summaries* summaries, const ia_geom* geom,

@@ -277,8 +277,8 @@ class DecodeAttention:
     """
 
     def __init__(self, kv: PagedKV, summ: BlockSummaries, n_q_heads: int, *, top_k: Optional[int] = None,
-                 eps: Optional[float] = None, rep_mode: str = "sparse_only", n_splits: int = 1,
-                 max_sel: Optional[int] = None):
+                 eps: Optional[float] = None, rep_mode: str = "sparse_only", n_splits: Optional[int] = None,
+                 max_sel: Optional[int] = None, expected_blocks: Optional[int] = None):
         self.lib = _lib.load()
         if (top_k is None) == (eps is None):
             raise ValueError("give exactly one of top_k and eps")
@@ -290,10 +290,13 @@ class DecodeAttention:
         self.group = n_q_heads // kv.n_kv_heads
         self.mode = IA_SELECT_TOPK if top_k is not None else IA_SELECT_EPS
         self.top_k, self.eps = int(top_k or 0), float(eps or 0.0)
-        self.rep_mode, self.n_splits = rep_mode, int(n_splits)
         nb = summ.max_blocks
         self.max_sel = int(max_sel) if max_sel is not None else (max(self.top_k, 1) if top_k is not None else nb)
         self.geom = kv.geom(self.group, summ.block_size, nb)
+        if n_splits is None:   # wave-aware choice for this device
+            expect = expected_blocks or (min(self.top_k, nb) if top_k is not None else max(1, nb // 16))
+            n_splits = self.lib.ia_suggest_splits(ctypes.byref(self.geom), int(max(1, expect)))
+        self.rep_mode, self.n_splits = rep_mode, int(n_splits)
         self.c_summ = summ.c_struct()
         need = self.lib.ia_workspace_bytes(ctypes.byref(self.geom), self.max_sel, self.n_splits, _REP[rep_mode])
         if need < 0:
