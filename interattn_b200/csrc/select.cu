@@ -46,14 +46,14 @@ int read_and_clear_device_status(int* out) {
 
 namespace {
 
-constexpr int kGroups = 4;         // warp groups, one ring stage each at a time
+constexpr int kGroups = 3;         // warp groups, one ring stage each at a time
 constexpr int kGroupWarps = 4;     // warps per group: each takes head_dim / 4
 constexpr int kConsumerWarps = kGroups * kGroupWarps;
 constexpr int kWarps = kConsumerWarps + 1;  // + one TMA producer warp
 constexpr int kThreads = kWarps * 32;
 constexpr int kTileBlocks = 32;
 constexpr int kMaxStages = 8;
-constexpr uint32_t kWaitPolls = 4u << 20;  // bounded mbarrier wait (~0.3 s), then give up
+constexpr uint32_t kWaitPolls = 1u << 20;  // bounded mbarrier wait, then give up
 
 struct SelectParams {
   // TMA descriptors of the three summary arrays viewed as [rows, D] matrices
@@ -91,7 +91,7 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -102,10 +102,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // caller records that in the device status word and carries on (the results
 // are then garbage, but the GPU is not left spinning).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitPolls; ++i) {
+  // try_wait parks the thread for a hardware-defined time before it reports "not yet"
+  for (uint32_t i = 0; i < kWaitPolls; ++i)
     if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(32);
-  }
   return false;
 }
 // one 2-D tile (box) global -> shared, completing on an mbarrier; x = element column, y = row
@@ -116,6 +115,64 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// D(16x8, f32) += A(16x8, tf32, row-major) * B(8x8, tf32, col-major)
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// D(16x8, f32) += A(16x16, bf16, row-major) * B(16x8, bf16, col-major)
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Running softmax normalisers of one query row: m = max z, l = sum e^{z - m},
+// d = sum e^{z - m} cosh(delta).  Blocks are absorbed as they are scored and the
+// per-lane / per-warp states are merged afterwards, so no extra pass over the
+// blocks is needed for the normalisers.
+struct RowNorm { float m, l, d; };
+__device__ __forceinline__ void norm_absorb(RowNorm& a, float z, float ch) {
+  const float m = fmaxf(a.m, z);
+  const float sa = expf(a.m - m);  // a.m = -inf on first use: 0
+  const float w = expf(z - m);
+  a.l = fmaf(a.l, sa, w);
+  a.d = fmaf(a.d, sa, w * ch);
+  a.m = m;
+}
+__device__ __forceinline__ void norm_merge(RowNorm& a, float bm, float bl, float bd) {
+  const float m = fmaxf(a.m, bm);
+  if (m == -INFINITY) return;  // both empty
+  const float sa = expf(a.m - m), sb = expf(bm - m);
+  a.l = a.l * sa + bl * sb;
+  a.d = a.d * sa + bd * sb;
+  a.m = m;
+}
+// What the score needs from delta, and the block's contribution to the normalisers:
+//   A = cosh(delta) - 1,  th = tanh(delta / 2)
+__device__ __forceinline__ void delta_terms(float delta, float& ch, float& a_term, float& th) {
+  const float e = expf(delta);
+  ch = 0.5f * (e + 1.f / e);
+  a_term = ch - 1.f;
+  th = 1.f - 2.f / (e + 1.f);
+}
+
+// The tensor-core form of phase 1 needs exact operands: bf16 summaries / query
+// (exact in tf32 and bf16) and at most eight query rows per kv head.
+template <typename T, int G> constexpr bool kUseMma = (sizeof(T) == 2) && (G <= 8);
+
 // barrier among the 128 threads of one warp group (ids 1..kGroups; 0 is __syncthreads)
 __device__ __forceinline__ void group_sync(int group) {
   asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kGroupWarps * 32) : "memory");
@@ -167,44 +224,24 @@ __device__ __forceinline__ const E* swz(const unsigned char* vec_base, int row, 
 }
 
 // Fixed shared-memory carve-up (bytes), shared by the kernel and the launcher.
-template <int D, int G> struct SmemPlan {
+template <int D, int G, bool MMA> struct SmemPlan {
   static constexpr size_t bars = 2 * kMaxStages * 8;
-  static constexpr size_t hist = 256 * 4;
+  static constexpr size_t hist = 3 * 256 * 4;
   static constexpr size_t scan = 32 * 4;
-  static constexpr size_t red = (size_t)kWarps * 32 * 4;
+  static constexpr size_t red = (size_t)kWarps * 16 * 3 * 4 + (size_t)kWarps * 4 + 12;  // [warp][row][m,l,d] + b_max per warp
   static constexpr size_t norm = 4 * 16 * 4;
   static constexpr size_t state = 8 * 4;
   static constexpr size_t qrows = 2 * (size_t)G * D * 4;
-  static constexpr size_t part = (size_t)kConsumerWarps * 3 * G * 32 * 4;
+  static constexpr size_t part = MMA ? 0 : (size_t)kConsumerWarps * 3 * G * 32 * 4;
   static constexpr size_t fixed = bars + hist + scan + red + norm + state + qrows + part;
-  static size_t per_blocks(int nb_cap) { return (size_t)nb_cap * 4 * (2 + 2 * G); }
+  static size_t per_blocks(int nb_cap) { return (size_t)nb_cap * 4 * (2 + 3 * G); }
 };
-
-// exclusive block-wide scan of a 0/1 flag; returns this thread's prefix and the
-// block total.  scratch: kWarps ints.  Contains two __syncthreads().
-__device__ __forceinline__ int block_scan_flag(bool flag, int* scratch, int& total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t bal = __ballot_sync(0xffffffffu, flag);
-  const int within = __popc(bal & ((1u << lane) - 1u));
-  if (lane == 0) scratch[warp] = __popc(bal);
-  __syncthreads();
-  int before = 0, sum = 0;
-#pragma unroll
-  for (int w = 0; w < kWarps; ++w) {
-    const int c = scratch[w];
-    if (w < warp) before += c;
-    sum += c;
-  }
-  __syncthreads();
-  total = sum;
-  return before + within;
-}
 
 template <typename T, int D, int G>
 __global__ void __launch_bounds__(kThreads, 1)
 condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   using L = TileLayout<T, D>;
-  using P = SmemPlan<D, G>;
+  using P = SmemPlan<D, G, kUseMma<T, G>>;
   constexpr int DQ = D / kGroupWarps;  // head_dim slice of one warp of a group
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -219,25 +256,27 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   unsigned char* sp = smem_raw;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(sp);
   uint64_t* empty_bar = full_bar + kMaxStages;         sp += P::bars;
-  int* hist = reinterpret_cast<int*>(sp);              sp += P::hist;
+  int* hist = reinterpret_cast<int*>(sp);              sp += P::hist;   // three rotating 256-bin histograms
   int* scan_scratch = reinterpret_cast<int*>(sp);      sp += P::scan;
-  float* red_s = reinterpret_cast<float*>(sp);         sp += P::red;    // [kWarps][32]
-  float* norm_s = reinterpret_cast<float*>(sp);        sp += P::norm;   // z_m[16], z_l[16], denom[16], b_all
-  int* sel_state = reinterpret_cast<int*>(sp);         sp += P::state;
+  float* red_s = reinterpret_cast<float*>(sp);                          // [kWarps][16][3] row normalisers
+  float* redb_s = red_s + kWarps * 16 * 3;             sp += P::red;    // [kWarps] max value norm
+  float* norm_s = reinterpret_cast<float*>(sp);        sp += P::norm;   // z_m[16], 1/z_l[16], 2 b_all/denom[16]
+  sp += P::state;
   float* q_s = reinterpret_cast<float*>(sp);                            // [G][D]
   float* aq_s = q_s + G * D;                           sp += P::qrows;  // |q|
   float* part_s = reinterpret_cast<float*>(sp);        sp += P::part;   // [consumer warp][3G][32]
   float* vn_s = reinterpret_cast<float*>(sp);                           // [nb_cap]
   float* score_s = vn_s + nb_cap;                                       // [nb_cap]
-  float* z_s = score_s + nb_cap;                                        // [G][nb_cap]: z, later exp(z - z_m)
-  float* d_s = z_s + (size_t)G * nb_cap;                                // [G][nb_cap]: delta, later exp(delta)
+  float* z_s = score_s + nb_cap;                                        // [G][nb_cap]: z = s + log count
+  float* a_s = z_s + (size_t)G * nb_cap;                                // [G][nb_cap]: cosh(delta) - 1
+  float* t_s = a_s + (size_t)G * nb_cap;                                // [G][nb_cap]: tanh(delta / 2)
   unsigned char* stage_base = reinterpret_cast<unsigned char*>(
-      (reinterpret_cast<uintptr_t>(d_s + (size_t)G * nb_cap) + 1023) & ~uintptr_t(1023));
+      (reinterpret_cast<uintptr_t>(t_s + (size_t)G * nb_cap) + 1023) & ~uintptr_t(1023));
 
   if (tid == 0) {
     for (int s = 0; s < p.n_stages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kGroupWarps);
+      mbar_init(&empty_bar[s], kUseMma<T, G> ? 2 : kGroupWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -248,10 +287,20 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     aq_s[i] = fabsf(v);
   }
   const float* vn_g = p.v_norm_max + (int64_t)pair * p.max_blocks;
-  for (int b = tid; b < nb; b += kThreads) vn_s[b] = vn_g[b];
+  {
+    float bmax = 0.f;  // b_all = max_b v_norm_max[b]
+    for (int b = tid; b < nb; b += kThreads) {
+      const float v = vn_g[b];
+      vn_s[b] = v;
+      bmax = fmaxf(bmax, v);
+    }
+    bmax = warp_max(bmax);
+    if (lane == 0) redb_s[warp] = bmax;
+  }
   __syncthreads();
 
   const float root = sqrtf((float)D);
+  const float log_full = logf((float)p.block_size);
   const int64_t sum_row0 = (int64_t)pair * p.max_blocks;  // first summary row of this pair
 
   // ---- phase 1: stream the summaries, s / delta per (row, block) -----------------
@@ -284,12 +333,160 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       }
       __syncwarp();
     }
+  } else if constexpr (kUseMma<T, G>) {
+    // Tensor-core consumers.  A stage holds 32 blocks; the two warps of a slot
+    // take 16 blocks each as the M side of the MMAs, the query rows are the N
+    // side (padded to 8), head_dim is K.  All operands are exact: k_bar is cut
+    // into three tf32 pieces (11 + 11 + 2 bits), the bounds and the query are
+    // bf16; q+ = max(q, 0) and q- = min(q, 0) turn the reference's
+    // sum_d max(q k_max, q k_min) into k_max . q+ + k_min . q- (IMPL/core.py:520-530).
+    const int mh = warp & 1, slot = warp >> 1;
+    constexpr int kSlots = kConsumerWarps / 2;
+    const int n = lane >> 2, kq = lane & 3;
+    uint32_t bq[D / 8][2], bp[D / 16][2], bm[D / 16][2];
+#pragma unroll
+    for (int kk = 0; kk < D / 8; ++kk) {
+      bq[kk][0] = n < G ? __float_as_uint(q_s[n * D + kk * 8 + kq]) : 0u;
+      bq[kk][1] = n < G ? __float_as_uint(q_s[n * D + kk * 8 + kq + 4]) : 0u;
+    }
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float x0 = n < G ? q_s[n * D + kk * 16 + h * 8 + kq * 2] : 0.f;
+        const float x1 = n < G ? q_s[n * D + kk * 16 + h * 8 + kq * 2 + 1] : 0.f;
+        bp[kk][h] = pack_bf16(fmaxf(x0, 0.f), fmaxf(x1, 0.f));
+        bm[kk][h] = pack_bf16(fminf(x0, 0.f), fminf(x1, 0.f));
+      }
+    }
+    // ldmatrix row addressing: matrix m of the x4 = (rows 8 (m & 1) .., 16-byte chunk (m >> 1))
+    const int lm = lane >> 3, lr = lane & 7;
+    const int arow = mh * 16 + (lm & 1) * 8 + lr;
+    const uint32_t row_off = (uint32_t)(arow * 128);
+    const uint32_t row_xor = (uint32_t)(arow & 7);
+    RowNorm rn[2] = {{-INFINITY, 0.f, 0.f}, {-INFINITY, 0.f, 0.f}};
+    // A parity wait can only tell a phase from its neighbour: a consumer must
+    // never wait on a stage more than one use ahead of the producer.  With at
+    // most n_stages slots walking the tiles in order that holds (finishing tile
+    // t - n_slots implies every earlier tile, including t - n_stages, was filled).
+    const int n_slots = min(kSlots, p.n_stages);
+    bool alive = true;
+    for (int t = slot; slot < n_slots && t < n_tiles; t += n_slots) {
+      const int stage = t % p.n_stages;
+      const int use = t / p.n_stages;
+      if (alive && !mbar_wait(&full_bar[stage], (uint32_t)(use & 1))) {
+        alive = false;
+        if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
+      }
+      const uint32_t st = smem_u32(stage_base + (size_t)stage * L::bytes);
+      float cd[4] = {0.f, 0.f, 0.f, 0.f};
+      float xp[4] = {0.f, 0.f, 0.f, 0.f}, xm[4] = {0.f, 0.f, 0.f, 0.f};  // k_max . q+, k_max . q-
+      float np_[4] = {0.f, 0.f, 0.f, 0.f}, nm[4] = {0.f, 0.f, 0.f, 0.f};  // k_min . q+, k_min . q-
+#pragma unroll
+      for (int kk = 0; kk < D / 8; ++kk) {
+        const int byte = (kk * 8 + (lm >> 1) * 4) * 4;
+        uint32_t a[4], hi[4], md[4], lo[4];
+        ldmatrix_x4(st + (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4), a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          hi[i] = a[i] & 0xffffe000u;
+          const float r1 = __uint_as_float(a[i]) - __uint_as_float(hi[i]);
+          md[i] = __float_as_uint(r1) & 0xffffe000u;
+          lo[i] = __float_as_uint(r1 - __uint_as_float(md[i]));
+        }
+        mma_tf32(cd, hi, bq[kk]);
+        mma_tf32(cd, md, bq[kk]);
+        mma_tf32(cd, lo, bq[kk]);
+      }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const int byte = (kk * 16 + (lm >> 1) * 8) * 2;
+        const uint32_t off = (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4);
+        uint32_t a[4];
+        ldmatrix_x4(st + L::kbar_bytes + off, a);
+        mma_bf16(xp, a, bp[kk]);
+        mma_bf16(xm, a, bm[kk]);
+        ldmatrix_x4(st + L::kbar_bytes + L::bnd_bytes + off, a);
+        mma_bf16(np_, a, bp[kk]);
+        mma_bf16(nm, a, bm[kk]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp is done with the stage
+      // Accumulator element e of this lane = (block row n + 8 (e >> 1), query row 2 kq + (e & 1)).
+      // With G <= 4 only the lanes kq < 2 hold real rows: they hand their e = 2, 3
+      // to the idle lanes kq + 2, so every lane finishes two (block, row) entries.
+      auto finish = [&](int g, int b, float dotv, float up, float lw, RowNorm& acc) {
+        if (g < G && b < nb) {
+          const int count = min(p.block_size, prefix - b * p.block_size);
+          const float s = dotv / root;
+          const float upper = up / root;  // sum_d max(q k_max, q k_min)
+          const float lower = lw / root;  // sum_d min(q k_max, q k_min)
+          const float delta = fmaxf(fabsf(upper - s), fabsf(lower - s));
+          const float z = (count == p.block_size ? log_full : logf((float)count)) + s;
+          float ch, a_term, th;
+          delta_terms(delta, ch, a_term, th);
+          norm_absorb(acc, z, ch);
+          z_s[g * nb_cap + b] = z;
+          a_s[g * nb_cap + b] = a_term;
+          t_s[g * nb_cap + b] = th;
+          const int64_t o = ((int64_t)pair * G + g) * p.max_blocks + b;
+          if (p.aux.s != nullptr) p.aux.s[o] = s;
+          if (p.aux.z != nullptr) p.aux.z[o] = z;
+          if (p.aux.delta != nullptr) p.aux.delta[o] = delta;
+        }
+      };
+      const int b0 = t * kTileBlocks + mh * 16 + n;
+      if constexpr (G <= 4) {
+        float dv[2], up[2], lw[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float d2 = __shfl_xor_sync(0xffffffffu, cd[2 + j], 2);
+          const float u2 = __shfl_xor_sync(0xffffffffu, xp[2 + j] + nm[2 + j], 2);
+          const float l2 = __shfl_xor_sync(0xffffffffu, np_[2 + j] + xm[2 + j], 2);
+          dv[j] = kq < 2 ? cd[j] : d2;
+          up[j] = kq < 2 ? xp[j] + nm[j] : u2;
+          lw[j] = kq < 2 ? np_[j] + xm[j] : l2;
+        }
+        const int b = b0 + (kq >> 1) * 8;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) finish((kq & 1) * 2 + j, b, dv[j], up[j], lw[j], rn[j]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          finish(kq * 2 + (e & 1), b0 + (e >> 1) * 8, cd[e], xp[e] + nm[e], np_[e] + xm[e], rn[e & 1]);
+      }
+    }
+    // rows held by this lane: G <= 4: 2 (kq & 1) + {0, 1}, shared by the 16 lanes with the same
+    // kq & 1; else 2 kq + {0, 1}, shared by 8 lanes.  Merge them; one lane per row reports.
+    constexpr int kFirstXor = G <= 4 ? 2 : 4;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+#pragma unroll
+      for (int o = kFirstXor; o < 32; o <<= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, rn[r].m, o);
+        const float ol = __shfl_xor_sync(0xffffffffu, rn[r].l, o);
+        const float od = __shfl_xor_sync(0xffffffffu, rn[r].d, o);
+        norm_merge(rn[r], om, ol, od);
+      }
+      const int g = (G <= 4 ? (kq & 1) : kq) * 2 + r;
+      const bool reporter = (G <= 4) ? (lane < 2) : (n == 0);
+      if (reporter && g < G) {
+        red_s[(warp * 16 + g) * 3 + 0] = rn[r].m;
+        red_s[(warp * 16 + g) * 3 + 1] = rn[r].l;
+        red_s[(warp * 16 + g) * 3 + 2] = rn[r].d;
+      }
+    }
   } else {
     const int group = warp / kGroupWarps, wq = warp % kGroupWarps;
     float* my_part = part_s + (size_t)warp * 3 * G * 32;
     const float* grp_part = part_s + (size_t)group * kGroupWarps * 3 * G * 32;
+    constexpr int kRowsPerWarp = (G + kGroupWarps - 1) / kGroupWarps;
+    RowNorm rn[kRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) rn[r] = RowNorm{-INFINITY, 0.f, 0.f};
+    const int n_groups = min(kGroups, p.n_stages);  // see the note on parity waits above
     bool alive = true;
-    for (int t = group; t < n_tiles; t += kGroups) {
+    for (int t = group; group < n_groups && t < n_tiles; t += n_groups) {
       const int stage = t % p.n_stages;
       const int use = t / p.n_stages;
       if (alive && !mbar_wait(&full_bar[stage], (uint32_t)(use & 1))) {
@@ -348,7 +545,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       const int b = t * kTileBlocks + lane;
       if (b < nb) {
         const int count = min(p.block_size, prefix - b * p.block_size);
-        const float logc = logf((float)count);
+        const float logc = count == p.block_size ? log_full : logf((float)count);
         for (int g = wq; g < G; g += kGroupWarps) {
           float v[3];
 #pragma unroll
@@ -364,8 +561,12 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           const float lower = (0.5f * (v[1] - v[2])) / root;
           const float delta = fmaxf(fabsf(upper - s), fabsf(lower - s));
           const float z = logc + s;
+          float ch, a_term, th;
+          delta_terms(delta, ch, a_term, th);
+          norm_absorb(rn[g / kGroupWarps], z, ch);
           z_s[g * nb_cap + b] = z;
-          d_s[g * nb_cap + b] = delta;
+          a_s[g * nb_cap + b] = a_term;
+          t_s[g * nb_cap + b] = th;
           const int64_t o = ((int64_t)pair * G + g) * p.max_blocks + b;
           if (p.aux.s != nullptr) p.aux.s[o] = s;
           if (p.aux.z != nullptr) p.aux.z[o] = z;
@@ -374,103 +575,76 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       }
       group_sync(group);  // partial sums may be overwritten from here on
     }
+    // this warp scored rows wq, wq + 4, ...: merge its 32 lanes, lane 0 reports
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, rn[r].m, o);
+        const float ol = __shfl_xor_sync(0xffffffffu, rn[r].l, o);
+        const float od = __shfl_xor_sync(0xffffffffu, rn[r].d, o);
+        norm_merge(rn[r], om, ol, od);
+      }
+      const int g = wq + r * kGroupWarps;
+      if (lane == 0 && g < G) {
+        red_s[(warp * 16 + g) * 3 + 0] = rn[r].m;
+        red_s[(warp * 16 + g) * 3 + 1] = rn[r].l;
+        red_s[(warp * 16 + g) * 3 + 2] = rn[r].d;
+      }
+    }
   }
   __syncthreads();
 
-  // ---- phase 2: per-row normalisers (all threads) ----------------------------------
-  {
-    float zmax[G];
+  // ---- phase 2: merge the warps' row normalisers (warp g merges row g as a tree) ---------
+  for (int g = warp; g < G; g += kWarps) {
+    // which warps scored row g: every tensor-core consumer warp, or the warps with
+    // w mod 4 = g mod 4 (fma form); the others left nothing
+    const bool has = lane < kConsumerWarps && (kUseMma<T, G> ? true : (lane % kGroupWarps == g % kGroupWarps));
+    RowNorm tot{-INFINITY, 0.f, 0.f};
+    if (has) tot = RowNorm{red_s[(lane * 16 + g) * 3], red_s[(lane * 16 + g) * 3 + 1], red_s[(lane * 16 + g) * 3 + 2]};
 #pragma unroll
-    for (int g = 0; g < G; ++g) zmax[g] = -INFINITY;
-    float bmax = 0.f;
-    for (int b = tid; b < nb; b += kThreads) {
-      bmax = fmaxf(bmax, vn_s[b]);
-#pragma unroll
-      for (int g = 0; g < G; ++g) zmax[g] = fmaxf(zmax[g], z_s[g * nb_cap + b]);
+    for (int o = 1; o < 16; o <<= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, tot.m, o);
+      const float ol = __shfl_xor_sync(0xffffffffu, tot.l, o);
+      const float od = __shfl_xor_sync(0xffffffffu, tot.d, o);
+      norm_merge(tot, om, ol, od);
     }
-    bmax = warp_max(bmax);
-#pragma unroll
-    for (int g = 0; g < G; ++g) zmax[g] = warp_max(zmax[g]);
+    float b_all = lane < kWarps ? redb_s[lane] : 0.f;
+    b_all = warp_max(b_all);
+
     if (lane == 0) {
-#pragma unroll
-      for (int g = 0; g < G; ++g) red_s[warp * 32 + g] = zmax[g];
-      red_s[warp * 32 + 31] = bmax;
-    }
-  }
-  __syncthreads();
-  if (tid < G) {
-    float m = -INFINITY;
-    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, red_s[w * 32 + tid]);
-    norm_s[tid] = m;
-  } else if (tid == 31) {
-    float m = 0.f;
-    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, red_s[w * 32 + 31]);
-    norm_s[48] = m;
-  }
-  __syncthreads();
-  {
-    // z_l = sum_b exp(z - z_m);  dn = sum_b exp(z - z_m) cosh(delta).  The arrays are
-    // rewritten in place with exp(z - z_m) and exp(delta) for the scoring pass.
-    float zl[G], dn[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) { zl[g] = 0.f; dn[g] = 0.f; }
-    for (int b = tid; b < nb; b += kThreads) {
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float ez = expf(z_s[g * nb_cap + b] - norm_s[g]);
-        const float e = expf(d_s[g * nb_cap + b]);
-        const float ch = 0.5f * (e + 1.f / e);
-        zl[g] += ez;
-        dn[g] = fmaf(ez, ch, dn[g]);
-        z_s[g * nb_cap + b] = ez;
-        d_s[g * nb_cap + b] = e;
+      const float denom = fmaxf(tot.d / tot.l, 1e-30f);  // sum_b softmax(z)_b cosh(delta_b)
+      norm_s[g] = tot.m;
+      norm_s[16 + g] = 1.f / tot.l;
+      norm_s[32 + g] = 2.f * b_all / denom;
+      if (p.aux.globals != nullptr) {
+        // [batch, 4, rows]: (z_m, z_l) and a normaliser pair (c_m, c_l) with
+        // c_l e^{c_m} = sum_b e^{z_b} cosh(delta_b); here c_m = z_m.
+        const int rows = p.n_kv_heads * G;
+        const int head = pair - seq * p.n_kv_heads;
+        float* gl = p.aux.globals + (int64_t)seq * 4 * rows + head * G + g;
+        gl[0 * rows] = tot.m;
+        gl[1 * rows] = tot.l;
+        gl[2 * rows] = tot.m;
+        gl[3 * rows] = tot.d;
       }
-    }
-#pragma unroll
-    for (int g = 0; g < G; ++g) { zl[g] = warp_sum(zl[g]); dn[g] = warp_sum(dn[g]); }
-    if (lane == 0) {
-#pragma unroll
-      for (int g = 0; g < G; ++g) { red_s[warp * 32 + g] = zl[g]; red_s[warp * 32 + 16 + g] = dn[g]; }
-    }
-  }
-  __syncthreads();
-  if (tid < G) {
-    float zl = 0.f, dn = 0.f;
-    for (int w = 0; w < kWarps; ++w) { zl += red_s[w * 32 + tid]; dn += red_s[w * 32 + 16 + tid]; }
-    norm_s[16 + tid] = zl;
-    norm_s[32 + tid] = fmaxf(dn / zl, 1e-30f);  // sum_b softmax(z)_b cosh(delta_b)
-    if (p.aux.globals != nullptr) {
-      // [batch, 4, rows]: (z_m, z_l) and a normaliser pair (c_m, c_l) with
-      // c_l e^{c_m} = sum_b e^{z_b} cosh(delta_b); here c_m = z_m.
-      const int rows = p.n_kv_heads * G;
-      const int head = pair - seq * p.n_kv_heads;
-      float* gl = p.aux.globals + (int64_t)seq * 4 * rows + head * G + tid;
-      gl[0 * rows] = norm_s[tid];
-      gl[1 * rows] = zl;
-      gl[2 * rows] = norm_s[tid];
-      gl[3 * rows] = dn;
     }
   }
   __syncthreads();
 
   // ---- phase 3: GQA-mean condition score -------------------------------------------
-  {
-    const float b_all = norm_s[48];
-    for (int b = tid; b < nb; b += kThreads) {
-      const float b_c = vn_s[b];
-      float sum = 0.f;
+  // cond = softmax(z) (2 b_all (cosh d - 1) / denom + 2 b_c tanh(d / 2))   (IMPL/core.py:535-544)
+  for (int b = tid; b < nb; b += kThreads) {
+    const float two_bc = 2.f * vn_s[b];
+    float sum = 0.f;
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float pm = z_s[g * nb_cap + b] / norm_s[16 + g];
-        const float e = d_s[g * nb_cap + b];
-        const float ch = 0.5f * (e + 1.f / e);
-        const float th = 1.f - 2.f / (e + 1.f);  // tanh(delta / 2)
-        sum += pm * (2.f * b_all * (ch - 1.f) / norm_s[32 + g] + 2.f * b_c * th);
-      }
-      const float sc = sum / (float)G;
-      score_s[b] = sc;
-      if (p.aux.score != nullptr) p.aux.score[(int64_t)pair * p.max_blocks + b] = sc;
+    for (int g = 0; g < G; ++g) {
+      const float pm = expf(z_s[g * nb_cap + b] - norm_s[g]) * norm_s[16 + g];
+      sum += pm * fmaf(norm_s[32 + g], a_s[g * nb_cap + b], two_bc * t_s[g * nb_cap + b]);
     }
+    const float sc = sum / (float)G;
+    score_s[b] = sc;
+    if (p.aux.score != nullptr) p.aux.score[(int64_t)pair * p.max_blocks + b] = sc;
   }
   __syncthreads();
 
@@ -480,76 +654,114 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   int take_equal = 0;
   const int k_eff = (p.mode == IA_SELECT_TOPK) ? min(min(p.top_k, nb), p.max_sel) : 0;
   if (k_eff > 0 && k_eff < nb) {
+    // Radix select of the k_eff-th largest key, 8 bits per pass.  Three
+    // histograms rotate: pass p fills hist[p % 3] and clears hist[(p + 1) % 3]
+    // (last read two passes ago), and every warp resolves the digit for itself
+    // from the finished histogram - so a pass needs one barrier.
     uint32_t fixed = 0, fixed_mask = 0;
     int remaining = k_eff;
+    for (int i = tid; i < 256; i += kThreads) hist[i] = 0;
+    __syncthreads();
+#pragma unroll 1  // executed once per launch: keep the cold code short (it is fetched from L2)
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
-      for (int i = tid; i < 256; i += kThreads) hist[i] = 0;
-      __syncthreads();
-      for (int b = tid; b < nb; b += kThreads) {
-        const uint32_t key = order_key(score_s[b]);
-        if ((key & fixed_mask) == fixed) atomicAdd(&hist[(key >> shift) & 255u], 1);
+      int* h = hist + (pass % 3) * 256;
+      int* h_next = hist + ((pass + 1) % 3) * 256;
+      for (int i = tid; i < 256; i += kThreads) h_next[i] = 0;
+      for (int base = 0; base < nb; base += kThreads) {
+        const int b = base + tid;
+        const uint32_t key = b < nb ? order_key(score_s[b]) : 0u;
+        const bool live = b < nb && (key & fixed_mask) == fixed;
+        const uint32_t digit = (key >> shift) & 255u;
+        // scores cluster in a few bins: lanes that share the first live lane's digit
+        // send one atomic together, the rest go one by one
+        const uint32_t alive_mask = __ballot_sync(0xffffffffu, live);
+        if (alive_mask != 0u) {
+          const uint32_t lead_digit = __shfl_sync(0xffffffffu, digit, __ffs(alive_mask) - 1);
+          const uint32_t same = __ballot_sync(0xffffffffu, live && digit == lead_digit);
+          if (lane == __ffs(alive_mask) - 1) atomicAdd(&h[lead_digit], __popc(same));
+          if (live && digit != lead_digit) atomicAdd(&h[digit], 1);
+        }
       }
       __syncthreads();
-      if (warp == 0) {
-        // lane owns bins [8*lane, 8*lane+8); walk from the top digit down
-        int mine = 0;
+      // lane owns bins [8 lane, 8 lane + 8); `above` = keys in the bins of higher lanes
+      int c[8], mine = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) mine += hist[lane * 8 + i];
-        int above = 0;  // keys in the bins owned by higher lanes
-        for (int l = 31; l >= 0; --l) {
-          const int v = __shfl_sync(0xffffffffu, mine, l);
-          if (l > lane) above += v;
-        }
-        if ((above < remaining) && (above + mine >= remaining)) {
-          int acc = above, digit = 0;
-          for (int i = 7; i >= 0; --i) {
-            const int c = hist[lane * 8 + i];
-            if (acc + c >= remaining) { digit = lane * 8 + i; break; }
-            acc += c;
-          }
-          sel_state[0] = (int)(fixed | ((uint32_t)digit << shift));
-          sel_state[1] = remaining - acc;
-        }
+      for (int i = 0; i < 8; ++i) { c[i] = h[lane * 8 + i]; mine += c[i]; }
+      int incl = mine;  // inclusive suffix sum over lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_down_sync(0xffffffffu, incl, o);
+        if (lane + o < 32) incl += v;
       }
-      __syncthreads();
-      fixed = (uint32_t)sel_state[0];
-      remaining = sel_state[1];
+      const int above = incl - mine;
+      const bool owner = (above < remaining) && (incl >= remaining);
+      int digit = 0, left = 0;
+      if (owner) {
+        int acc = above;
+#pragma unroll
+        for (int i = 7; i >= 0; --i) {
+          if (acc + c[i] >= remaining) { digit = lane * 8 + i; break; }
+          acc += c[i];
+        }
+        left = remaining - acc;
+      }
+      const int src = max(__ffs(__ballot_sync(0xffffffffu, owner)) - 1, 0);  // exactly one owner lane
+      digit = __shfl_sync(0xffffffffu, digit, src);
+      remaining = __shfl_sync(0xffffffffu, left, src);
+      fixed |= (uint32_t)digit << shift;
       fixed_mask |= 255u << shift;
-      __syncthreads();
     }
     thr_key = fixed;
     take_equal = remaining;
   }
 
-  int n_written = 0, n_equal_seen = 0;
+  // Ordered compaction.  Selected = key above the threshold, plus the first
+  // `take_equal` keys equal to it in index order; one block scan of the packed
+  // counts (greater: low 16 bits, equal: high 16 bits) gives every output slot.
+  int n_written = 0;
   const bool any = (p.mode == IA_SELECT_EPS) ? (nb > 0) : (k_eff > 0);
   if (any) {
     const bool everything = (p.mode == IA_SELECT_TOPK) && (k_eff >= nb);
+    int gt_seen = 0, eq_seen = 0;
     for (int base = 0; base < nb; base += kThreads) {
       const int b = base + tid;
       const bool in = b < nb;
       const float sc = in ? score_s[b] : 0.f;
-      bool take;
+      bool gt, eq = false;
       if (p.mode == IA_SELECT_EPS) {
-        take = in && (sc > p.eps);
+        gt = in && (sc > p.eps);
       } else if (everything) {
-        take = in;
+        gt = in;
       } else {
         const uint32_t key = order_key(sc);
-        const bool eq = in && key == thr_key;
-        int eq_total;
-        const int eq_before = block_scan_flag(eq, scan_scratch, eq_total);
-        take = in && (key > thr_key || (eq && n_equal_seen + eq_before < take_equal));
-        n_equal_seen += eq_total;
+        gt = in && key > thr_key;
+        eq = in && key == thr_key;
       }
-      int total;
-      const int pos = block_scan_flag(take, scan_scratch, total);
-      if (take && n_written + pos < p.max_sel) out_idx[n_written + pos] = b;
-      n_written += total;
+      // exclusive scan of (gt, eq) over the block
+      const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
+      const uint32_t below = (1u << lane) - 1u;
+      if (lane == 0) scan_scratch[warp] = __popc(bg) | (__popc(be) << 16);
+      __syncthreads();
+      int packed_before = 0, packed_total = 0;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const int c = scan_scratch[w];
+        if (w < warp) packed_before += c;
+        packed_total += c;
+      }
+      __syncthreads();
+      const int gt_before = gt_seen + (packed_before & 0xffff) + __popc(bg & below);
+      const int eq_before = eq_seen + (packed_before >> 16) + __popc(be & below);
+      const bool take = gt || (eq && eq_before < take_equal);
+      const int pos = gt_before + min(eq_before, take_equal);
+      if (take && pos >= 0 && pos < p.max_sel) out_idx[pos] = b;
+      gt_seen += packed_total & 0xffff;
+      eq_seen += packed_total >> 16;
     }
+    n_written = gt_seen + min(eq_seen, take_equal);
   }
-  const int count = min(n_written, p.max_sel);
+  const int count = max(min(n_written, p.max_sel), 0);
   for (int i = count + tid; i < p.max_sel; i += kThreads) out_idx[i] = -1;
   if (tid == 0) p.sel_count[pair] = count;
 }
@@ -592,7 +804,7 @@ static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t 
 template <typename T, int D, int G>
 static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stream) {
   using L = TileLayout<T, D>;
-  using P = SmemPlan<D, G>;
+  using P = SmemPlan<D, G, kUseMma<T, G>>;
   SelectParams p = base;
   p.nb_cap = (p.max_blocks + 31) & ~31;
   const size_t fixed = P::fixed + P::per_blocks(p.nb_cap) + 1024;

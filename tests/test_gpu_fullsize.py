@@ -1,0 +1,128 @@
+"""Full-size configurations on the GPU: size-independent properties over every
+(sequence, kv head), and oracle parity on a few sampled sequences.
+
+The CPU oracle cannot run a whole 32k / 128k-context batch in test time, so at
+the benchmark sizes the checks are: the selection is a valid top-k of the
+kernel's own score vector (count, order, uniqueness, every kept score >= every
+dropped score), split-KV invariance of the attention output, no device status
+bit, and - for sampled sequences copied back to the host - the same index and
+output parity against the oracle as the small cases.
+"""
+
+from dataclasses import replace
+
+import pytest
+import torch
+
+from oracle import condition_block_oracle as orc
+from oracle.configs import CONFIGS
+
+pytestmark = pytest.mark.gpu
+
+
+def _device_case(cfg, seed=0):
+    """A full-size paged KV cache generated on the device (same distributions as
+    the seeded CPU generator)."""
+    from interattn_b200 import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(seed)
+    P, D, hkv = cfg.page_size, cfg.head_dim, cfg.n_kv_heads
+    pages_per_seq = [(n + s + P - 1) // P for n, s in zip(cfg.prefix_lens, cfg.suffix_lens)]
+    n_pages, max_pages = sum(pages_per_seq), max(pages_per_seq)
+    k_pool = torch.randn((n_pages, hkv, P, D), generator=g, device=dev)
+    if cfg.k_channel_sigma > 0:
+        k_pool *= torch.exp(cfg.k_channel_sigma * torch.randn((D,), generator=g, device=dev))
+    k_pool = k_pool.to(cfg.torch_dtype)
+    v_pool = torch.randn((n_pages, hkv, P, D), generator=g, device=dev).to(cfg.torch_dtype)
+    perm = torch.randperm(n_pages, generator=g, device=dev).to(torch.int32)
+    table = torch.zeros((cfg.batch, max_pages), dtype=torch.int32, device=dev)
+    at = 0
+    for b, n in enumerate(pages_per_seq):
+        table[b, :n] = perm[at: at + n]
+        at += n
+    prefix = torch.tensor(cfg.prefix_lens, dtype=torch.int32, device=dev)
+    seq = torch.tensor([p + s for p, s in zip(cfg.prefix_lens, cfg.suffix_lens)], dtype=torch.int32, device=dev)
+    q = torch.randn((cfg.batch, cfg.n_q_heads, D), generator=g, device=dev).to(cfg.torch_dtype)
+    return q, ops.PagedKV(k_pool, v_pool, table, prefix, seq)
+
+
+FULL = [
+    ("cfg2_llama8b_32k", CONFIGS["cfg2_llama8b_32k"], [0, 15]),
+    ("cfg4_longctx_128k", CONFIGS["cfg4_longctx_128k"], [3]),
+    ("cfg5_llama70b_ragged", replace(CONFIGS["cfg5_llama70b_ragged"], suffix_lens=(3,) * 64), [0, 37]),
+]
+
+
+@pytest.mark.parametrize("name,cfg,sample", FULL, ids=[f[0] for f in FULL])
+def test_full_size_properties_and_sampled_parity(name, cfg, sample):
+    from interattn_b200 import ops
+    q, kv = _device_case(cfg)
+    nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb)
+    idx, cnt, aux = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, want=("score", "z"))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+
+    # ---- every (sequence, kv head): a valid top-k of the kernel's own scores ----
+    nb_seq = torch.tensor([(n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens], device=q.device)
+    want_cnt = torch.minimum(nb_seq, torch.tensor(cfg.top_k, device=q.device))[:, None].expand(-1, cfg.n_kv_heads)
+    assert torch.equal(cnt.long(), want_cnt)
+    pos = torch.arange(idx.shape[-1], device=q.device)[None, None, :]
+    live = pos < cnt[..., None]
+    assert bool(((idx >= 0) & (idx < nb_seq[:, None, None]))[live].all())
+    assert bool((idx == -1)[~live].all())
+    inc = (idx[..., 1:] > idx[..., :-1]) | ~live[..., 1:]
+    assert bool(inc.all()), "indices must be strictly ascending"
+    score = aux["score"]
+    assert bool(torch.isfinite(score).all())
+    chosen = torch.zeros((*score.shape[:2], nb + 1), dtype=torch.bool, device=q.device)
+    chosen.scatter_(2, torch.where(live, idx, torch.full_like(idx, nb)).long(), live)  # padding -> spare column
+    chosen = chosen[..., :nb]
+    exists = torch.arange(nb, device=q.device)[None, None, :] < nb_seq[:, None, None]
+    kept_min = torch.where(chosen, score, torch.full_like(score, float("inf"))).amin(dim=2)
+    dropped_max = torch.where(exists & ~chosen, score, torch.full_like(score, float("-inf"))).amax(dim=2)
+    assert bool((kept_min >= dropped_max).all()), "a dropped block outscores a kept one"
+
+    # ---- split-KV invariance of the attention output --------------------------------
+    outs = []
+    for n_splits in (1, 2, 5):
+        o, lse = ops.sparse_decode(q, kv, idx, cnt, block_size=cfg.block_size, max_blocks=nb, n_splits=n_splits)
+        outs.append(ops.finalize(o, lse, torch.float32))
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(outs[0]).all())
+    for other in outs[1:]:
+        torch.testing.assert_close(other, outs[0], rtol=1e-2, atol=3e-3)
+    hyb_o, hyb_lse = ops.sparse_decode(q, kv, idx, cnt, block_size=cfg.block_size, max_blocks=nb, rep_mode="hybrid",
+                                       summ=summ, z=aux["z"], n_splits=2)
+    hyb = ops.finalize(hyb_o, hyb_lse, torch.float32)
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k)
+    one_call = step.step(q).float()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(one_call, outs[0], rtol=1e-2, atol=2e-2)
+
+    # ---- sampled sequences against the CPU oracle ----------------------------------------
+    g = cfg.group_size
+    table = kv.block_table.cpu()
+    for b in sample:
+        plen, slen = cfg.prefix_lens[b], cfg.prefix_lens[b] + cfg.suffix_lens[b]
+        n_pg = (slen + cfg.page_size - 1) // cfg.page_size
+        pages = table[b, :n_pg].long()
+        k_all = kv.k_pool[pages.to(q.device)].permute(1, 0, 2, 3).reshape(cfg.n_kv_heads, -1, cfg.head_dim)[:, :slen].cpu()
+        v_all = kv.v_pool[pages.to(q.device)].permute(1, 0, 2, 3).reshape(cfg.n_kv_heads, -1, cfg.head_dim)[:, :slen].cpu()
+        counts = orc.block_counts(plen, cfg.block_size)
+        n = counts.numel()
+        osum = orc.Summaries(summ.k_bar[b, :, :n].cpu(), summ.v_bar[b, :, :n].cpu(), summ.k_max[b, :, :n].cpu(),
+                             summ.k_min[b, :, :n].cpu(), summ.v_norm_max[b, :, :n].cpu(), counts, cfg.block_size)
+        want_summ = orc.block_summaries(k_all[:, :plen], v_all[:, :plen], cfg.block_size, storage="mixed")
+        assert torch.equal(osum.k_max.float(), want_summ.k_max.float())
+        assert torch.allclose(osum.k_bar, want_summ.k_bar, rtol=2e-6, atol=2e-6)
+        qg = q[b].cpu().reshape(cfg.n_kv_heads, g, cfg.head_dim).float()
+        terms = orc.condition_terms(qg, osum)
+        ranked, mask = orc.select_topk(terms["score"], counts, cfg.top_k)
+        for h in range(cfg.n_kv_heads):
+            got = idx[b, h, : int(cnt[b, h])].cpu().tolist()
+            assert got == sorted(ranked[h]), f"{name} seq {b} head {h}: selected blocks differ from the oracle"
+        for rep_mode, got in (("sparse_only", outs[0]), ("hybrid", hyb)):
+            want = orc.decode_attention(qg, k_all, v_all, plen, cfg.block_size, mask, rep_mode=rep_mode,
+                                        z=terms["z"], v_bar=osum.v_bar)
+            torch.testing.assert_close(got[b].cpu().reshape(want.shape), want, rtol=1e-2, atol=2e-2)
