@@ -144,7 +144,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -303,10 +303,13 @@ def run_gpu_arm(args):
                 peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured"
         except (OSError, KeyError, ValueError):
             pass
-        traffic = None
+        traffic = None   # DRAM bytes per launch of the attention kernel, from the committed ncu summary
         try:
-            with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
-                traffic = json.load(f).get(args.workload, {}).get("sparse_decode_bytes_per_launch")
+            with open(os.path.join(ROOT, "profiles", "dram_traffic.txt")) as f:
+                for ln in f:
+                    parts = ln.split()
+                    if len(parts) == 3 and parts[0] == args.workload and parts[1] == "sparse_decode":
+                        traffic = int(parts[2])
         except (OSError, ValueError):
             pass
         att_gbs = kv_bytes / (att_ms * 1e-3) / 1e9
