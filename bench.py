@@ -360,10 +360,75 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_split_kv_arm(args):
+    """Long-context split-KV (strong scaling): the blocks of every sequence are cut
+    into contiguous ranges, one per rank; every rank selects globally from the
+    replicated summaries, attends over its range and the ranks all-gather (o, lse)
+    over NCCL before the merge.  A step is the whole exchange."""
+    import torch
+    import torch.distributed as dist
+    from interattn_b200 import ops, partition
+    from oracle.configs import CONFIGS
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=device)
+    cfg = CONFIGS[args.workload]
+    nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
+    n_pools = max(1, args.layer_pools)
+    steps_obj = []
+    for l in range(n_pools):
+        kv = make_device_layer(cfg, device, seed=l)      # same seed on every rank: a rank reads only its range
+        summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb)
+        g = torch.Generator(device=device).manual_seed(77 + l)
+        q = torch.randn((cfg.batch, cfg.n_q_heads, cfg.head_dim), generator=g, device=device).to(cfg.torch_dtype)
+        steps_obj.append(partition.cuda_split_kv_step(q, kv, summ, top_k=cfg.top_k, rep_mode=args.rep_mode,
+                                                      n_splits=args.n_splits or 4))
+    K, W = args.steps, args.warmup
+
+    def sync_all():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for i in range(W):
+        steps_obj[i % n_pools].run(nb)
+    sync_all()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(K):
+        out = steps_obj[i % n_pools].run(nb)
+    t1.record()
+    sync_all()
+    clocks = sampler.stop()
+    times = torch.tensor([t0.elapsed_time(t1)], device=device, dtype=torch.float64)
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = float(times[0])
+        line = {
+            "metric": METRIC, "value": cfg.batch * K / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": cfg.batch, "context": max(cfg.prefix_lens),
+                       "top_k": cfg.top_k, "rep_mode": args.rep_mode, "parallelism": f"split-kv x{world}",
+                       "exchange": "all_gather of (o, lse) partials, selection replicated"},
+            "us_per_layer": 1e3 * ms / K, "gpu_launches": 5 * K, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "cfg4_longctx_128k" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        run_split_kv_arm(args)
     else:
         run_gpu_arm(args)
 

@@ -1,0 +1,152 @@
+"""1/2/4/8-GPU partitioning of the decode-attention layer-step.
+
+Two ways the step shards (one process per GPU, ``torch.distributed``):
+
+* **batch x kv-head sharding** - the units (sequence, kv head) share nothing:
+  summaries, selection, pages and output rows are all per unit.  Each rank
+  owns a subset of units and runs the ordinary single-GPU step on them; there
+  is no collective on the data path.  ``plan_unit_shards`` balances the
+  subsets by attended tokens (longest-processing-time greedy), which matters
+  for ragged batches.
+
+* **split-KV** for long single sequences - each rank owns a contiguous range
+  of logical blocks of every sequence (their K/V pages).  Block summaries are
+  small (about 1 KB per 64 tokens) and are replicated, so every rank computes
+  the same global selection with no exchange; it then attends over the
+  selected blocks inside its own range (the suffix lives on the last rank)
+  and the ranks all-gather their normalised partials ``(o, lse)`` -
+  ``rows x (D + 1)`` floats per rank, tens of KB - over NCCL / NVLink and
+  merge them with the same log-sum-exp finalize kernel that merges split-KV
+  parts inside one GPU.
+
+The reference has no multi-GPU form of this path; its single-GPU building
+block is the ``(acc, m, l)`` merge of
+``condition_block_triton_impl/legacy.py:765-794``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+# --------------------------------------------------------------------------
+# plans (pure host arithmetic)
+# --------------------------------------------------------------------------
+
+def plan_block_ranges(n_blocks: int, world: int) -> List[Tuple[int, int]]:
+    """Contiguous, near-equal block ranges [lo, hi) for ranks 0..world-1 (some may be empty)."""
+    if world <= 0 or n_blocks < 0:
+        raise ValueError("world must be positive and n_blocks non-negative")
+    return [(n_blocks * r // world, n_blocks * (r + 1) // world) for r in range(world)]
+
+
+def unit_costs(prefix_lens: Sequence[int], n_kv_heads: int, block_size: int, top_k: int,
+               suffix_lens: Optional[Sequence[int]] = None) -> List[int]:
+    """Attended tokens of every unit (sequence-major, then kv head): min(k, blocks) * block + suffix."""
+    costs = []
+    for i, n in enumerate(prefix_lens):
+        blocks = (int(n) + block_size - 1) // block_size
+        tokens = min(int(top_k), blocks) * block_size + (int(suffix_lens[i]) if suffix_lens is not None else 0)
+        costs.extend([tokens] * n_kv_heads)
+    return costs
+
+
+def plan_unit_shards(costs: Sequence[int], world: int) -> List[List[int]]:
+    """Assign units to ranks, heaviest first onto the lightest rank; ties go to the lower rank.
+    Returns, per rank, the sorted unit ids it owns."""
+    if world <= 0:
+        raise ValueError("world must be positive")
+    loads = [0] * world
+    owned: List[List[int]] = [[] for _ in range(world)]
+    for unit in sorted(range(len(costs)), key=lambda u: (-costs[u], u)):
+        r = min(range(world), key=lambda i: (loads[i], i))
+        owned[r].append(unit)
+        loads[r] += costs[unit]
+    return [sorted(x) for x in owned]
+
+
+def plan_head_shards(n_kv_heads: int, world: int) -> List[Tuple[int, int]]:
+    """kv heads [lo, hi) per rank when the head count divides over the ranks
+    (8 kv heads: one per GPU on 8, two on 4, four on 2)."""
+    if n_kv_heads % world != 0:
+        raise ValueError(f"{n_kv_heads} kv heads do not divide over {world} ranks")
+    per = n_kv_heads // world
+    return [(r * per, (r + 1) * per) for r in range(world)]
+
+
+# --------------------------------------------------------------------------
+# the one exchange step of split-KV
+# --------------------------------------------------------------------------
+
+def allgather_partials(o: torch.Tensor, lse: torch.Tensor, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """o [rows, D] f32 and lse [rows] f32 of this rank -> (o [rows, world, D], lse [rows, world]).
+
+    One all-gather of the packed ``[rows, D + 1]`` buffer; works on any backend
+    (NCCL on GPUs, gloo on the CPU for tests)."""
+    if o.dtype != torch.float32 or lse.dtype != torch.float32:
+        raise ValueError("partials are float32")
+    world = dist.get_world_size(group)
+    rows, d = o.shape
+    packed = torch.cat([o, lse.unsqueeze(1)], dim=1).contiguous()
+    gathered = torch.empty((world * rows, d + 1), dtype=torch.float32, device=o.device)  # rank-major concatenation
+    dist.all_gather_into_tensor(gathered, packed, group=group)
+    gathered = gathered.view(world, rows, d + 1).permute(1, 0, 2)
+    return gathered[..., :d].contiguous(), gathered[..., d].contiguous()
+
+
+@dataclass
+class SplitKVStep:
+    """One rank's half of a split-KV decode-attention layer-step.
+
+    ``select`` returns the global selection (identical on every rank),
+    ``attend(block_range, with_suffix)`` this rank's normalised partial
+    ``(o [rows, D], lse [rows])`` over its share, ``merge(o [rows, W, D],
+    lse [rows, W])`` the final output.  On GPUs these are the CUDA operators
+    (see ``cuda_split_kv_step``); the CPU tests plug in the oracle."""
+
+    select: Callable[[], object]
+    attend: Callable[[object, Tuple[int, int], bool], Tuple[torch.Tensor, torch.Tensor]]
+    merge: Callable[[torch.Tensor, torch.Tensor], torch.Tensor]
+
+    def run(self, n_blocks: int, group=None) -> torch.Tensor:
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        lo, hi = plan_block_ranges(n_blocks, world)[rank]
+        selection = self.select()
+        o, lse = self.attend(selection, (lo, hi), rank == world - 1)
+        all_o, all_lse = allgather_partials(o, lse, group)
+        return self.merge(all_o, all_lse)
+
+
+def cuda_split_kv_step(q, kv, summ, *, top_k=None, eps=None, rep_mode="sparse_only", n_splits=2,
+                       out_dtype=None) -> SplitKVStep:
+    """The CUDA operators wired into a ``SplitKVStep``.
+
+    ``kv`` is this rank's paged cache: its block table needs valid entries only
+    for the pages of its own block range (and, on the last rank, the suffix);
+    ``summ`` holds the summaries of all blocks (replicated)."""
+    from . import ops
+    nb = summ.max_blocks
+    rows, d = q.shape[0] * q.shape[1], q.shape[2]
+    out_dtype = out_dtype or q.dtype
+
+    def select():
+        idx, cnt, aux = ops.select_blocks(q, summ, kv.prefix_lens, top_k=top_k, eps=eps,
+                                          want=("z",) if rep_mode == "hybrid" else ())
+        return idx, cnt, aux.get("z")
+
+    def attend(selection, block_range, with_suffix):
+        idx, cnt, z = selection
+        o, lse = ops.sparse_decode(q, kv, idx, cnt, block_size=summ.block_size, max_blocks=nb, rep_mode=rep_mode,
+                                   summ=summ, z=z, n_splits=n_splits, block_range=block_range,
+                                   with_suffix=with_suffix)
+        part, part_lse = ops.finalize(o, lse, torch.float32, return_lse=True)
+        return part.reshape(rows, d), part_lse.reshape(rows)
+
+    def merge(all_o, all_lse):
+        return ops.finalize(all_o, all_lse, out_dtype).reshape(q.shape)
+
+    return SplitKVStep(select, attend, merge)

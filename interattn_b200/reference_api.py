@@ -426,6 +426,58 @@ class ConditionBlockDecodeRunner:
         return out.to(query.dtype), None
 
 
+def generate_condition_block_cached(*, model, tokenizer, input_ids, attention_mask, method, device=None,
+                                    dataset=None, term1_mass_exp=False):
+    """Greedy generation with block-sparse decode attention; the interface of the
+    reference's ``generate_condition_block_cached`` (``core.py:60-187``).
+
+    The prompt is prefilled with dense causal attention, every later token runs
+    through ``ConditionBlockDecodeRunner``.  ``method`` supplies
+    ``max_new_tokens``, ``full_attention_layers``, ``condition_block_size``,
+    ``condition_eps`` (and optionally ``condition_top_k`` / ``condition_rep_mode``).
+    Returns ``(output_ids [1, n], metadata)``; generation stops early at the
+    tokenizer's EOS id.  Batch size 1, as in the reference."""
+    if getattr(method, "condition_delta_mode", "range_bound") != "range_bound":
+        raise ValueError("condition_block only supports delta_mode='range_bound'.")
+    if int(input_ids.shape[0]) != 1:
+        raise ValueError("condition_block generate currently expects batch_size=1.")
+    if term1_mass_exp:
+        raise ValueError("the term1-softmax score variant is not built")
+    prompt_len = int(input_ids.shape[1])
+    budget = int(method.max_new_tokens)
+    meta = {"method": "condition_block_b200", "prompt_len": prompt_len, "decode_steps": 0}
+    if budget <= 0:
+        return torch.empty((1, 0), device=input_ids.device, dtype=input_ids.dtype), meta
+    stop = set()
+    eos = getattr(tokenizer, "eos_token_id", None) if tokenizer is not None else None
+    if eos is not None:
+        stop.update(eos if isinstance(eos, (list, tuple)) else [eos])
+    with torch.no_grad():
+        out = model(input_ids=input_ids, attention_mask=attention_mask, use_cache=True)
+    cache = out.past_key_values
+    token = torch.argmax(out.logits[:, -1, :].float(), dim=-1, keepdim=True)
+    tokens = [token]
+    mask = attention_mask
+    runner = ConditionBlockDecodeRunner(
+        model=model, model_config=model.config, full_attention_layers=method.full_attention_layers,
+        block_size=method.condition_block_size, eps=method.condition_eps, prompt_len=prompt_len,
+        top_k=getattr(method, "condition_top_k", None), rep_mode=getattr(method, "condition_rep_mode", "hybrid"))
+    total = prompt_len + 1
+    with condition_block_decode_context(runner):
+        while len(tokens) < budget and int(token) not in stop:
+            runner.reset_step(total - 1)
+            if mask is not None:
+                mask = torch.cat([mask, torch.ones_like(token)], dim=1)
+            with torch.no_grad():
+                out = model(input_ids=token, attention_mask=mask, past_key_values=cache, use_cache=True)
+            cache = out.past_key_values
+            token = torch.argmax(out.logits[:, -1, :].float(), dim=-1, keepdim=True)
+            tokens.append(token)
+            total += 1
+            meta["decode_steps"] += 1
+    return torch.cat(tokens, dim=1), meta
+
+
 @contextlib.contextmanager
 def condition_block_decode_context(runner: ConditionBlockDecodeRunner):
     """Install the runner as ``modeling_llama.eager_attention_forward`` for the

@@ -1,0 +1,77 @@
+"""Split-KV across real GPUs (one process per GPU, NCCL): every rank holds only
+the K/V pages of its own block range, selects globally from replicated
+summaries, attends over its share and all-gathers (o, lse); the merged output
+must equal the single-GPU layer-step.  Skipped on boxes with one GPU."""
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, rep_mode, result_path):
+    import torch.distributed as dist
+    from interattn_b200 import ops, partition
+    from oracle.configs import CONFIGS, make_case, scaled
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        cfg = scaled(CONFIGS["cfg4_longctx_128k"], batch=2, max_len=6000, suffix=11, top_k=12)
+        case = make_case(cfg)
+        nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
+        q = case["q"].to(dev)
+        table = case["block_table"].clamp_min(0).to(dev).contiguous()
+        full = ops.PagedKV(case["k_pool"].to(dev), case["v_pool"].to(dev), table,
+                           case["prefix_lens"].to(dev), case["seq_lens"].to(dev))
+        summ = ops.build_summaries(full, cfg.block_size, max_blocks=nb)        # replicated summaries
+        whole = ops.DecodeAttention(full, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode,
+                                    n_splits=2).step(q).clone()
+
+        # this rank's pool: NaN everywhere except the pages of its own block range (+ suffix on the last rank)
+        lo, hi = partition.plan_block_ranges(nb, world)[rank]
+        ppb = cfg.block_size // cfg.page_size
+        keep = torch.zeros(case["k_pool"].shape[0], dtype=torch.bool)
+        for b in range(cfg.batch):
+            n_prefix_pages = (cfg.prefix_lens[b] + cfg.page_size - 1) // cfg.page_size
+            mine = [p for p in range(lo * ppb, min(hi * ppb, n_prefix_pages))]
+            if rank == world - 1:
+                first_suffix = cfg.prefix_lens[b] // cfg.page_size
+                last = (cfg.prefix_lens[b] + cfg.suffix_lens[b] - 1) // cfg.page_size
+                mine += list(range(first_suffix, last + 1))
+            keep[case["block_table"][b, mine].long()] = True
+        k_mine = torch.where(keep[:, None, None, None], case["k_pool"].float(), torch.tensor(float("nan"))).to(q.dtype)
+        v_mine = torch.where(keep[:, None, None, None], case["v_pool"].float(), torch.tensor(float("nan"))).to(q.dtype)
+        local = ops.PagedKV(k_mine.to(dev), v_mine.to(dev), table, full.prefix_lens, full.seq_lens)
+
+        step = partition.cuda_split_kv_step(q, local, summ, top_k=cfg.top_k, rep_mode=rep_mode, n_splits=2)
+        out = step.run(nb)
+        torch.cuda.synchronize()
+        ok = bool(torch.isfinite(out.float()).all())
+        ok = ok and torch.allclose(out.float(), whole.float(), rtol=1e-2, atol=3e-3)
+        with open(f"{result_path}.{rank}", "w") as f:
+            f.write("ok" if ok else f"mismatch {float((out.float() - whole.float()).abs().max())}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("rep_mode", ["sparse_only", "hybrid"])
+def test_split_kv_over_nccl(tmp_path, rep_mode):
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    result = str(tmp_path / "result")
+    mp.spawn(_rank_main, args=(world, _free_port(), rep_mode, result), nprocs=world, join=True)
+    for r in range(world):
+        assert open(f"{result}.{r}").read() == "ok"

@@ -243,3 +243,66 @@ def test_attention_hook_in_a_small_llama():
     with api.condition_block_decode_context(r):
         assert modeling_llama.eager_attention_forward == r.hybrid_attention_forward
     assert modeling_llama.eager_attention_forward is before
+
+
+def test_generate_condition_block_cached_matches_oracle_greedy_tokens():
+    """The generation entry point (greedy) against a hand-rolled loop whose decode
+    attention is the CPU oracle, on a small random fp32 Llama."""
+    pytest.importorskip("transformers")
+    from types import SimpleNamespace
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from transformers.models.llama import modeling_llama
+    api = _api()
+    torch.manual_seed(3)
+    cfg = LlamaConfig(vocab_size=96, hidden_size=256, intermediate_size=128, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64, max_position_embeddings=512,
+                      attn_implementation="eager")
+    model = LlamaForCausalLM(cfg).float().eval()
+    prompt_len, new_tokens, block, top_k = 150, 5, 64, 2
+    ids = torch.randint(0, 96, (1, prompt_len), generator=torch.Generator().manual_seed(4))
+    method = SimpleNamespace(condition_delta_mode="range_bound", max_new_tokens=new_tokens, full_attention_layers=1,
+                             condition_block_size=block, condition_eps=0.0, condition_top_k=top_k,
+                             condition_rep_mode="hybrid")
+
+    # reference loop on the CPU: layer 0 dense, layer 1 = oracle block-sparse attention
+    state = {"pos": prompt_len, "summ": None}
+
+    def hook(module, query, key, value, attention_mask, scaling, dropout=0.0, **kw):
+        if query.shape[2] != 1:
+            return api._sdpa_prefill(query, key, value, scaling)
+        if module.layer_idx < 1:
+            return api._sdpa_full(query, key[:, :, : state["pos"] + 1], value[:, :, : state["pos"] + 1], scaling)
+        hkv, hq, d = key.shape[1], query.shape[1], query.shape[3]
+        k_all, v_all = key[0, :, : state["pos"] + 1], value[0, :, : state["pos"] + 1]
+        if state["summ"] is None:
+            state["summ"] = orc.block_summaries(k_all[:, :prompt_len], v_all[:, :prompt_len], block)
+        out, *_ = _oracle_step(query[0].reshape(hkv, hq // hkv, 1, d), k_all, v_all, prompt_len, block, top_k=top_k,
+                               summ=state["summ"])
+        return out.reshape(hq, 1, d).permute(1, 0, 2).unsqueeze(0).to(query.dtype), None
+
+    want = []
+    with torch.no_grad():
+        out = model(ids, use_cache=True)
+        cache, tok = out.past_key_values, out.logits[:, -1].argmax(-1, keepdim=True)
+        want.append(tok)
+        original = modeling_llama.eager_attention_forward
+        modeling_llama.eager_attention_forward = hook
+        try:
+            for s in range(new_tokens - 1):
+                state["pos"] = prompt_len + s
+                out = model(tok, past_key_values=cache, use_cache=True)
+                tok = out.logits[:, -1].argmax(-1, keepdim=True)
+                want.append(tok)
+        finally:
+            modeling_llama.eager_attention_forward = original
+    want = torch.cat(want, dim=1)
+
+    gpu_model = model.to(DEV)
+    got, meta = api.generate_condition_block_cached(
+        model=gpu_model, tokenizer=None, input_ids=ids.to(DEV), attention_mask=torch.ones_like(ids).to(DEV),
+        method=method, device=DEV)
+    assert got.shape == (1, new_tokens) and meta["decode_steps"] == new_tokens - 1
+    assert torch.equal(got.cpu(), want)
+    with pytest.raises(ValueError):
+        api.generate_condition_block_cached(model=gpu_model, tokenizer=None, input_ids=ids.repeat(2, 1).to(DEV),
+                                            attention_mask=None, method=method, device=DEV)
