@@ -162,10 +162,12 @@ int64_t ia_workspace_bytes(const ia_geom* geom, int max_sel, int n_splits, int r
  * grid fills whole waves of resident CTAs.  Host arithmetic only. */
 int ia_suggest_splits(const ia_geom* geom, int expected_blocks);
 
-/* One decode-attention layer-step: ia_select, ia_sparse_decode and
- * ia_finalize on one stream, replacing _condition_block_decode_output_fused_triton
- * (IMPL/core.py:1035-1155).  workspace: ia_workspace_bytes() bytes, 256-byte
- * aligned.  out [batch, rows, head_dim] in geom->dtype.  sel_idx/sel_count
+/* One decode-attention layer-step, replacing
+ * _condition_block_decode_output_fused_triton (IMPL/core.py:1035-1155): the
+ * selection kernel, then the attention kernel with the split-KV finalize fused
+ * in (the CTA that completes a (sequence, kv head) last merges its parts and
+ * writes out) - two launches on one stream instead of the reference's three.
+ * workspace: ia_workspace_bytes() bytes, 256-byte aligned.  out [batch, rows, head_dim] in geom->dtype.  sel_idx/sel_count
  * may be null (the selection then lives in the workspace). */
 int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool,
                         const int32_t* block_table, const int32_t* prefix_lens,
@@ -176,9 +178,9 @@ int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool,
 
 /* ia_decode_attention that also records four caller-created CUDA events
  * (cudaEvent_t, timing enabled) on the stream: events[0] before the selection
- * kernel, [1] between selection and attention, [2] between attention and
- * finalize, [3] after finalize - per-kernel device times of a live step
- * without a profiler.  A null entry is skipped. */
+ * kernel, [1] between selection and attention, [2] and [3] after the
+ * attention kernel (the finalize is fused into it) - per-kernel device times
+ * of a live step without a profiler.  A null entry is skipped. */
 int ia_decode_attention_timed(const void* q, const void* k_pool, const void* v_pool,
                               const int32_t* block_table, const int32_t* prefix_lens,
                               const int32_t* seq_lens, const ia_summaries* summaries,

@@ -74,6 +74,7 @@ struct Workspace {
   float* z;
   float* o_partial;
   float* lse_partial;
+  int* split_counters;
   int64_t bytes;
 };
 
@@ -95,6 +96,7 @@ static Workspace carve(const ia_geom& g, int max_sel, int n_splits, int rep_mode
   w.z = reinterpret_cast<float*>(take(rep_mode == IA_REP_HYBRID ? rows * g.max_blocks * 4 : 0));
   w.o_partial = reinterpret_cast<float*>(take(rows * n_splits * g.head_dim * 4));
   w.lse_partial = reinterpret_cast<float*>(take(rows * n_splits * 4));
+  w.split_counters = reinterpret_cast<int*>(take(pairs * 4));
   w.bytes = off;
   return w;
 }
@@ -142,7 +144,7 @@ int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefi
                 geom->max_blocks);
   ia_select_aux none{};
   return launch_select(q, *summaries, prefix_lens, *geom, mode, top_k, eps, max_sel, sel_idx, sel_count,
-                       aux ? *aux : none, (cudaStream_t)stream);
+                       aux ? *aux : none, nullptr, (cudaStream_t)stream);
 }
 
 int ia_sparse_decode(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
@@ -168,7 +170,7 @@ int ia_sparse_decode(const void* q, const void* k_pool, const void* v_pool, cons
   if (block_lo < 0 || block_hi < block_lo) return fail(IA_ERR_BAD_ARG, "sparse_decode: block range [%d, %d)", block_lo, block_hi);
   return launch_sparse_decode(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, sel_idx, sel_count, max_sel,
                               summaries, z, *geom, rep_mode, n_splits, block_lo, block_hi, with_suffix, o_partial,
-                              lse_partial, (cudaStream_t)stream);
+                              lse_partial, nullptr, (cudaStream_t)stream);
 }
 
 int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts, int head_dim,
@@ -243,18 +245,35 @@ static int decode_attention_impl(const void* q, const void* k_pool, const void* 
   int32_t* cnt = sel_count ? sel_count : w.sel_count;
   ia_select_aux aux{};
   if (rep_mode == IA_REP_HYBRID) aux.z = w.z;
+  // Argument checks of the public entry points, then two launches: the selection
+  // kernel (which also clears the per-pair split counters) and the attention kernel
+  // with the fused finalize - the CTA that finishes a (sequence, kv head) last merges
+  // its splits and writes `out`, so no third kernel is needed.
+  if (int s = check_summaries(summaries)) return s;
+  if (!q || !k_pool || !v_pool || !block_table || !prefix_lens || !seq_lens)
+    return fail(IA_ERR_BAD_ARG, "decode_attention: null argument");
+  if (!aligned16(k_pool) || !aligned16(v_pool) || !aligned16(q))
+    return fail(IA_ERR_BAD_ARG, "decode_attention: q and pools must be 16-byte aligned");
+  if (mode != IA_SELECT_TOPK && mode != IA_SELECT_EPS) return fail(IA_ERR_BAD_ARG, "decode_attention: mode %d", mode);
+  if (mode == IA_SELECT_TOPK && (top_k < 0 || top_k > max_sel))
+    return fail(IA_ERR_BAD_ARG, "decode_attention: top_k %d outside [0, max_sel %d]", top_k, max_sel);
+  if (mode == IA_SELECT_EPS && max_sel < geom->max_blocks)
+    return fail(IA_ERR_BAD_ARG, "decode_attention: epsilon mode may keep every block: max_sel %d < max_blocks %d",
+                max_sel, geom->max_blocks);
+  if (rep_mode != IA_REP_SPARSE_ONLY && rep_mode != IA_REP_HYBRID)
+    return fail(IA_ERR_BAD_ARG, "decode_attention: rep_mode %d", rep_mode);
+  if (n_splits > 64) return fail(IA_ERR_BAD_ARG, "decode_attention: n_splits %d outside [1, 64]", n_splits);
   mark(0);
-  if (int s = ia_select(q, summaries, prefix_lens, geom, mode, top_k, eps, max_sel, idx, cnt, &aux, stream)) return s;
-  mark(1);
-  if (int s = ia_sparse_decode(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, idx, cnt, max_sel, summaries,
-                               w.z, geom, rep_mode, n_splits, 0, geom->max_blocks, 1, w.o_partial, w.lse_partial,
-                               stream))
+  if (int s = launch_select(q, *summaries, prefix_lens, *geom, mode, top_k, eps, max_sel, idx, cnt, aux,
+                            w.split_counters, st))
     return s;
+  mark(1);
+  FusedFinalize fused{out, geom->dtype, w.split_counters};
+  const int s = launch_sparse_decode(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, idx, cnt, max_sel,
+                                     summaries, w.z, *geom, rep_mode, n_splits, 0, geom->max_blocks, 1, w.o_partial,
+                                     w.lse_partial, &fused, st);
   mark(2);
-  const int n_rows = geom->batch * geom->n_kv_heads * geom->group_size;
-  const int s = ia_finalize(w.o_partial, w.lse_partial, n_rows, n_splits, geom->head_dim, out, geom->dtype, nullptr,
-                            stream);
-  mark(3);
+  mark(3);  // the finalize is part of the attention kernel: events 2 and 3 coincide
   return s;
 }
 

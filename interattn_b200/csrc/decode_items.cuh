@@ -27,6 +27,11 @@ struct DecodeParams {
   const float* z;     // hybrid only: [batch, rows, max_blocks]
   float* o_partial;
   float* lse_partial;
+  // optional fused finalize: the CTA that completes a (sequence, kv head) last merges
+  // its n_splits partials and writes the output rows [batch, rows, D] itself
+  void* final_out;      // null: partials only
+  int* split_counters;  // [batch * kv heads], zero at launch; reset by the merging CTA
+  int final_dtype;      // ia_dtype of final_out
   int64_t page_stride, head_stride;
   int n_kv_heads, group_size, page_size, block_size, max_pages, max_blocks, max_sel;
   int rep_mode, n_splits, block_lo, block_hi, with_suffix;
@@ -119,6 +124,51 @@ __device__ __forceinline__ void resolve_items(const DecodeParams& p, const ItemR
     items_s[i - chunk_begin] = it;
   }
   __syncthreads();
+}
+
+// Fused split-KV finalize (same arithmetic as condition_block_stage2_reduce_kernel).
+// Called by every thread of a CTA right after it wrote its partial.  `flag` is one
+// int of shared memory.
+template <int D>
+__device__ __forceinline__ void finish_pair(const DecodeParams& p, int seq, int head, int G, int* flag) {
+  if (p.final_out == nullptr) return;
+  const int pair = seq * p.n_kv_heads + head;
+  const int rows = p.n_kv_heads * G;
+  if (p.n_splits > 1) {
+    __threadfence();  // publish this CTA's partial before it is counted
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int old = atomicAdd(&p.split_counters[pair], 1);
+      const int is_last = old == p.n_splits - 1;
+      if (is_last) p.split_counters[pair] = 0;  // ready for the next launch
+      *flag = is_last;
+    }
+    __syncthreads();
+    if (*flag == 0) return;
+    __threadfence();
+  } else {
+    __syncthreads();
+  }
+  for (int e = threadIdx.x; e < G * D; e += blockDim.x) {
+    const int g = e / D, d = e - g * D;
+    const int64_t row = (int64_t)seq * rows + head * G + g;
+    const float* lse = p.lse_partial + row * p.n_splits;
+    const float* o = p.o_partial + row * p.n_splits * D + d;
+    float top = -INFINITY;
+    for (int s = 0; s < p.n_splits; ++s) top = fmaxf(top, __ldcg(lse + s));
+    const float ref = top == -INFINITY ? 0.f : top;
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < p.n_splits; ++s) {
+      const float w = expf(__ldcg(lse + s) - ref);  // exp(-inf) = 0 for an empty part
+      num = fmaf(w, __ldcg(o + (int64_t)s * D), num);
+      den += w;
+    }
+    const float v = num * (1.f / fmaxf(den, 1e-30f));  // same rounding as the stand-alone finalize kernel
+    if (p.final_dtype == IA_BF16)
+      static_cast<__nv_bfloat16*>(p.final_out)[row * D + d] = __float2bfloat16_rn(v);
+    else
+      static_cast<float*>(p.final_out)[row * D + d] = v;
+  }
 }
 
 }  // namespace ia

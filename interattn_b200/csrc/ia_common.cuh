@@ -108,15 +108,23 @@ constexpr float kLn2 = 0.6931471805599453f;
 int launch_build_summaries(const void* k_pool, const void* v_pool, const int32_t* block_table,
                            const int32_t* prefix_lens, const ia_geom& g, const ia_summaries& out,
                            cudaStream_t stream);
+// split_counters (may be null): one int per (sequence, kv head), cleared by the selection
+// kernel for the attention kernel's fused finalize
 int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_lens, const ia_geom& g,
                   int mode, int top_k, float eps, int max_sel, int32_t* sel_idx, int32_t* sel_count,
-                  const ia_select_aux& aux, cudaStream_t stream);
+                  const ia_select_aux& aux, int* split_counters, cudaStream_t stream);
+// Fused finalize of the attention kernel: the last CTA of a (sequence, kv head) merges the splits.
+struct FusedFinalize {
+  void* out;            // [batch, rows, D]
+  int out_dtype;        // ia_dtype
+  int* split_counters;  // [batch * kv heads], zero at launch
+};
 int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* block_table, const int32_t* prefix_lens,
                          const int32_t* seq_lens, const int32_t* sel_idx, const int32_t* sel_count,
                          int max_sel, const ia_summaries* summaries, const float* z, const ia_geom& g,
                          int rep_mode, int n_splits, int block_lo, int block_hi, int with_suffix,
-                         float* o_partial, float* lse_partial, cudaStream_t stream);
+                         float* o_partial, float* lse_partial, const FusedFinalize* fused, cudaStream_t stream);
 int launch_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts,
                     int head_dim, void* out, int out_dtype, float* out_lse, cudaStream_t stream);
 

@@ -70,6 +70,7 @@ struct SelectParams {
   float eps;
   int32_t* sel_idx;
   int32_t* sel_count;
+  int* split_counters;  // may be null
   ia_select_aux aux;
   int n_stages, nb_cap;
 };
@@ -763,7 +764,10 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   }
   const int count = max(min(n_written, p.max_sel), 0);
   for (int i = count + tid; i < p.max_sel; i += kThreads) out_idx[i] = -1;
-  if (tid == 0) p.sel_count[pair] = count;
+  if (tid == 0) {
+    p.sel_count[pair] = count;
+    if (p.split_counters != nullptr) p.split_counters[pair] = 0;
+  }
 }
 
 // cuTensorMapEncodeTiled lives in the driver library; fetch it through the
@@ -847,13 +851,13 @@ static int launch_group(const SelectParams& p, int n_pairs, int group, cudaStrea
 
 int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_lens, const ia_geom& g,
                   int mode, int top_k, float eps, int max_sel, int32_t* sel_idx, int32_t* sel_count,
-                  const ia_select_aux& aux, cudaStream_t stream) {
+                  const ia_select_aux& aux, int* split_counters, cudaStream_t stream) {
   SelectParams p{};
   p.q = q; p.k_bar = s.k_bar; p.k_max = s.k_max; p.k_min = s.k_min; p.v_norm_max = s.v_norm_max;
   p.prefix_lens = prefix_lens;
   p.n_kv_heads = g.n_kv_heads; p.max_blocks = g.max_blocks; p.block_size = g.block_size;
   p.mode = mode; p.top_k = top_k; p.max_sel = max_sel; p.eps = eps;
-  p.sel_idx = sel_idx; p.sel_count = sel_count; p.aux = aux;
+  p.sel_idx = sel_idx; p.sel_count = sel_count; p.aux = aux; p.split_counters = split_counters;
   const int n_pairs = g.batch * g.n_kv_heads;
   if (n_pairs <= 0) return IA_OK;
   if (g.dtype == IA_BF16) {

@@ -139,6 +139,7 @@ condition_block_finalize_attention_fma_kernel(DecodeParams p) {
     p.o_partial[orow * D + d] = den > 0.f ? num / den : 0.f;
     if (d == 0) p.lse_partial[orow] = den > 0.f ? top + logf(den) : -INFINITY;
   }
+  finish_pair<D>(p, seq, head, G, scratch);
 }
 
 template <typename T, int D, int G>
@@ -168,8 +169,13 @@ int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* seq_lens, const int32_t* sel_idx, const int32_t* sel_count,
                          int max_sel, const ia_summaries* summaries, const float* z, const ia_geom& g,
                          int rep_mode, int n_splits, int block_lo, int block_hi, int with_suffix,
-                         float* o_partial, float* lse_partial, cudaStream_t stream) {
+                         float* o_partial, float* lse_partial, const FusedFinalize* fused, cudaStream_t stream) {
   DecodeParams p{};
+  if (fused != nullptr) {
+    p.final_out = fused->out;
+    p.split_counters = fused->split_counters;
+    p.final_dtype = fused->out_dtype;
+  }
   p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.block_table = block_table;
   p.prefix_lens = prefix_lens; p.seq_lens = seq_lens; p.sel_idx = sel_idx; p.sel_count = sel_count;
   p.v_bar = summaries ? summaries->v_bar : nullptr;

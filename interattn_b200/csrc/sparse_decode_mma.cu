@@ -315,6 +315,7 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
     p.o_partial[orow * D + d] = den > 0.f ? num / den : 0.f;
     if (d == 0) p.lse_partial[orow] = den > 0.f ? (top + log2f(den)) * kLn2 : -INFINITY;
   }
+  finish_pair<D>(p, seq, head, G, scratch);
 }
 
 template <int D, int NS>
