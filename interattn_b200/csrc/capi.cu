@@ -33,6 +33,14 @@ int check_launch(const char* what) {
   return fail(IA_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
 }
 
+bool overlapped_launch_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("INTERATTN_B200_NO_PDL");
+    return !(v != nullptr && v[0] == '1');
+  }();
+  return on;
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_geom(const ia_geom* g) {

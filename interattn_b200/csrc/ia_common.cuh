@@ -101,6 +101,36 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------
+// The layer-step is a chain of short kernels on one stream; between two of them the
+// GPU would idle for a launch latency and a drain.  A kernel launched through
+// launch_overlapped() may be scheduled while its predecessor is still running: its
+// CTAs take whatever SM resources become free and park in grid_dependency_wait(),
+// which returns once the predecessor grid has completed and its writes are visible.
+// Rule for kernels launched this way: call grid_dependency_wait() before the first
+// access to memory the predecessor writes - or still reads, if this kernel overwrites it.
+// INTERATTN_B200_NO_PDL=1 falls back to ordinary stream order.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+bool overlapped_launch_enabled();
+template <typename Kern, typename Params>
+inline cudaError_t launch_overlapped(Kern kern, unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
+                                     const Params& params) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlapped_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, params);
+}
+
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 

@@ -274,6 +274,11 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   unsigned char* stage_base = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(t_s + (size_t)G * nb_cap) + 1023) & ~uintptr_t(1023));
 
+  // The previous kernel on the stream (the attention kernel of the step before) may still
+  // be reading the selection this kernel is about to overwrite: wait for it, then let the
+  // attention kernel of this step start occupying free SMs.
+  grid_dependency_wait();
+  grid_launch_dependents();
   if (tid == 0) {
     for (int s = 0; s < p.n_stages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -831,7 +836,8 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   auto kern = condition_block_select_kernel<T, D, G>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "select: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  kern<<<n_pairs, kThreads, smem, stream>>>(p);
+  e = launch_overlapped(kern, (unsigned)n_pairs, (unsigned)kThreads, smem, stream, p);
+  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "condition_block_select_kernel: %s", cudaGetErrorString(e));
   return check_launch("condition_block_select_kernel");
 }
 

@@ -92,6 +92,10 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
   const int G = p.group_size;
   const int rows = p.n_kv_heads * G;
 
+  // Let the next kernel on the stream start filling SMs as this grid drains, then wait
+  // for the selection kernel: everything below reads what it wrote.
+  grid_launch_dependents();
+  grid_dependency_wait();
   const ItemRange r = item_range(p, seq, head, split, scratch);
   if (p.rep_mode == IA_REP_HYBRID) {
     const int words = (p.max_blocks + 31) / 32;
@@ -328,12 +332,14 @@ int launch_typed(const DecodeParams& p, const ia_geom& g, cudaStream_t stream) {
     auto kern = condition_block_finalize_attention_kernel<D, NS, true>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "sparse_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kern<<<(unsigned)grid, kWarps * 32, smem, stream>>>(p);
+    e = launch_overlapped(kern, (unsigned)grid, (unsigned)(kWarps * 32), smem, stream, p);
+    if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "condition_block_finalize_attention_kernel: %s", cudaGetErrorString(e));
   } else {
     auto kern = condition_block_finalize_attention_kernel<D, NS, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "sparse_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kern<<<(unsigned)grid, kWarps * 32, smem, stream>>>(p);
+    e = launch_overlapped(kern, (unsigned)grid, (unsigned)(kWarps * 32), smem, stream, p);
+    if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "condition_block_finalize_attention_kernel: %s", cudaGetErrorString(e));
   }
   return check_launch("condition_block_finalize_attention_kernel");
 }

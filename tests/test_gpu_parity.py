@@ -182,6 +182,40 @@ def test_one_call_layer_step_matches_the_three_calls(bundle):
         assert torch.equal(out_host, want.cpu())
 
 
+def test_layer_step_replays_from_a_cuda_graph():
+    """The step allocates nothing and reads its per-step quantities from device
+    memory, so it can be captured once and replayed (the reference's graphed
+    decode loop, condition_block_triton_impl/core.py:190-316): new q and a longer
+    suffix are picked up by the replay."""
+    ops = _ops()
+    cfg = scaled(CONFIGS["cfg2_llama8b_32k"], batch=2, max_len=2304, suffix=40)
+    case = make_case(cfg)
+    q, kv = to_device(case)
+    nb = max_blocks_of(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb)
+    full_seq = kv.seq_lens.clone()
+    kv.seq_lens.copy_(kv.prefix_lens + 3)                 # start with 3 suffix tokens
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode="hybrid", n_splits=3)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step.step(q)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step.step(q)
+    for extra in (3, 17, 40):
+        kv.seq_lens.copy_(kv.prefix_lens + extra)
+        q.copy_(torch.roll(q, extra, dims=2))
+        graph.replay()
+        got = step.out.clone()
+        want = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode="hybrid", n_splits=3).step(q)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    assert torch.equal(kv.seq_lens, full_seq)
+
+
 def test_block_range_shares_merge_to_the_whole(bundle):
     """Split-KV across ranks, emulated on one GPU: each 'rank' attends over its
     own block range (the last one also over the suffix); merging the (o, lse)
