@@ -344,7 +344,7 @@ def run_gpu_arm(args):
                     "us_per_layer": 1e3 * e2e_ms / K,
                     "note": "KV pool and block summaries are cache state resident on the device; the step's "
                             "inputs (q) and outputs cross PCIe every step"},
-            "gpu_launches": 3 * K,
+            "gpu_launches": 2 * K,   # selection + attention (finalize fused) per step, headline region
             "clocks": clocks,
             "device_status": status,
         }

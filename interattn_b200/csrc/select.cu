@@ -9,23 +9,25 @@
 // The reference spreads this over two launches and parks s / delta / four
 // online-softmax partials in HBM in between.  Here one CTA owns one
 // (sequence, kv head): it streams the three summary vectors of every block
-// once through a TMA (cp.async.bulk) + mbarrier shared-memory ring, keeps
-// z = s + log(count) and the range bound delta of all G x n_blocks
-// (row, block) pairs in shared memory, forms the two global normalisers, the
-// GQA-mean score and then routes - a radix select for the k best blocks
-// (higher score first, lower block index first among equal scores) or the
-// reference's score > eps rule - without the score vector leaving the SM.
+// once through a TMA (cp.async.bulk.tensor) + mbarrier shared-memory ring,
+// keeps z = s + log(count), cosh(delta) - 1 and tanh(delta / 2) of all
+// G x n_blocks (row, block) pairs in shared memory, forms the global
+// normalisers on the fly, the GQA-mean score and then routes - a radix select
+// for the k best blocks (higher score first, lower block index first among
+// equal scores) or the reference's score > eps rule - without the score
+// vector leaving the SM.
 //
 // Roofline: HBM.  Algorithmic bytes per block and kv head:
 //   D*4 (k_bar f32) + 2*D*sizeof(T) (k_max, k_min) + 4 (v_norm_max).
 //
-// Layout of one ring stage (32 blocks, lane <-> block): rows are padded by 16
-// bytes so that the 32 lanes, each walking its own row with 16-byte loads, hit
-// distinct banks; the query rows are read as warp-uniform broadcasts.  A stage
-// is consumed by a group of four warps, each taking a quarter of head_dim;
-// their partial sums meet in shared memory, and each warp of the group then
-// finishes the rows g = warp, warp + 4, ... (s, delta, z) - so sixteen compute
-// warps stay busy on four stages while the producer fills the others.
+// A ring stage is 32 blocks: every summary vector arrives as TMA boxes of
+// 128 bytes x 32 rows written with the 128-byte swizzle, so both access
+// patterns below are bank-conflict free without padding.
+//   * bf16 pools, G <= 8: tensor cores.  Blocks are the M side, query rows the
+//     N side, head_dim is K; two warps take 16 blocks each of a stage.
+//   * otherwise: CUDA cores.  Lane <-> block; a stage is consumed by a group of
+//     four warps, each taking a quarter of head_dim; their partial sums meet in
+//     shared memory and warp w of the group finishes rows g = w, w + 4, ...
 #include <cuda.h>  // CUtensorMap (types only; the encoder is fetched through the runtime)
 
 #include "ia_common.cuh"
@@ -656,7 +658,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
 
   // ---- phase 4: routing ----------------------------------------------------------------
   int32_t* out_idx = p.sel_idx + (int64_t)pair * p.max_sel;
-  uint32_t thr_key = 0;
+  uint32_t thr_key = 0, thr_mask = 0xffffffffu;  // keys are compared on the digits resolved so far
   int take_equal = 0;
   const int k_eff = (p.mode == IA_SELECT_TOPK) ? min(min(p.top_k, nb), p.max_sel) : 0;
   if (k_eff > 0 && k_eff < nb) {
@@ -702,12 +704,12 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       }
       const int above = incl - mine;
       const bool owner = (above < remaining) && (incl >= remaining);
-      int digit = 0, left = 0;
+      int digit = 0, left = 0, in_bin = 0;
       if (owner) {
         int acc = above;
 #pragma unroll
         for (int i = 7; i >= 0; --i) {
-          if (acc + c[i] >= remaining) { digit = lane * 8 + i; break; }
+          if (acc + c[i] >= remaining) { digit = lane * 8 + i; in_bin = c[i]; break; }
           acc += c[i];
         }
         left = remaining - acc;
@@ -715,10 +717,14 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       const int src = max(__ffs(__ballot_sync(0xffffffffu, owner)) - 1, 0);  // exactly one owner lane
       digit = __shfl_sync(0xffffffffu, digit, src);
       remaining = __shfl_sync(0xffffffffu, left, src);
+      in_bin = __shfl_sync(0xffffffffu, in_bin, src);
       fixed |= (uint32_t)digit << shift;
       fixed_mask |= 255u << shift;
+      // every key of the threshold bin is wanted: the remaining digits cannot change the outcome
+      if (in_bin == remaining) break;
     }
     thr_key = fixed;
+    thr_mask = fixed_mask;
     take_equal = remaining;
   }
 
@@ -740,7 +746,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       } else if (everything) {
         gt = in;
       } else {
-        const uint32_t key = order_key(sc);
+        const uint32_t key = order_key(sc) & thr_mask;
         gt = in && key > thr_key;
         eq = in && key == thr_key;
       }
