@@ -117,17 +117,28 @@ __device__ __forceinline__ void grid_launch_dependents() {
 bool overlapped_launch_enabled();
 template <typename Kern, typename Params>
 inline cudaError_t launch_overlapped(Kern kern, unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
-                                     const Params& params) {
+                                     const Params& params, int cluster = 1) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(block);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster > 1) {  // grid is a multiple of the cluster size; CTAs of a cluster are co-scheduled
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (overlapped_launch_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = overlapped_launch_enabled() ? 1 : 0;
+  cfg.numAttrs = (unsigned)n;
   return cudaLaunchKernelEx(&cfg, kern, params);
 }
 

@@ -75,6 +75,8 @@ struct SelectParams {
   int* split_counters;  // may be null
   ia_select_aux aux;
   int n_stages, nb_cap;
+  int cluster;     // CTAs per (sequence, kv head): a thread-block cluster splits the blocks
+  int nb_loc_cap;  // row stride of the per-CTA (row, block) arrays
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -176,6 +178,20 @@ __device__ __forceinline__ void delta_terms(float delta, float& ch, float& a_ter
 // (exact in tf32 and bf16) and at most eight query rows per kv head.
 template <typename T, int G> constexpr bool kUseMma = (sizeof(T) == 2) && (G <= 8);
 
+// ---- thread-block cluster: distributed shared memory and the cluster barrier --------
+__device__ __forceinline__ uint32_t map_to_rank(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// every thread of every CTA of the cluster; orders the remote stores before it against the loads after it
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // barrier among the 128 threads of one warp group (ids 1..kGroups; 0 is __syncthreads)
 __device__ __forceinline__ void group_sync(int group) {
   asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kGroupWarps * 32) : "memory");
@@ -236,8 +252,11 @@ template <int D, int G, bool MMA> struct SmemPlan {
   static constexpr size_t state = 8 * 4;
   static constexpr size_t qrows = 2 * (size_t)G * D * 4;
   static constexpr size_t part = MMA ? 0 : (size_t)kConsumerWarps * 3 * G * 32 * 4;
-  static constexpr size_t fixed = bars + hist + scan + red + norm + state + qrows + part;
-  static size_t per_blocks(int nb_cap) { return (size_t)nb_cap * 4 * (2 + 3 * G); }
+  static constexpr size_t xch = 8 * 16 * 3 * 4;  // [cluster rank][row][m, l, d]
+  static constexpr size_t fixed = bars + hist + scan + red + norm + state + qrows + part + xch;
+  static size_t per_blocks(int nb_cap, int nb_loc_cap) {
+    return (size_t)nb_cap * 4 * 2 + (size_t)nb_loc_cap * 4 * 3 * G;
+  }
 };
 
 template <typename T, int D, int G>
@@ -248,12 +267,19 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   constexpr int DQ = D / kGroupWarps;  // head_dim slice of one warp of a group
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int pair = blockIdx.x;  // (sequence, kv head)
+  const int C = p.cluster;
+  const int pair = blockIdx.x / C;  // (sequence, kv head)
+  const int crank = blockIdx.x - pair * C;  // rank inside the cluster that shares this pair
   const int seq = pair / p.n_kv_heads;
   const int prefix = p.prefix_lens[seq];
   const int nb = min((prefix + p.block_size - 1) / p.block_size, p.max_blocks);
   const int n_tiles = (nb + kTileBlocks - 1) / kTileBlocks;
   const int nb_cap = p.nb_cap;
+  // this CTA scores the tiles [t_lo, t_hi) = blocks [b_lo, b_hi); rank 0 routes for the pair
+  const int t_lo = n_tiles * crank / C, t_hi = n_tiles * (crank + 1) / C;
+  const int n_my_tiles = t_hi - t_lo;
+  const int b_lo = t_lo * kTileBlocks, b_hi = min(t_hi * kTileBlocks, nb);
+  const int nbl = p.nb_loc_cap;
 
   // ---- shared memory carve-up -------------------------------------------------
   unsigned char* sp = smem_raw;
@@ -268,13 +294,14 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   float* q_s = reinterpret_cast<float*>(sp);                            // [G][D]
   float* aq_s = q_s + G * D;                           sp += P::qrows;  // |q|
   float* part_s = reinterpret_cast<float*>(sp);        sp += P::part;   // [consumer warp][3G][32]
+  float* xch_s = reinterpret_cast<float*>(sp);         sp += P::xch;    // [cluster rank][16][3], written by peers
   float* vn_s = reinterpret_cast<float*>(sp);                           // [nb_cap]
   float* score_s = vn_s + nb_cap;                                       // [nb_cap]
-  float* z_s = score_s + nb_cap;                                        // [G][nb_cap]: z = s + log count
-  float* a_s = z_s + (size_t)G * nb_cap;                                // [G][nb_cap]: cosh(delta) - 1
-  float* t_s = a_s + (size_t)G * nb_cap;                                // [G][nb_cap]: tanh(delta / 2)
+  float* z_s = score_s + nb_cap;                                        // [G][nbl]: z = s + log count (own blocks)
+  float* a_s = z_s + (size_t)G * nbl;                                   // [G][nbl]: cosh(delta) - 1
+  float* t_s = a_s + (size_t)G * nbl;                                   // [G][nbl]: tanh(delta / 2)
   unsigned char* stage_base = reinterpret_cast<unsigned char*>(
-      (reinterpret_cast<uintptr_t>(t_s + (size_t)G * nb_cap) + 1023) & ~uintptr_t(1023));
+      (reinterpret_cast<uintptr_t>(t_s + (size_t)G * nbl) + 1023) & ~uintptr_t(1023));
 
   // The previous kernel on the stream (the attention kernel of the step before) may still
   // be reading the selection this kernel is about to overwrite: wait for it, then let the
@@ -316,9 +343,10 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     // producer: one elected lane issues the TMA box copies of each stage
     bool alive = true;
     const int row0 = (int)sum_row0;
-    for (int t = 0; t < n_tiles; ++t) {
-      const int stage = t % p.n_stages;
-      const int use = t / p.n_stages;
+    for (int lt = 0; lt < n_my_tiles; ++lt) {
+      const int t = t_lo + lt;
+      const int stage = lt % p.n_stages;
+      const int use = lt / p.n_stages;
       if (use > 0 && alive) {
         if (!mbar_wait(&empty_bar[stage], (uint32_t)((use - 1) & 1))) {
           alive = false;
@@ -379,9 +407,10 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     // t - n_slots implies every earlier tile, including t - n_stages, was filled).
     const int n_slots = min(kSlots, p.n_stages);
     bool alive = true;
-    for (int t = slot; slot < n_slots && t < n_tiles; t += n_slots) {
-      const int stage = t % p.n_stages;
-      const int use = t / p.n_stages;
+    for (int lt = slot; slot < n_slots && lt < n_my_tiles; lt += n_slots) {
+      const int t = t_lo + lt;
+      const int stage = lt % p.n_stages;
+      const int use = lt / p.n_stages;
       if (alive && !mbar_wait(&full_bar[stage], (uint32_t)(use & 1))) {
         alive = false;
         if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
@@ -434,9 +463,9 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           float ch, a_term, th;
           delta_terms(delta, ch, a_term, th);
           norm_absorb(acc, z, ch);
-          z_s[g * nb_cap + b] = z;
-          a_s[g * nb_cap + b] = a_term;
-          t_s[g * nb_cap + b] = th;
+          z_s[g * nbl + b - b_lo] = z;
+          a_s[g * nbl + b - b_lo] = a_term;
+          t_s[g * nbl + b - b_lo] = th;
           const int64_t o = ((int64_t)pair * G + g) * p.max_blocks + b;
           if (p.aux.s != nullptr) p.aux.s[o] = s;
           if (p.aux.z != nullptr) p.aux.z[o] = z;
@@ -494,9 +523,10 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     for (int r = 0; r < kRowsPerWarp; ++r) rn[r] = RowNorm{-INFINITY, 0.f, 0.f};
     const int n_groups = min(kGroups, p.n_stages);  // see the note on parity waits above
     bool alive = true;
-    for (int t = group; group < n_groups && t < n_tiles; t += n_groups) {
-      const int stage = t % p.n_stages;
-      const int use = t / p.n_stages;
+    for (int lt = group; group < n_groups && lt < n_my_tiles; lt += n_groups) {
+      const int t = t_lo + lt;
+      const int stage = lt % p.n_stages;
+      const int use = lt / p.n_stages;
       if (alive && !mbar_wait(&full_bar[stage], (uint32_t)(use & 1))) {
         alive = false;
         if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
@@ -572,9 +602,9 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           float ch, a_term, th;
           delta_terms(delta, ch, a_term, th);
           norm_absorb(rn[g / kGroupWarps], z, ch);
-          z_s[g * nb_cap + b] = z;
-          a_s[g * nb_cap + b] = a_term;
-          t_s[g * nb_cap + b] = th;
+          z_s[g * nbl + b - b_lo] = z;
+          a_s[g * nbl + b - b_lo] = a_term;
+          t_s[g * nbl + b - b_lo] = th;
           const int64_t o = ((int64_t)pair * G + g) * p.max_blocks + b;
           if (p.aux.s != nullptr) p.aux.s[o] = s;
           if (p.aux.z != nullptr) p.aux.z[o] = z;
@@ -617,6 +647,25 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       const float od = __shfl_xor_sync(0xffffffffu, tot.d, o);
       norm_merge(tot, om, ol, od);
     }
+    // this CTA's share of row g goes to every CTA of the cluster (slot = own rank)
+    if (lane < C) {
+      const uint32_t dst = map_to_rank(xch_s + (crank * 16 + g) * 3, (uint32_t)lane);
+      st_cluster_f32(dst, tot.m);
+      st_cluster_f32(dst + 4, tot.l);
+      st_cluster_f32(dst + 8, tot.d);
+    }
+  }
+  cluster_sync_all();
+  for (int g = warp; g < G; g += kWarps) {
+    RowNorm tot{-INFINITY, 0.f, 0.f};
+    if (lane < C) tot = RowNorm{xch_s[(lane * 16 + g) * 3], xch_s[(lane * 16 + g) * 3 + 1], xch_s[(lane * 16 + g) * 3 + 2]};
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, tot.m, o);
+      const float ol = __shfl_xor_sync(0xffffffffu, tot.l, o);
+      const float od = __shfl_xor_sync(0xffffffffu, tot.d, o);
+      norm_merge(tot, om, ol, od);
+    }
     float b_all = lane < kWarps ? redb_s[lane] : 0.f;
     b_all = warp_max(b_all);
 
@@ -625,7 +674,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       norm_s[g] = tot.m;
       norm_s[16 + g] = 1.f / tot.l;
       norm_s[32 + g] = 2.f * b_all / denom;
-      if (p.aux.globals != nullptr) {
+      if (p.aux.globals != nullptr && crank == 0) {
         // [batch, 4, rows]: (z_m, z_l) and a normaliser pair (c_m, c_l) with
         // c_l e^{c_m} = sum_b e^{z_b} cosh(delta_b); here c_m = z_m.
         const int rows = p.n_kv_heads * G;
@@ -642,19 +691,25 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
 
   // ---- phase 3: GQA-mean condition score -------------------------------------------
   // cond = softmax(z) (2 b_all (cosh d - 1) / denom + 2 b_c tanh(d / 2))   (IMPL/core.py:535-544)
-  for (int b = tid; b < nb; b += kThreads) {
-    const float two_bc = 2.f * vn_s[b];
-    float sum = 0.f;
+  // Each CTA scores its own blocks and delivers the scores to rank 0 of the cluster,
+  // which routes for the whole (sequence, kv head).
+  {
+    const uint32_t score_r0 = map_to_rank(score_s, 0u);
+    for (int b = b_lo + tid; b < b_hi; b += kThreads) {
+      const float two_bc = 2.f * vn_s[b];
+      float sum = 0.f;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float pm = expf(z_s[g * nb_cap + b] - norm_s[g]) * norm_s[16 + g];
-      sum += pm * fmaf(norm_s[32 + g], a_s[g * nb_cap + b], two_bc * t_s[g * nb_cap + b]);
+      for (int g = 0; g < G; ++g) {
+        const float pm = expf(z_s[g * nbl + b - b_lo] - norm_s[g]) * norm_s[16 + g];
+        sum += pm * fmaf(norm_s[32 + g], a_s[g * nbl + b - b_lo], two_bc * t_s[g * nbl + b - b_lo]);
+      }
+      const float sc = sum / (float)G;
+      st_cluster_f32(score_r0 + (uint32_t)b * 4u, sc);
+      if (p.aux.score != nullptr) p.aux.score[(int64_t)pair * p.max_blocks + b] = sc;
     }
-    const float sc = sum / (float)G;
-    score_s[b] = sc;
-    if (p.aux.score != nullptr) p.aux.score[(int64_t)pair * p.max_blocks + b] = sc;
   }
-  __syncthreads();
+  cluster_sync_all();
+  if (crank != 0) return;  // nobody reads this CTA's shared memory any more
 
   // ---- phase 4: routing ----------------------------------------------------------------
   int32_t* out_idx = p.sel_idx + (int64_t)pair * p.max_sel;
@@ -822,11 +877,25 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   using P = SmemPlan<D, G, kUseMma<T, G>>;
   SelectParams p = base;
   p.nb_cap = (p.max_blocks + 31) & ~31;
-  const size_t fixed = P::fixed + P::per_blocks(p.nb_cap) + 1024;
-  int dev = 0, max_smem = 0;
+  int dev = 0, max_smem = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (max_smem <= 0) max_smem = 227 * 1024;
+  if (sms <= 0) sms = 148;
+  // One CTA per SM (shared memory).  With few (sequence, kv head) pairs a thread-block
+  // cluster shares each pair: double the cluster while the grid still fits the SMs and
+  // every CTA keeps at least two 32-block tiles.  INTERATTN_B200_SELECT_CLUSTER pins it.
+  const int max_tiles = p.nb_cap / kTileBlocks;
+  int cluster = 1;
+  while (cluster < 8 && n_pairs * cluster * 2 <= sms && max_tiles / (cluster * 2) >= 2) cluster *= 2;
+  if (const char* force = getenv("INTERATTN_B200_SELECT_CLUSTER")) {
+    const int c = atoi(force);
+    if (c == 1 || c == 2 || c == 4 || c == 8) cluster = c;
+  }
+  p.cluster = cluster;
+  p.nb_loc_cap = (max_tiles / cluster + 1) * kTileBlocks;
+  const size_t fixed = P::fixed + P::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
   if ((size_t)max_smem < fixed + 2 * (size_t)L::bytes)
     return fail(IA_ERR_UNSUPPORTED, "select: %d blocks x %d query rows per kv head do not fit in shared memory",
                 p.max_blocks, G);
@@ -842,7 +911,7 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   auto kern = condition_block_select_kernel<T, D, G>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "select: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  e = launch_overlapped(kern, (unsigned)n_pairs, (unsigned)kThreads, smem, stream, p);
+  e = launch_overlapped(kern, (unsigned)(n_pairs * cluster), (unsigned)kThreads, smem, stream, p, cluster);
   if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "condition_block_select_kernel: %s", cudaGetErrorString(e));
   return check_launch("condition_block_select_kernel");
 }
