@@ -271,6 +271,13 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   const int pair = blockIdx.x / C;  // (sequence, kv head)
   const int crank = blockIdx.x - pair * C;  // rank inside the cluster that shares this pair
   const int seq = pair / p.n_kv_heads;
+  // Launched with programmatic dependent launch: nothing in global memory may be read
+  // before the predecessor on the stream has completed (it may have produced the
+  // lengths or the query, and the attention kernel of the previous step may still be
+  // reading the selection this kernel overwrites).  Then let this step's attention
+  // kernel start occupying free SMs.
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int prefix = p.prefix_lens[seq];
   const int nb = min((prefix + p.block_size - 1) / p.block_size, p.max_blocks);
   const int n_tiles = (nb + kTileBlocks - 1) / kTileBlocks;
@@ -303,11 +310,6 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   unsigned char* stage_base = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(t_s + (size_t)G * nbl) + 1023) & ~uintptr_t(1023));
 
-  // The previous kernel on the stream (the attention kernel of the step before) may still
-  // be reading the selection this kernel is about to overwrite: wait for it, then let the
-  // attention kernel of this step start occupying free SMs.
-  grid_dependency_wait();
-  grid_launch_dependents();
   if (tid == 0) {
     for (int s = 0; s < p.n_stages; ++s) {
       mbar_init(&full_bar[s], 1);
