@@ -245,6 +245,32 @@ def test_attention_hook_in_a_small_llama():
     assert modeling_llama.eager_attention_forward is before
 
 
+def test_batched_static_cache_decode_matches_per_sequence_generation():
+    """The batched decode loop (static cache addressed in place as a paged pool,
+    eager and CUDA-graph replay) produces the tokens of the per-sequence
+    generation entry point, which the test below pins to the CPU oracle."""
+    pytest.importorskip("transformers")
+    from types import SimpleNamespace
+    from interattn_b200 import llama_decode
+    api = _api()
+    model = llama_decode.build_random_llama("tiny", dtype=torch.float32, device=DEV, seed=5)
+    batch, prompt_len, new_tokens, block, top_k = 3, 200, 7, 64, 2
+    ids = torch.randint(0, 512, (batch, prompt_len), generator=torch.Generator().manual_seed(6)).to(DEV)
+    method = SimpleNamespace(condition_delta_mode="range_bound", max_new_tokens=new_tokens, full_attention_layers=0,
+                             condition_block_size=block, condition_eps=0.0, condition_top_k=top_k,
+                             condition_rep_mode="sparse_only")
+    want = torch.cat([api.generate_condition_block_cached(
+        model=model, tokenizer=None, input_ids=ids[b:b + 1], attention_mask=torch.ones_like(ids[b:b + 1]),
+        method=method, device=DEV)[0] for b in range(batch)], dim=0)
+    eager, stats = llama_decode.generate_batched(model, ids, new_tokens, block_size=block, top_k=top_k)
+    assert torch.equal(eager, want)
+    assert stats["decode_steps_timed"] > 0 and not stats["cuda_graph"]
+    graphed, stats = llama_decode.generate_batched(model, ids, new_tokens, block_size=block, top_k=top_k,
+                                                   cuda_graph=True)
+    assert stats["cuda_graph"]
+    assert torch.equal(graphed, want)
+
+
 def test_generate_condition_block_cached_matches_oracle_greedy_tokens():
     """The generation entry point (greedy) against a hand-rolled loop whose decode
     attention is the CPU oracle, on a small random fp32 Llama."""
