@@ -238,16 +238,19 @@ def main():
     ap.add_argument("--top-k", type=int, default=64)
     ap.add_argument("--rep-mode", default="sparse_only", choices=["sparse_only", "hybrid"])
     ap.add_argument("--cuda-graph", action="store_true")
+    ap.add_argument("--full-attention-layers", type=int, default=0,
+                    help="layers below this index decode with dense SDPA (all layers: the dense baseline)")
     a = ap.parse_args()
     model = build_random_llama(a.preset, a.layers)
     g = torch.Generator(device="cuda").manual_seed(0)
     ids = torch.randint(0, model.config.vocab_size, (a.batch, a.prompt), generator=g, device="cuda")
     tokens, stats = generate_batched(model, ids, a.steps, block_size=a.block, top_k=a.top_k, rep_mode=a.rep_mode,
-                                     cuda_graph=a.cuda_graph)
+                                     cuda_graph=a.cuda_graph, full_attention_layers=a.full_attention_layers)
     line = {"metric": "llama_decode_tokens_per_s", "value": stats["tokens_per_s"], "unit": "tok/s",
             "config": {"preset": a.preset, "layers": model.config.num_hidden_layers, "batch": a.batch,
                        "prompt": a.prompt, "new_tokens": a.steps, "block": a.block, "top_k": a.top_k,
                        "rep_mode": a.rep_mode, "cuda_graph": stats["cuda_graph"], "dtype": "bf16",
+                       "full_attention_layers": a.full_attention_layers,
                        "weights": "random init", "data": "uniform random token ids"},
             "ms_per_decode_step": 1e3 * stats["decode_s"] / max(stats["decode_steps_timed"], 1),
             "prefill_s": stats["prefill_s"], "decode_steps_timed": stats["decode_steps_timed"]}
