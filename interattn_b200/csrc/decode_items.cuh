@@ -135,17 +135,21 @@ __device__ __forceinline__ void finish_pair(const DecodeParams& p, int seq, int 
   const int pair = seq * p.n_kv_heads + head;
   const int rows = p.n_kv_heads * G;
   if (p.n_splits > 1) {
-    __threadfence();  // publish this CTA's partial before it is counted
+    // The barrier orders every thread's partial stores before thread 0; its fence is
+    // cumulative, so they are visible device-wide before the count is.
     __syncthreads();
     if (threadIdx.x == 0) {
+      __threadfence();
       const int old = atomicAdd(&p.split_counters[pair], 1);
       const int is_last = old == p.n_splits - 1;
-      if (is_last) p.split_counters[pair] = 0;  // ready for the next launch
+      if (is_last) {
+        p.split_counters[pair] = 0;  // ready for the next launch
+        __threadfence();             // the other splits' partials, before this CTA reads them
+      }
       *flag = is_last;
     }
     __syncthreads();
     if (*flag == 0) return;
-    __threadfence();
   } else {
     __syncthreads();
   }
