@@ -115,6 +115,17 @@ int ia_build_summaries(const void* k_pool, const void* v_pool, const int32_t* bl
                        const int32_t* prefix_lens, const ia_geom* geom, const ia_summaries* out,
                        ia_stream_t stream);
 
+/* Summary maintenance during decode: recompute only the blocks
+ * b >= first_blocks[sequence] (int32 [batch], device) for the prefix lengths
+ * given - e.g. after 64 more generated tokens, raise prefix_lens by one block
+ * and call this with first_blocks = the old block count.  The reference never
+ * re-blocks the generated suffix (GEN/CONDITION_BLOCK_TRITON_README.md:244-246):
+ * its suffix is always attended in full and grows linearly; with this call a
+ * long generation keeps a bounded suffix.  Same kernel as ia_build_summaries. */
+int ia_update_summaries(const void* k_pool, const void* v_pool, const int32_t* block_table,
+                        const int32_t* prefix_lens, const int32_t* first_blocks, const ia_geom* geom,
+                        const ia_summaries* out, ia_stream_t stream);
+
 /* Replaces the selection stats kernel plus the routing decision
  * (IMPL/core.py:751-814, IMPL/page_attention.py:84-171): condition score of
  * every block, then either the top_k best blocks per (sequence, kv head) -

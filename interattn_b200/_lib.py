@@ -50,6 +50,8 @@ SIGNATURES = {
     "ia_last_error_string": (c_char_p, []),
     "ia_read_device_status": (c_int, [POINTER(c_int)]),
     "ia_build_summaries": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Geom), POINTER(Summaries), c_void_p]),
+    "ia_update_summaries": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Geom), POINTER(Summaries),
+                                    c_void_p]),
     "ia_select": (c_int, [c_void_p, POINTER(Summaries), c_void_p, POINTER(Geom), c_int, c_int, c_float, c_int,
                           c_void_p, c_void_p, POINTER(SelectAux), c_void_p]),
     "ia_sparse_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

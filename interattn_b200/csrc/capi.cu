@@ -134,7 +134,19 @@ int ia_build_summaries(const void* k_pool, const void* v_pool, const int32_t* bl
   if (int s = check_summaries(out)) return s;
   if (!k_pool || !v_pool || !block_table || !prefix_lens) return fail(IA_ERR_BAD_ARG, "build_summaries: null argument");
   if (!aligned16(k_pool) || !aligned16(v_pool)) return fail(IA_ERR_BAD_ARG, "build_summaries: pools must be 16-byte aligned");
-  return launch_build_summaries(k_pool, v_pool, block_table, prefix_lens, *geom, *out, (cudaStream_t)stream);
+  return launch_build_summaries(k_pool, v_pool, block_table, prefix_lens, nullptr, *geom, *out, (cudaStream_t)stream);
+}
+
+int ia_update_summaries(const void* k_pool, const void* v_pool, const int32_t* block_table,
+                        const int32_t* prefix_lens, const int32_t* first_blocks, const ia_geom* geom,
+                        const ia_summaries* out, ia_stream_t stream) {
+  if (int s = check_geom(geom)) return s;
+  if (int s = check_summaries(out)) return s;
+  if (!k_pool || !v_pool || !block_table || !prefix_lens || !first_blocks)
+    return fail(IA_ERR_BAD_ARG, "update_summaries: null argument");
+  if (!aligned16(k_pool) || !aligned16(v_pool)) return fail(IA_ERR_BAD_ARG, "update_summaries: pools must be 16-byte aligned");
+  return launch_build_summaries(k_pool, v_pool, block_table, prefix_lens, first_blocks, *geom, *out,
+                                (cudaStream_t)stream);
 }
 
 int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefix_lens,

@@ -147,8 +147,8 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 // ---- kernel launchers (one per translation unit) -------------------------------
 int launch_build_summaries(const void* k_pool, const void* v_pool, const int32_t* block_table,
-                           const int32_t* prefix_lens, const ia_geom& g, const ia_summaries& out,
-                           cudaStream_t stream);
+                           const int32_t* prefix_lens, const int32_t* first_blocks, const ia_geom& g,
+                           const ia_summaries& out, cudaStream_t stream);
 // split_counters (may be null): one int per (sequence, kv head), cleared by the selection
 // kernel for the attention kernel's fused finalize
 int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_lens, const ia_geom& g,

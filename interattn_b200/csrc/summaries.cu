@@ -17,7 +17,8 @@ template <typename T, int D>
 __global__ void __launch_bounds__(128)
 condition_block_build_summaries_kernel(const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                                        const int32_t* __restrict__ block_table,
-                                       const int32_t* __restrict__ prefix_lens, ia_geom g,
+                                       const int32_t* __restrict__ prefix_lens,
+                                       const int32_t* __restrict__ first_blocks, ia_geom g,
                                        ia_summaries out) {
   constexpr int VEC = D / 32;  // elements of a token row per lane
   const int lane = threadIdx.x & 31;
@@ -30,6 +31,8 @@ condition_block_build_summaries_kernel(const T* __restrict__ k_pool, const T* __
   const int prefix = prefix_lens[seq];
   const int first = blk * g.block_size;
   if (first >= prefix) return;  // block holds no token: its summary is never read
+  // incremental update: blocks below first_blocks[seq] keep the summary they already have
+  if (first_blocks != nullptr && blk < first_blocks[seq]) return;
   const int count = min(g.block_size, prefix - first);
 
   float ksum[VEC], vsum[VEC], kmax[VEC], kmin[VEC];
@@ -82,31 +85,31 @@ condition_block_build_summaries_kernel(const T* __restrict__ k_pool, const T* __
 
 template <typename T, int D>
 static int launch_typed(const void* k_pool, const void* v_pool, const int32_t* block_table,
-                        const int32_t* prefix_lens, const ia_geom& g, const ia_summaries& out,
-                        cudaStream_t stream) {
+                        const int32_t* prefix_lens, const int32_t* first_blocks, const ia_geom& g,
+                        const ia_summaries& out, cudaStream_t stream) {
   const int64_t n_units = (int64_t)g.batch * g.n_kv_heads * g.max_blocks;
   const int warps = 4;
   const int64_t grid = ceil_div64(n_units, warps);
   if (grid <= 0) return IA_OK;
   if (grid > 0x7fffffff) return fail(IA_ERR_UNSUPPORTED, "build_summaries: grid too large");
   condition_block_build_summaries_kernel<T, D><<<(unsigned)grid, warps * 32, 0, stream>>>(
-      static_cast<const T*>(k_pool), static_cast<const T*>(v_pool), block_table, prefix_lens, g, out);
+      static_cast<const T*>(k_pool), static_cast<const T*>(v_pool), block_table, prefix_lens, first_blocks, g, out);
   return check_launch("condition_block_build_summaries_kernel");
 }
 
 int launch_build_summaries(const void* k_pool, const void* v_pool, const int32_t* block_table,
-                           const int32_t* prefix_lens, const ia_geom& g, const ia_summaries& out,
-                           cudaStream_t stream) {
+                           const int32_t* prefix_lens, const int32_t* first_blocks, const ia_geom& g,
+                           const ia_summaries& out, cudaStream_t stream) {
   if (g.dtype == IA_BF16) {
     if (g.head_dim == 128)
-      return launch_typed<__nv_bfloat16, 128>(k_pool, v_pool, block_table, prefix_lens, g, out, stream);
+      return launch_typed<__nv_bfloat16, 128>(k_pool, v_pool, block_table, prefix_lens, first_blocks, g, out, stream);
     if (g.head_dim == 64)
-      return launch_typed<__nv_bfloat16, 64>(k_pool, v_pool, block_table, prefix_lens, g, out, stream);
+      return launch_typed<__nv_bfloat16, 64>(k_pool, v_pool, block_table, prefix_lens, first_blocks, g, out, stream);
   } else if (g.dtype == IA_F32) {
     if (g.head_dim == 128)
-      return launch_typed<float, 128>(k_pool, v_pool, block_table, prefix_lens, g, out, stream);
+      return launch_typed<float, 128>(k_pool, v_pool, block_table, prefix_lens, first_blocks, g, out, stream);
     if (g.head_dim == 64)
-      return launch_typed<float, 64>(k_pool, v_pool, block_table, prefix_lens, g, out, stream);
+      return launch_typed<float, 64>(k_pool, v_pool, block_table, prefix_lens, first_blocks, g, out, stream);
   }
   return fail(IA_ERR_UNSUPPORTED, "build_summaries: head_dim %d / dtype %d not built", g.head_dim, g.dtype);
 }

@@ -56,7 +56,12 @@ class BatchedBlockSparseDecoder:
 
     def __init__(self, *, prompt_len: int, block_size: int = 64, top_k: Optional[int] = 64,
                  eps: Optional[float] = None, rep_mode: str = "sparse_only", full_attention_layers: int = 0,
-                 device="cuda"):
+                 device="cuda", reblock: bool = False, max_len: Optional[int] = None):
+        # reblock: whenever the generated suffix has grown by a whole block, that block joins
+        # the summarised prefix (ia_update_summaries) - the suffix stays shorter than a block
+        # instead of growing with the generation.  The reference never re-blocks its suffix.
+        self.reblock, self.max_len = bool(reblock), int(max_len or prompt_len)
+        self.cur_prefix = int(prompt_len)
         self.prompt_len, self.block_size = int(prompt_len), int(block_size)
         self.top_k, self.eps, self.rep_mode = top_k, eps, rep_mode
         self.full_attention_layers = int(full_attention_layers)
@@ -74,12 +79,27 @@ class BatchedBlockSparseDecoder:
                 self.seq_lens = torch.full((b,), self.prompt_len + 1, dtype=torch.int32, device=key.device)
             k_pool, v_pool, table = cache_as_pool(key, value)
             kv = ops.PagedKV(k_pool, v_pool, table, self.prefix_lens, self.seq_lens)
-            nb = max(1, (self.prompt_len + self.block_size - 1) // self.block_size)
+            span = self.max_len if self.reblock else self.prompt_len
+            nb = max(1, (span + self.block_size - 1) // self.block_size)
             summ = ops.build_summaries(kv, self.block_size, max_blocks=nb)
             kw = dict(top_k=self.top_k) if self.top_k is not None else dict(eps=self.eps)
             st = ops.DecodeAttention(kv, summ, n_q_heads, rep_mode=self.rep_mode, **kw)
             self.layers[idx] = st
         return st
+
+    def absorb_full_blocks(self, pos: int) -> None:
+        """Before decoding the token at cache position ``pos``: move every complete block of
+        generated tokens into the summarised prefix (all layers).  Runs between steps."""
+        if not self.reblock or self.prefix_lens is None:
+            return
+        grown = (int(pos) - self.cur_prefix) // self.block_size * self.block_size
+        if grown <= 0:
+            return
+        first = torch.full_like(self.prefix_lens, self.cur_prefix // self.block_size)
+        self.cur_prefix += grown
+        self.prefix_lens.fill_(self.cur_prefix)
+        for st in self.layers.values():
+            ops.build_summaries(st.kv, self.block_size, out=st.summ, first_blocks=first)
 
     def set_position(self, pos: int) -> None:
         """Eager loops: the token being decoded sits at cache position ``pos``."""
@@ -126,7 +146,7 @@ def _attn_impl(model, name):
 
 
 def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, block_size=64, top_k=64, eps=None,
-                     rep_mode="sparse_only", full_attention_layers=0, cuda_graph=False, prefill_chunk=None):
+                     rep_mode="sparse_only", full_attention_layers=0, cuda_graph=False, reblock=False):
     """Greedy batched generation.  Returns (tokens [B, max_new_tokens], stats dict with timings)."""
     from transformers import StaticCache
     b, prompt_len = (int(x) for x in input_ids.shape)
@@ -145,7 +165,8 @@ def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, blo
     tokens = torch.empty((b, max_new_tokens), dtype=tok.dtype, device=dev)
     tokens[:, 0:1] = tok
     decoder = BatchedBlockSparseDecoder(prompt_len=prompt_len, block_size=block_size, top_k=top_k, eps=eps,
-                                        rep_mode=rep_mode, full_attention_layers=full_attention_layers, device=dev)
+                                        rep_mode=rep_mode, full_attention_layers=full_attention_layers, device=dev,
+                                        reblock=reblock, max_len=cache_len)
     tok_buf = tok.clone()
     pos_buf = torch.tensor([prompt_len], device=dev, dtype=torch.long)
 
@@ -181,6 +202,7 @@ def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, blo
         ev0.record()
         timed = 0
         while done < n_decode:
+            decoder.absorb_full_blocks(prompt_len + done)
             if graph is not None:
                 graph.replay()
             else:
@@ -238,6 +260,7 @@ def main():
     ap.add_argument("--top-k", type=int, default=64)
     ap.add_argument("--rep-mode", default="sparse_only", choices=["sparse_only", "hybrid"])
     ap.add_argument("--cuda-graph", action="store_true")
+    ap.add_argument("--reblock", action="store_true", help="summarise generated tokens block by block")
     ap.add_argument("--full-attention-layers", type=int, default=0,
                     help="layers below this index decode with dense SDPA (all layers: the dense baseline)")
     a = ap.parse_args()
@@ -245,12 +268,13 @@ def main():
     g = torch.Generator(device="cuda").manual_seed(0)
     ids = torch.randint(0, model.config.vocab_size, (a.batch, a.prompt), generator=g, device="cuda")
     tokens, stats = generate_batched(model, ids, a.steps, block_size=a.block, top_k=a.top_k, rep_mode=a.rep_mode,
-                                     cuda_graph=a.cuda_graph, full_attention_layers=a.full_attention_layers)
+                                     cuda_graph=a.cuda_graph, full_attention_layers=a.full_attention_layers,
+                                     reblock=a.reblock)
     line = {"metric": "llama_decode_tokens_per_s", "value": stats["tokens_per_s"], "unit": "tok/s",
             "config": {"preset": a.preset, "layers": model.config.num_hidden_layers, "batch": a.batch,
                        "prompt": a.prompt, "new_tokens": a.steps, "block": a.block, "top_k": a.top_k,
                        "rep_mode": a.rep_mode, "cuda_graph": stats["cuda_graph"], "dtype": "bf16",
-                       "full_attention_layers": a.full_attention_layers,
+                       "full_attention_layers": a.full_attention_layers, "reblock": a.reblock,
                        "weights": "random init", "data": "uniform random token ids"},
             "ms_per_decode_step": 1e3 * stats["decode_s"] / max(stats["decode_steps_timed"], 1),
             "prefill_s": stats["prefill_s"], "decode_steps_timed": stats["decode_steps_timed"]}

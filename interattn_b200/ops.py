@@ -128,9 +128,26 @@ class BlockSummaries:
 
 
 def build_summaries(kv: PagedKV, block_size: int, max_blocks: Optional[int] = None,
-                    out: Optional[BlockSummaries] = None) -> BlockSummaries:
-    """Block summaries of every sequence's prefix (reference: ``_build_prompt_blocks``)."""
+                    out: Optional[BlockSummaries] = None,
+                    first_blocks: Optional[torch.Tensor] = None) -> BlockSummaries:
+    """Block summaries of every sequence's prefix (reference: ``_build_prompt_blocks``).
+
+    ``first_blocks`` (int32 [B], device; needs ``out``) makes it an incremental
+    update: only blocks ``b >= first_blocks[seq]`` are recomputed - used when
+    the generated suffix has grown by whole blocks and ``kv.prefix_lens`` was
+    raised to take them into the summarised prefix."""
     lib = _lib.load()
+    if first_blocks is not None:
+        if out is None:
+            raise ValueError("an incremental update needs the summaries to update (out=)")
+        _need_cuda(first_blocks)
+        if first_blocks.dtype != torch.int32 or not first_blocks.is_contiguous() or first_blocks.numel() != kv.batch:
+            raise ValueError("first_blocks must be a contiguous int32 tensor with one entry per sequence")
+        g = kv.geom(1, block_size, out.max_blocks)
+        s = out.c_struct()
+        check(lib.ia_update_summaries(_ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),
+                                      _ptr(first_blocks), ctypes.byref(g), ctypes.byref(s), _stream()))
+        return out
     if max_blocks is None:
         max_blocks = out.max_blocks if out is not None else max(
             1, (int(kv.block_table.shape[1]) * kv.page_size + block_size - 1) // block_size)

@@ -216,6 +216,47 @@ def test_layer_step_replays_from_a_cuda_graph():
     assert torch.equal(kv.seq_lens, full_seq)
 
 
+def test_incremental_summary_update_equals_full_rebuild():
+    """Summary maintenance during decode: when the generated suffix has grown by
+    whole blocks, raising prefix_lens and recomputing only the new blocks gives
+    the same summaries as rebuilding everything, and the next step then selects
+    among the new blocks too."""
+    ops = _ops()
+    cfg = DecodeConfig("grow", "bfloat16", 2, 8, 2, 128, 16, 64, 3, (640, 200), (150, 70), seed=12)
+    case = make_case(cfg)
+    q, kv = to_device(case)
+    nb = (max(p + s for p, s in zip(cfg.prefix_lens, cfg.suffix_lens)) + 63) // 64
+    summ = ops.build_summaries(kv, 64, max_blocks=nb)                  # prompt blocks only
+    before = summ.k_bar.clone()
+    old_blocks = torch.tensor([(p + 63) // 64 for p in cfg.prefix_lens], dtype=torch.int32, device=q.device)
+    # two more whole blocks of the first sequence and one of the second join the summarised prefix
+    grown = torch.tensor([cfg.prefix_lens[0] + 128, 256], dtype=torch.int32, device=q.device)
+    kv.prefix_lens.copy_(grown)
+    first = torch.tensor([cfg.prefix_lens[0] // 64, 200 // 64], dtype=torch.int32, device=q.device)
+    ops.build_summaries(kv, 64, out=summ, first_blocks=first)
+    full = ops.build_summaries(kv, 64, max_blocks=nb)
+    torch.cuda.synchronize()
+    for b, n_new in ((0, (640 + 128) // 64), (1, 4)):
+        for name in ("k_bar", "k_max", "k_min", "v_bar", "v_norm_max"):
+            assert torch.equal(getattr(summ, name)[b, :, :n_new], getattr(full, name)[b, :, :n_new]), name
+    assert torch.equal(summ.k_bar[0, :, : int(old_blocks[0])], before[0, :, : int(old_blocks[0])])   # untouched
+    # the step over the grown prefix matches the oracle (new blocks selectable, shorter suffix)
+    idx, cnt, aux = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, want=("z",))
+    o, lse = ops.sparse_decode(q, kv, idx, cnt, block_size=64, max_blocks=nb, n_splits=2)
+    out = ops.finalize(o, lse, torch.float32).cpu()
+    for b in range(cfg.batch):
+        plen = int(grown[b])
+        k, v = logical_kv(case, b)
+        osum = oracle_summaries_from_gpu(summ, b, plen)
+        qg = case["q"][b].reshape(2, 4, 128).float()
+        terms = orc.condition_terms(qg, osum)
+        ranked, mask = orc.select_topk(terms["score"], osum.counts, cfg.top_k)
+        for h in range(2):
+            assert idx[b, h, : int(cnt[b, h])].cpu().tolist() == sorted(ranked[h])
+        want = orc.decode_attention(qg, k, v, plen, 64, mask, rep_mode="sparse_only")
+        torch.testing.assert_close(out[b].reshape(2, 4, 128), want, rtol=1e-2, atol=2e-2)
+
+
 def test_block_range_shares_merge_to_the_whole(bundle):
     """Split-KV across ranks, emulated on one GPU: each 'rank' attends over its
     own block range (the last one also over the suffix); merging the (o, lse)
