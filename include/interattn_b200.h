@@ -243,6 +243,40 @@ int ia_decode_attention_noalloc(const void* q, const void* k_pool, const void* v
                                 const ia_geom* geom, int mode, int top_k, float eps, int max_sel,
                                 int rep_mode, int n_splits, void* out, ia_stream_t stream);
 
+/* ---- the element-wise part of a batched Llama decode step -----------------------
+ * The reference replays the Hugging Face model's own PyTorch ops around its
+ * attention hook inside one captured decode step (IMPL/core.py:190-316,
+ * _generate_condition_block_cuda_graph); each entry point below replaces one
+ * group of those ops by a single launch and keeps their bf16 rounding points
+ * (transformers 5.5.0, models/llama/modeling_llama.py).  All tensors are bf16
+ * device memory, rows contiguous, pointers 16-byte aligned.
+ *
+ * ia_llama_add_rmsnorm - LlamaDecoderLayer's `residual + hidden_states` followed
+ *   by LlamaRMSNorm.forward (modeling_llama.py:62-67).  residual [n_rows, hidden]
+ *   is updated in place with bf16(residual + delta) when delta is not null;
+ *   out = weight * bf16(x * rsqrt(mean(x^2) + eps)).
+ * ia_llama_rope_append - apply_rotary_pos_emb (modeling_llama.py:146-168) on the
+ *   q and k heads of the fused projection row qkv [batch, (Hq + 2 Hkv) * D],
+ *   with cos/sin rows [max_pos, D] as LlamaRotaryEmbedding.forward returns them,
+ *   fused with the static cache's update (one index_copy_ per tensor in
+ *   transformers/cache_utils.py StaticLayer.update): sequence b's token sits at
+ *   position seq_lens[b] - 1; k (rotated) and v go to
+ *   cache + b * cache_seq_stride + h * cache_head_stride + position * D (element
+ *   strides), q (rotated) to q_out [batch, Hq, D].
+ * ia_llama_silu_mul - LlamaMLP.forward's act_fn(gate) * up on the fused
+ *   projection row gate_up [n_rows, 2 * intermediate] -> out [n_rows, intermediate].
+ * ia_llama_argmax - the greedy `logits.argmax(-1)` of the generation loop
+ *   (IMPL/core.py:136, 178, 281); lowest index among equal maxima; out int64 [n_rows]. */
+int ia_llama_add_rmsnorm(void* residual, const void* delta, const void* weight, void* out, int n_rows,
+                         int hidden, float eps, ia_stream_t stream);
+int ia_llama_rope_append(const void* qkv, const void* cos_table, const void* sin_table, int max_pos,
+                         const int32_t* seq_lens, void* k_cache, void* v_cache, int64_t cache_seq_stride,
+                         int64_t cache_head_stride, int cache_len, void* q_out, int batch, int n_q_heads,
+                         int n_kv_heads, int head_dim, ia_stream_t stream);
+int ia_llama_silu_mul(const void* gate_up, void* out, int n_rows, int intermediate, ia_stream_t stream);
+int ia_llama_argmax(const void* logits, int64_t row_stride, int n_rows, int vocab, int64_t* out,
+                    ia_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -74,6 +74,11 @@ SIGNATURES = {
     "ia_decode_attention_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             POINTER(Summaries), POINTER(Geom), c_int, c_int, c_float, c_int, c_int,
                                             c_int, c_void_p, c_void_p]),
+    "ia_llama_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
+    "ia_llama_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                     c_int64, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "ia_llama_silu_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "ia_llama_argmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
 }
 
 _lib = None

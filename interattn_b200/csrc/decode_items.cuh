@@ -55,8 +55,10 @@ struct ItemRange {
 __device__ __forceinline__ ItemRange item_range(const DecodeParams& p, int seq, int head, int split,
                                                 int* scratch) {
   ItemRange r;
-  r.prefix = p.prefix_lens[seq];
-  r.seq_len = p.seq_lens[seq];
+  // lengths come from device memory: never index the block table past its row
+  const int capacity = p.max_pages * p.page_size;
+  r.prefix = min(max(p.prefix_lens[seq], 0), capacity);
+  r.seq_len = min(p.seq_lens[seq], capacity);
   r.nb_eff = min((r.prefix + p.block_size - 1) / p.block_size, p.max_blocks);
   r.lo_b = max(p.block_lo, 0);
   r.hi_b = min(p.block_hi, r.nb_eff);

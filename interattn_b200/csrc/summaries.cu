@@ -28,7 +28,8 @@ condition_block_build_summaries_kernel(const T* __restrict__ k_pool, const T* __
   const int blk = (int)(unit % g.max_blocks);
   const int head = (int)((unit / g.max_blocks) % g.n_kv_heads);
   const int seq = (int)(unit / ((int64_t)g.max_blocks * g.n_kv_heads));
-  const int prefix = prefix_lens[seq];
+  // lengths come from device memory: never index the block table past its row
+  const int prefix = min(prefix_lens[seq], g.max_pages * g.page_size);
   const int first = blk * g.block_size;
   if (first >= prefix) return;  // block holds no token: its summary is never read
   // incremental update: blocks below first_blocks[seq] keep the summary they already have

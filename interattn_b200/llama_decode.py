@@ -146,8 +146,15 @@ def _attn_impl(model, name):
 
 
 def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, block_size=64, top_k=64, eps=None,
-                     rep_mode="sparse_only", full_attention_layers=0, cuda_graph=False, reblock=False):
-    """Greedy batched generation.  Returns (tokens [B, max_new_tokens], stats dict with timings)."""
+                     rep_mode="sparse_only", full_attention_layers=0, cuda_graph=False, reblock=False,
+                     fused_step=False, force_tokens=None, collect_logits=False):
+    """Greedy batched generation.  Returns (tokens [B, max_new_tokens], stats dict with timings).
+
+    fused_step: decode through ``llama_step.FusedLlamaStep`` (fused element-wise kernels and
+    concatenated projection weights) instead of the Hugging Face modules around the hook.
+    force_tokens [B, max_new_tokens]: feed these tokens instead of the greedy ones (teacher
+    forcing, for comparing two decode paths step by step); collect_logits: keep every decode
+    step's logits in ``stats["logits"]`` ([steps, B, vocab]).  Neither works with cuda_graph."""
     from transformers import StaticCache
     b, prompt_len = (int(x) for x in input_ids.shape)
     dev = input_ids.device
@@ -169,11 +176,38 @@ def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, blo
                                         reblock=reblock, max_len=cache_len)
     tok_buf = tok.clone()
     pos_buf = torch.tensor([prompt_len], device=dev, dtype=torch.long)
+    if cuda_graph and (force_tokens is not None or collect_logits):
+        raise ValueError("force_tokens / collect_logits need the eager loop")
+    if force_tokens is not None:
+        tokens[:, 0:1] = force_tokens[:, 0:1]
+        tok_buf.copy_(force_tokens[:, 0:1])
+    kept_logits = []
+    fused = None
+    if fused_step:
+        if full_attention_layers > 0:
+            raise ValueError("the fused step needs every layer on the sparse path")
+        from .llama_step import FusedLlamaStep
+        n_q_heads = int(model.config.num_attention_heads)
+        attention = [decoder._layer(i, cache.layers[i].keys, cache.layers[i].values, n_q_heads)
+                     for i in range(int(model.config.num_hidden_layers))]
+        fused = FusedLlamaStep(model, cache, attention, decoder.seq_lens, cache_len)
 
     def one_step():
-        o = model(input_ids=tok_buf, past_key_values=cache, use_cache=True, logits_to_keep=1,
-                  cache_position=pos_buf)
-        tok_buf.copy_(o.logits[:, -1, :].argmax(dim=-1, keepdim=True))
+        if fused is not None:
+            fused.step(tok_buf)
+            logits = fused.logits
+        else:
+            o = model(input_ids=tok_buf, past_key_values=cache, use_cache=True, logits_to_keep=1,
+                      cache_position=pos_buf)
+            logits = o.logits[:, -1, :]
+            tok_buf.copy_(logits.argmax(dim=-1, keepdim=True))
+        if collect_logits:
+            kept_logits.append(logits.clone())
+
+    def keep_token(i):
+        if force_tokens is not None:
+            tok_buf.copy_(force_tokens[:, i:i + 1])
+        tokens[:, i:i + 1] = tok_buf
 
     n_decode = max_new_tokens - 1
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -184,7 +218,7 @@ def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, blo
             decoder.set_position(prompt_len + done)
             one_step()
             done += 1
-            tokens[:, done:done + 1] = tok_buf
+            keep_token(done)
             pos_buf.add_(1)
         torch.cuda.synchronize()
         stats["summaries_and_warmup_steps"] = warm
@@ -211,13 +245,16 @@ def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, blo
                 pos_buf.add_(1)
             done += 1
             timed += 1
-            tokens[:, done:done + 1] = tok_buf
+            keep_token(done)
         ev1.record()
         torch.cuda.synchronize()
     stats["decode_steps_timed"] = timed
     stats["decode_s"] = ev0.elapsed_time(ev1) * 1e-3
     stats["tokens_per_s"] = b * timed / stats["decode_s"] if timed else float("nan")
     stats["cuda_graph"] = graph is not None
+    stats["fused_step"] = fused is not None
+    if collect_logits:
+        stats["logits"] = torch.stack(kept_logits) if kept_logits else None
     return tokens, stats
 
 
@@ -261,6 +298,8 @@ def main():
     ap.add_argument("--rep-mode", default="sparse_only", choices=["sparse_only", "hybrid"])
     ap.add_argument("--cuda-graph", action="store_true")
     ap.add_argument("--reblock", action="store_true", help="summarise generated tokens block by block")
+    ap.add_argument("--fused-step", action="store_true",
+                    help="fused element-wise kernels and concatenated projections instead of the model's modules")
     ap.add_argument("--full-attention-layers", type=int, default=0,
                     help="layers below this index decode with dense SDPA (all layers: the dense baseline)")
     a = ap.parse_args()
@@ -269,12 +308,12 @@ def main():
     ids = torch.randint(0, model.config.vocab_size, (a.batch, a.prompt), generator=g, device="cuda")
     tokens, stats = generate_batched(model, ids, a.steps, block_size=a.block, top_k=a.top_k, rep_mode=a.rep_mode,
                                      cuda_graph=a.cuda_graph, full_attention_layers=a.full_attention_layers,
-                                     reblock=a.reblock)
+                                     reblock=a.reblock, fused_step=a.fused_step)
     line = {"metric": "llama_decode_tokens_per_s", "value": stats["tokens_per_s"], "unit": "tok/s",
             "config": {"preset": a.preset, "layers": model.config.num_hidden_layers, "batch": a.batch,
                        "prompt": a.prompt, "new_tokens": a.steps, "block": a.block, "top_k": a.top_k,
                        "rep_mode": a.rep_mode, "cuda_graph": stats["cuda_graph"], "dtype": "bf16",
-                       "full_attention_layers": a.full_attention_layers, "reblock": a.reblock,
+                       "full_attention_layers": a.full_attention_layers, "reblock": a.reblock, "fused_step": a.fused_step,
                        "weights": "random init", "data": "uniform random token ids"},
             "ms_per_decode_step": 1e3 * stats["decode_s"] / max(stats["decode_steps_timed"], 1),
             "prefill_s": stats["prefill_s"], "decode_steps_timed": stats["decode_steps_timed"]}

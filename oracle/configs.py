@@ -65,6 +65,11 @@ CONFIGS: Dict[str, DecodeConfig] = {
     "cfg4_longctx_128k": DecodeConfig(
         "cfg4_longctx_128k", "bfloat16", 4, 32, 8, 128, 16, 64, 32,
         (131072,) * 4, (0,) * 4, seed=0),
+    # one attention layer of the full Llama-3-8B decode (batch 32, 8192-token prompts, top-64 of
+    # 128 blocks), half way through its 256 generated tokens
+    "cfg3_layer_llama8b_8k": DecodeConfig(
+        "cfg3_layer_llama8b_8k", "bfloat16", 32, 32, 8, 128, 16, 64, 64,
+        (8192,) * 32, (128,) * 32, seed=0),
     # Llama-3-70B attention geometry, batch 64, ragged lengths in [1024, 65536], top-48
     "cfg5_llama70b_ragged": DecodeConfig(
         "cfg5_llama70b_ragged", "bfloat16", 64, 64, 8, 128, 16, 64, 48,
