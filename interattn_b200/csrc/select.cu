@@ -28,6 +28,8 @@
 //   * otherwise: CUDA cores.  Lane <-> block; a stage is consumed by a group of
 //     four warps, each taking a quarter of head_dim; their partial sums meet in
 //     shared memory and warp w of the group finishes rows g = w, w + 4, ...
+#include <string.h>
+
 #include <cuda.h>  // CUtensorMap (types only; the encoder is fetched through the runtime)
 
 #include "ia_common.cuh"
@@ -48,11 +50,20 @@ int read_and_clear_device_status(int* out) {
 
 namespace {
 
-constexpr int kGroups = 3;         // warp groups, one ring stage each at a time
+// CTA shape: NG warp groups of four warps (one ring stage each at a time) plus one
+// TMA producer warp.  The wide shape (3 groups, 416 threads, one CTA per SM) gives a
+// single (sequence, kv head) pair the whole SM; the narrow shape (1 group, 160
+// threads, two or three CTAs per SM) is for batches with more pairs than SMs, where
+// the serial phases of one pair overlap the streaming of its neighbours.
 constexpr int kGroupWarps = 4;     // warps per group: each takes head_dim / 4
-constexpr int kConsumerWarps = kGroups * kGroupWarps;
-constexpr int kWarps = kConsumerWarps + 1;  // + one TMA producer warp
-constexpr int kThreads = kWarps * 32;
+template <int NG> struct Shape {
+  static constexpr int groups = NG;
+  static constexpr int consumer_warps = NG * kGroupWarps;
+  static constexpr int warps = consumer_warps + 1;
+  static constexpr int threads = warps * 32;
+  static constexpr int min_ctas = NG >= 3 ? 1 : 3;
+};
+constexpr int kWideGroups = 3, kNarrowGroups = 1;
 constexpr int kTileBlocks = 32;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kWaitPolls = 1u << 20;  // bounded mbarrier wait, then give up
@@ -243,7 +254,8 @@ __device__ __forceinline__ const E* swz(const unsigned char* vec_base, int row, 
 }
 
 // Fixed shared-memory carve-up (bytes), shared by the kernel and the launcher.
-template <int D, int G, bool MMA> struct SmemPlan {
+template <int D, int G, bool MMA, int NG> struct SmemPlan {
+  static constexpr int kWarps = Shape<NG>::warps, kConsumerWarps = Shape<NG>::consumer_warps;
   static constexpr size_t bars = 2 * kMaxStages * 8;
   static constexpr size_t hist = 3 * 256 * 4;
   static constexpr size_t scan = 32 * 4;
@@ -259,11 +271,13 @@ template <int D, int G, bool MMA> struct SmemPlan {
   }
 };
 
-template <typename T, int D, int G>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, int D, int G, int NG>
+__global__ void __launch_bounds__(Shape<NG>::threads, Shape<NG>::min_ctas)
 condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   using L = TileLayout<T, D>;
-  using P = SmemPlan<D, G, kUseMma<T, G>>;
+  using P = SmemPlan<D, G, kUseMma<T, G>, NG>;
+  constexpr int kGroups = NG, kConsumerWarps = Shape<NG>::consumer_warps, kWarps = Shape<NG>::warps,
+                kThreads = Shape<NG>::threads;
   constexpr int DQ = D / kGroupWarps;  // head_dim slice of one warp of a group
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -873,21 +887,36 @@ static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t 
   return IA_OK;
 }
 
+template <typename T, int D, int G, int NG>
+static int launch_shaped(const SelectParams& p, int n_pairs, size_t smem, cudaStream_t stream) {
+  auto kern = condition_block_select_kernel<T, D, G, NG>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "select: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  e = launch_overlapped(kern, (unsigned)(n_pairs * p.cluster), (unsigned)Shape<NG>::threads, smem, stream, p,
+                        p.cluster);
+  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "condition_block_select_kernel: %s", cudaGetErrorString(e));
+  return check_launch("condition_block_select_kernel");
+}
+
 template <typename T, int D, int G>
 static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stream) {
   using L = TileLayout<T, D>;
-  using P = SmemPlan<D, G, kUseMma<T, G>>;
+  using PW = SmemPlan<D, G, kUseMma<T, G>, kWideGroups>;
+  using PN = SmemPlan<D, G, kUseMma<T, G>, kNarrowGroups>;
   SelectParams p = base;
   p.nb_cap = (p.max_blocks + 31) & ~31;
-  int dev = 0, max_smem = 0, sms = 0;
+  int dev = 0, max_smem = 0, sm_smem = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  cudaDeviceGetAttribute(&sm_smem, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (max_smem <= 0) max_smem = 227 * 1024;
+  if (sm_smem <= 0) sm_smem = 228 * 1024;
   if (sms <= 0) sms = 148;
-  // One CTA per SM (shared memory).  With few (sequence, kv head) pairs a thread-block
-  // cluster shares each pair: double the cluster while the grid still fits the SMs and
-  // every CTA keeps at least two 32-block tiles.  INTERATTN_B200_SELECT_CLUSTER pins it.
+  // Wide shape: one CTA per SM (shared memory).  With few (sequence, kv head) pairs a
+  // thread-block cluster shares each pair: double the cluster while the grid still fits
+  // the SMs and every CTA keeps at least two 32-block tiles.
+  // INTERATTN_B200_SELECT_CLUSTER pins it.
   const int max_tiles = p.nb_cap / kTileBlocks;
   int cluster = 1;
   while (cluster < 8 && n_pairs * cluster * 2 <= sms && max_tiles / (cluster * 2) >= 2) cluster *= 2;
@@ -897,25 +926,39 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   }
   p.cluster = cluster;
   p.nb_loc_cap = (max_tiles / cluster + 1) * kTileBlocks;
-  const size_t fixed = P::fixed + P::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
+  const int64_t rows = (int64_t)n_pairs * p.max_blocks;
+  if (rows > 0x7fffffff) return fail(IA_ERR_UNSUPPORTED, "select: %lld summary rows exceed the TMA coordinate range", (long long)rows);
+  if (int s = encode_rows(&p.tm_kbar, p.k_bar, false, rows, D)) return s;
+  if (int s = encode_rows(&p.tm_kmax, p.k_max, sizeof(T) == 2, rows, D)) return s;
+  if (int s = encode_rows(&p.tm_kmin, p.k_min, sizeof(T) == 2, rows, D)) return s;
+
+  // Narrow shape: more pairs than SMs and room for two or three CTAs per SM (each CTA
+  // pays 1 KB of reserved shared memory) with a ring of at least two stages.
+  // INTERATTN_B200_SELECT_SHAPE=wide|narrow pins the choice where it fits.
+  const char* shape = getenv("INTERATTN_B200_SELECT_SHAPE");
+  const bool want_narrow = shape != nullptr ? strcmp(shape, "narrow") == 0 : n_pairs > sms;
+  if (cluster == 1 && want_narrow) {
+    const size_t fixed = PN::fixed + PN::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
+    int ctas = (n_pairs + sms - 1) / sms;
+    ctas = ctas < 2 ? 2 : (ctas > 3 ? 3 : ctas);
+    for (; ctas >= 2; --ctas) {
+      const size_t budget = (size_t)sm_smem / ctas - 1024;
+      if (budget < fixed + 2 * (size_t)L::bytes) continue;
+      int stages = (int)((budget - fixed) / L::bytes);
+      if (stages > max_tiles) stages = max_tiles < 2 ? 2 : max_tiles;
+      if (stages > kMaxStages) stages = kMaxStages;
+      p.n_stages = stages;
+      return launch_shaped<T, D, G, kNarrowGroups>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
+    }
+  }
+  const size_t fixed = PW::fixed + PW::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
   if ((size_t)max_smem < fixed + 2 * (size_t)L::bytes)
     return fail(IA_ERR_UNSUPPORTED, "select: %d blocks x %d query rows per kv head do not fit in shared memory",
                 p.max_blocks, G);
   int stages = (int)(((size_t)max_smem - fixed) / L::bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.n_stages = stages;
-  const int64_t rows = (int64_t)n_pairs * p.max_blocks;
-  if (rows > 0x7fffffff) return fail(IA_ERR_UNSUPPORTED, "select: %lld summary rows exceed the TMA coordinate range", (long long)rows);
-  if (int s = encode_rows(&p.tm_kbar, p.k_bar, false, rows, D)) return s;
-  if (int s = encode_rows(&p.tm_kmax, p.k_max, sizeof(T) == 2, rows, D)) return s;
-  if (int s = encode_rows(&p.tm_kmin, p.k_min, sizeof(T) == 2, rows, D)) return s;
-  const size_t smem = fixed + (size_t)stages * L::bytes;
-  auto kern = condition_block_select_kernel<T, D, G>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "select: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  e = launch_overlapped(kern, (unsigned)(n_pairs * cluster), (unsigned)kThreads, smem, stream, p, cluster);
-  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "condition_block_select_kernel: %s", cudaGetErrorString(e));
-  return check_launch("condition_block_select_kernel");
+  return launch_shaped<T, D, G, kWideGroups>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
 }
 
 template <typename T, int D>
