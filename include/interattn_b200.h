@@ -277,6 +277,25 @@ int ia_llama_silu_mul(const void* gate_up, void* out, int n_rows, int intermedia
 int ia_llama_argmax(const void* logits, int64_t row_stride, int n_rows, int vocab, int64_t* out,
                     ia_stream_t stream);
 
+/* out[m, n] = x[m, k] * w[n, k]^T - nn.Linear without bias as the Llama modules
+ * call it (modeling_llama.py: q/k/v/o_proj, gate/up/down_proj, lm_head) for a
+ * decode batch of m <= 32 rows; bf16 in and out, fp32 accumulation, rows
+ * contiguous, k a multiple of 8.  The kernel is bound by reading the weights once;
+ * several projections of the same input run as one call on their row-concatenated
+ * weights.
+ * The weights are static, so they are packed once: ia_llama_gemm_pack turns the
+ * row-major w [n, k] into ia_llama_gemm_packed_bytes(n, k) bytes (tiles of 128 rows
+ * x 64 columns in the order and shared-memory layout the kernel streams them;
+ * ragged edges zero-filled), and ia_llama_gemm takes that packed buffer.
+ * workspace: ia_llama_gemm_workspace_bytes(n) bytes, 16-byte aligned, zero before
+ * its first use and left zero where it has to be by every call; calls that
+ * overlap on the GPU need workspaces of their own. */
+int64_t ia_llama_gemm_packed_bytes(int n, int k);
+int ia_llama_gemm_pack(const void* w, int n, int k, void* packed, ia_stream_t stream);
+int64_t ia_llama_gemm_workspace_bytes(int n);
+int ia_llama_gemm(const void* x, const void* w_packed, void* out, int m, int n, int k, void* workspace,
+                  int64_t workspace_bytes, ia_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

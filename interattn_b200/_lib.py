@@ -79,6 +79,10 @@ SIGNATURES = {
                                      c_int64, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "ia_llama_silu_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "ia_llama_argmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "ia_llama_gemm_packed_bytes": (c_int64, [c_int, c_int]),
+    "ia_llama_gemm_pack": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "ia_llama_gemm_workspace_bytes": (c_int64, [c_int]),
+    "ia_llama_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_void_p]),
 }
 
 _lib = None

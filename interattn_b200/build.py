@@ -21,7 +21,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "libinterattn_b200.so")
 SOURCES = ["capi.cu", "summaries.cu", "select.cu", "sparse_decode.cu", "sparse_decode_mma.cu", "finalize.cu",
-           "llama_step.cu"]
+           "llama_step.cu", "skinny_gemm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

@@ -21,7 +21,7 @@ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // Bit set by a kernel whose bounded wait (mbarrier) ran out; read with
 // ia_read_device_status().  Waiting is always bounded so that a programming
 // error shows up as a status bit instead of a hung GPU.
-enum : int { DEV_STATUS_SELECT_WAIT_TIMEOUT = 1 };
+enum : int { DEV_STATUS_SELECT_WAIT_TIMEOUT = 1, DEV_STATUS_GEMM_WAIT_TIMEOUT = 2 };
 int read_and_clear_device_status(int* out);  // defined next to the kernel that owns the word
 
 // ---- dtype traits ---------------------------------------------------------------

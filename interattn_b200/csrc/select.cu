@@ -39,6 +39,27 @@ namespace ia {
 // Set by a kernel whose bounded mbarrier wait ran out (see mbar_wait below).
 __device__ int g_device_status = 0;
 
+// device address of the status word on the current device, for kernels of other translation units
+int* device_status_address() {
+  constexpr int kMaxDevices = 64;
+  static int* cached[kMaxDevices] = {};  // every thread would store the same pointer
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    fail(IA_ERR_LAUNCH, "device status: no current device");
+    return nullptr;
+  }
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_device_status);
+    if (e != cudaSuccess) {
+      fail(IA_ERR_LAUNCH, "device status: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cached[dev] = static_cast<int*>(ptr);
+  }
+  return cached[dev];
+}
+
 int read_and_clear_device_status(int* out) {
   int v = 0, zero = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int));

@@ -147,14 +147,15 @@ def _attn_impl(model, name):
 
 def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, block_size=64, top_k=64, eps=None,
                      rep_mode="sparse_only", full_attention_layers=0, cuda_graph=False, reblock=False,
-                     fused_step=False, force_tokens=None, collect_logits=False):
+                     fused_step=False, force_tokens=None, collect_logits=False, own_gemm=None):
     """Greedy batched generation.  Returns (tokens [B, max_new_tokens], stats dict with timings).
 
     fused_step: decode through ``llama_step.FusedLlamaStep`` (fused element-wise kernels and
     concatenated projection weights) instead of the Hugging Face modules around the hook.
     force_tokens [B, max_new_tokens]: feed these tokens instead of the greedy ones (teacher
     forcing, for comparing two decode paths step by step); collect_logits: keep every decode
-    step's logits in ``stats["logits"]`` ([steps, B, vocab]).  Neither works with cuda_graph."""
+    step's logits in ``stats["logits"]`` ([steps, B, vocab]).  Neither works with cuda_graph.
+    own_gemm: passed to ``FusedLlamaStep`` (which projections use this library's GEMM kernel)."""
     from transformers import StaticCache
     b, prompt_len = (int(x) for x in input_ids.shape)
     dev = input_ids.device
@@ -190,7 +191,7 @@ def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, blo
         n_q_heads = int(model.config.num_attention_heads)
         attention = [decoder._layer(i, cache.layers[i].keys, cache.layers[i].values, n_q_heads)
                      for i in range(int(model.config.num_hidden_layers))]
-        fused = FusedLlamaStep(model, cache, attention, decoder.seq_lens, cache_len)
+        fused = FusedLlamaStep(model, cache, attention, decoder.seq_lens, cache_len, own_gemm=own_gemm)
 
     def one_step():
         if fused is not None:

@@ -10,8 +10,9 @@ static cache, as ten launches per layer:
     add+RMSNorm | QKV GEMM | RoPE+cache append | block selection | sparse attention
     | O GEMM | add+RMSNorm | gate/up GEMM | SiLU*up | down GEMM
 
-The GEMMs are ``torch.mm`` on concatenated weights (cuBLAS); everything else is
-this library's CUDA (``csrc/llama_step.cu`` and the attention kernels), keeping the
+The GEMMs run on concatenated weights through ``torch.mm`` (cuBLAS) or, on request,
+``csrc/skinny_gemm.cu`` (a tcgen05 weight-streaming kernel for batches of at most
+32 rows); everything else is ``csrc/llama_step.cu`` and the attention kernels, keeping the
 bf16 rounding points of ``transformers.models.llama.modeling_llama`` so that the
 fused and the module-by-module step agree up to fp32 summation order.
 """
@@ -88,6 +89,39 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gemm_workspace(n: int, device) -> torch.Tensor:
+    """Zeroed scratch for ``gemm`` calls with at most ``n`` output columns (one per stream)."""
+    size = int(_lib.load().ia_llama_gemm_workspace_bytes(int(n)))
+    return torch.zeros(size, dtype=torch.uint8, device=device)
+
+
+class PackedWeight:
+    """A linear layer's weight ``[n, k]`` in the tile order ``gemm`` streams it (packed once)."""
+
+    def __init__(self, w: torch.Tensor):
+        _need_cuda(w)
+        _bf16(w)
+        if w.dim() != 2:
+            raise ValueError("a [n, k] weight is needed")
+        self.n, self.k = int(w.shape[0]), int(w.shape[1])
+        lib = _lib.load()
+        self.data = torch.empty(int(lib.ia_llama_gemm_packed_bytes(self.n, self.k)), dtype=torch.uint8,
+                                device=w.device)
+        _lib.check(lib.ia_llama_gemm_pack(_ptr(w), self.n, self.k, _ptr(self.data), _stream()))
+
+
+def gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor, workspace: torch.Tensor) -> torch.Tensor:
+    """``out [m, n] = x [m, k] @ w [n, k].T`` for m <= 32 (``nn.Linear`` without bias)."""
+    _need_cuda(x)
+    _bf16(x, out)
+    m, k = x.shape
+    if k != w.k or out.shape != (m, w.n):
+        raise ValueError("gemm: shapes differ")
+    _lib.check(_lib.load().ia_llama_gemm(_ptr(x), _ptr(w.data), _ptr(out), m, w.n, k, _ptr(workspace),
+                                         int(workspace.numel()), _stream()))
+    return out
+
+
 class FusedLlamaStep:
     """Decode step of a Hugging Face ``LlamaForCausalLM`` over its ``StaticCache``.
 
@@ -98,7 +132,25 @@ class FusedLlamaStep:
     sequence; the caller advances ``seq_lens`` between steps.  Nothing is allocated inside
     ``step``: it can be captured into a CUDA graph."""
 
-    def __init__(self, model, cache, attention, seq_lens: torch.Tensor, cache_len: int):
+    PROJECTIONS = ("w_qkv", "w_o", "w_gu", "w_down", "lm_head")
+
+    def __init__(self, model, cache, attention, seq_lens: torch.Tensor, cache_len: int,
+                 own_gemm: Optional[str] = None):
+        # own_gemm: which projections run on this library's GEMM kernel instead of torch.mm
+        # (cuBLAS): "all", "none" or a comma-separated subset of PROJECTIONS.  None reads
+        # INTERATTN_B200_LLAMA_GEMM, default "none" (see _linear).  Batches above 32 rows always
+        # use torch.mm.
+        import os
+        if own_gemm is None:
+            own_gemm = os.environ.get("INTERATTN_B200_LLAMA_GEMM", "none")
+        if own_gemm == "all":
+            own = set(self.PROJECTIONS)
+        elif own_gemm in ("none", "cublas", ""):
+            own = set()
+        else:
+            own = {name.strip() for name in own_gemm.split(",")}
+            if not own <= set(self.PROJECTIONS):
+                raise ValueError(f"own_gemm names must come from {self.PROJECTIONS}")
         cfg = model.config
         if getattr(cfg, "attention_bias", False) or getattr(cfg, "mlp_bias", False):
             raise ValueError("projection biases are not supported")
@@ -133,6 +185,26 @@ class FusedLlamaStep:
         self.qkv, self.q = new(b, (self.hq + 2 * self.hkv) * self.d), new(b, self.hq, self.d)
         self.gu, self.act = new(b, 2 * inter), new(b, inter)
         self.logits = new(b, int(self.lm_head.shape[0]))
+        self.own_gemm = set() if b > 32 else own
+        self.gemm_ws = None
+        if self.own_gemm:   # pack the chosen projections once (their concatenated copies are then dropped)
+            self.gemm_ws = gemm_workspace(int(self.lm_head.shape[0]), dev)
+            for L in self.layers:
+                for name in self.own_gemm - {"lm_head"}:
+                    L[name] = PackedWeight(L[name])
+            if "lm_head" in self.own_gemm:
+                self.lm_head = PackedWeight(self.lm_head)
+            torch.cuda.synchronize(dev)
+
+    def _linear(self, x: torch.Tensor, w, out: torch.Tensor) -> torch.Tensor:
+        """nn.Linear without bias.  Which kernel: back to back on its own, this library's kernel
+        matches cuBLAS at 32 rows and passes it on the widest shape (lm head, 6.6 against 6.5
+        TB/s); inside the captured Llama-3-8B step its longer start-up and partial-tile tail
+        cost about 7 us per projection (7.6 against 6.7 ms per step with every projection on
+        it), so cuBLAS is the default and the kernel is opt-in."""
+        if isinstance(w, PackedWeight):
+            return gemm(x, w, out, self.gemm_ws)
+        return torch.mm(x, w.t(), out=out)
 
     @torch.no_grad()
     def step(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -141,16 +213,16 @@ class FusedLlamaStep:
         delta = None
         for L, attn in zip(self.layers, self.attention):
             add_rmsnorm(self.x, delta, L["norm1"], self.eps, self.h)
-            torch.mm(self.h, L["w_qkv"].t(), out=self.qkv)
+            self._linear(self.h, L["w_qkv"], self.qkv)
             rope_append(self.qkv, self.cos, self.sin, self.seq_lens, L["k"], L["v"], self.q)
             ctx = attn.step(self.q)
-            torch.mm(ctx.view(b, self.hq * self.d), L["w_o"].t(), out=self.o)
+            self._linear(ctx.view(b, self.hq * self.d), L["w_o"], self.o)
             add_rmsnorm(self.x, self.o, L["norm2"], self.eps, self.h)
-            torch.mm(self.h, L["w_gu"].t(), out=self.gu)
+            self._linear(self.h, L["w_gu"], self.gu)
             silu_mul(self.gu, self.act)
-            torch.mm(self.act, L["w_down"].t(), out=self.down)
+            self._linear(self.act, L["w_down"], self.down)
             delta = self.down
         add_rmsnorm(self.x, delta, self.final_norm, self.eps, self.h)
-        torch.mm(self.h, self.lm_head.t(), out=self.logits)
+        self._linear(self.h, self.lm_head, self.logits)
         argmax(self.logits, tokens)
         return tokens

@@ -106,6 +106,26 @@ def test_argmax_lowest_index_wins():
     assert torch.equal(out2.cpu(), lo.argmax_first(odd))
 
 
+@pytest.mark.parametrize("m,n,k", [(32, 6144, 4096), (32, 4096, 14336), (32, 28672, 4096), (5, 512, 512),
+                                   (1, 1000, 72), (17, 130, 200), (32, 128256, 256)])
+def test_skinny_gemm(m, n, k):
+    ls = _step()
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).to(BF).to(DEV)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(BF).to(DEV)
+    ws = ls.gemm_workspace(n, DEV)
+    out = torch.full((m, n), float("nan"), dtype=BF, device=DEV)
+    packed = ls.PackedWeight(w)
+    ls.gemm(x, packed, out, ws)
+    want = x.float() @ w.float().t()                              # fp32 accumulate of the same bf16 inputs
+    err = (out.float() - want).abs()
+    assert bool((err <= 2.0 ** -8 * want.abs() + 1e-3).all()), float(err.max())
+    again = torch.empty_like(out)
+    ls.gemm(x, packed, again, ws)                                 # the workspace is reusable as left behind,
+    assert torch.equal(out, again)                                # and the result does not depend on timing
+    assert int(ws[: ((n + 127) // 128) * 4].view(torch.int32).abs().sum()) == 0
+
+
 def test_bad_arguments_raise():
     ls = _step()
     x = torch.zeros(2, 100, dtype=BF, device=DEV)               # hidden not a multiple of 8
@@ -115,10 +135,17 @@ def test_bad_arguments_raise():
         ls.silu_mul(torch.zeros(2, 64, device=DEV), torch.zeros(2, 32, device=DEV))   # fp32
     with pytest.raises(ValueError):
         ls.add_rmsnorm(x.cpu(), None, torch.ones(100, dtype=BF), 1e-5, torch.empty(2, 100, dtype=BF))
+    big = torch.zeros(33, 64, dtype=BF, device=DEV)               # more than 32 rows
+    with pytest.raises(ValueError):
+        ls.gemm(big, ls.PackedWeight(torch.zeros(128, 64, dtype=BF, device=DEV)),
+                torch.zeros(33, 128, dtype=BF, device=DEV), ls.gemm_workspace(128, DEV))
+    with pytest.raises(ValueError):                               # workspace too small
+        ls.gemm(big[:4], ls.PackedWeight(torch.zeros(128, 64, dtype=BF, device=DEV)),
+                torch.zeros(4, 128, dtype=BF, device=DEV), torch.zeros(16, dtype=torch.uint8, device=DEV))
 
 
-@pytest.mark.parametrize("graph", [False, True])
-def test_fused_step_matches_the_module_by_module_step(graph):
+@pytest.mark.parametrize("graph,own_gemm", [(False, "none"), (True, "none"), (False, "all"), (True, "w_down,lm_head")])
+def test_fused_step_matches_the_module_by_module_step(graph, own_gemm):
     """Same weights, same prompts, the same tokens fed at every step: the logits of the fused
     step follow those of the Hugging Face modules around the attention hook."""
     pytest.importorskip("transformers")
@@ -129,7 +156,7 @@ def test_fused_step_matches_the_module_by_module_step(graph):
     forced = torch.randint(0, 512, (batch, new_tokens), generator=torch.Generator().manual_seed(13)).to(DEV)
     kw = dict(block_size=block, top_k=top_k, force_tokens=forced, collect_logits=True)
     _, ref = llama_decode.generate_batched(model, ids, new_tokens, **kw)
-    _, got = llama_decode.generate_batched(model, ids, new_tokens, fused_step=True, **kw)
+    _, got = llama_decode.generate_batched(model, ids, new_tokens, fused_step=True, own_gemm=own_gemm, **kw)
     assert got["fused_step"] and not ref["fused_step"]
     a, b = ref["logits"].float(), got["logits"].float()
     assert a.shape == b.shape == (new_tokens - 1, batch, 512)
@@ -137,8 +164,8 @@ def test_fused_step_matches_the_module_by_module_step(graph):
     assert float((a - b).abs().max()) <= 0.03 * scale
     if graph:   # greedy tokens of the captured fused step == greedy tokens of the eager fused step
         t_eager, _ = llama_decode.generate_batched(model, ids, new_tokens, block_size=block, top_k=top_k,
-                                                   fused_step=True)
+                                                   fused_step=True, own_gemm=own_gemm)
         t_graph, st = llama_decode.generate_batched(model, ids, new_tokens, block_size=block, top_k=top_k,
-                                                    fused_step=True, cuda_graph=True)
+                                                    fused_step=True, own_gemm=own_gemm, cuda_graph=True)
         assert st["cuda_graph"] and st["fused_step"]
         assert torch.equal(t_eager, t_graph)
