@@ -57,6 +57,9 @@ def parse_args():
     ap.add_argument("--workload", default=WORKLOAD)
     ap.add_argument("--cpu-sample-seqs", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--llama-steps", type=int, default=48,
+                    help="greedy decode steps of the full Llama-3-8B-architecture model (batch 32, 8192-token "
+                         "prompts, random weights) timed after the layer-step, 1 GPU only; 0 skips it")
     ap.add_argument("--layer-pools", type=int, default=N_LAYER_POOLS,
                     help="KV pools rotated between steps (1 keeps a profiler capture small)")
     return ap.parse_args()
@@ -370,9 +373,33 @@ def run_gpu_arm(args):
                 "value": n / dt, "unit": UNIT, "cores": cores, "kind": "port",
                 "sample": f"{n} of {cfg.batch} sequences, one layer-step x {reps}: score + top-k + sparse "
                           f"attention ({dt:.2f} s per step), summaries excluded"}
+        if args.llama_steps > 1 and world == 1 and args.workload == WORKLOAD:
+            line["llama_decode"] = llama_decode_line(args.llama_steps)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def llama_decode_line(steps):
+    """Second figure of the metric: decode tokens/s of the whole Llama-3-8B-architecture model
+    (32 layers, random bf16 weights, batch 32, 8192 uniform-random prompt ids, block 64, top-64
+    in every layer) through the fused decode step captured in a CUDA graph."""
+    import torch
+    try:
+        from interattn_b200 import llama_decode as ld
+        torch.cuda.empty_cache()
+        model = ld.build_random_llama("llama3-8b")
+        g = torch.Generator(device="cuda").manual_seed(0)
+        ids = torch.randint(0, model.config.vocab_size, (32, 8192), generator=g, device="cuda")
+        _, st = ld.generate_batched(model, ids, int(steps), cuda_graph=True, fused_step=True)
+        return {"metric": "llama3_8b_decode_tokens_per_s", "value": st["tokens_per_s"], "unit": "tok/s",
+                "ms_per_decode_step": 1e3 * st["decode_s"] / max(st["decode_steps_timed"], 1),
+                "decode_steps_timed": st["decode_steps_timed"], "prefill_s": st["prefill_s"],
+                "config": {"layers": 32, "batch": 32, "prompt": 8192, "block": 64, "top_k": 64, "dtype": "bf16",
+                           "cuda_graph": True, "fused_step": True, "weights": "random init",
+                           "data": "uniform random token ids"}}
+    except Exception as e:   # the layer-step line above must still be printed
+        return {"metric": "llama3_8b_decode_tokens_per_s", "error": f"{type(e).__name__}: {e}"[:300]}
 
 
 def run_split_kv_arm(args):
