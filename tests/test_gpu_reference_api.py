@@ -332,3 +332,53 @@ def test_generate_condition_block_cached_matches_oracle_greedy_tokens():
     with pytest.raises(ValueError):
         api.generate_condition_block_cached(model=gpu_model, tokenizer=None, input_ids=ids.repeat(2, 1).to(DEV),
                                             attention_mask=None, method=method, device=DEV)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 3e-2)])
+def test_factory_attention_module_prefills_densely_and_decodes_sparsely(dtype, tol):
+    """attention_factory seam: forward(x[B, T, C]) -> y[B, T, C]; with every block selected a decode
+    step equals dense causal attention of the last position, with top-2 it equals the oracle."""
+    from types import SimpleNamespace
+    from interattn_b200 import caller_surface as cs
+    torch.manual_seed(21)
+    cfg = SimpleNamespace(attn=SimpleNamespace(type=cs.ATTN_TYPE, select_block=64, top_k=64), n_embd=256, n_head=4,
+                          n_kv_head=2, bias=False, block_size=512)
+    mod = cs.create_attention(cfg, layer_index=0).to(DEV).to(dtype)
+    b, t = 2, 300
+    x = torch.randn(b, t + 1, 256, device=DEV, dtype=dtype)
+    y_prefill = mod(x[:, :t])
+    assert y_prefill.shape == (b, t, 256)
+    y_step = mod(x[:, t:t + 1])
+    assert y_step.shape == (b, 1, 256)
+    mod.reset_cache()
+    y_full = mod(x)                                       # dense causal attention over all T + 1 tokens
+    assert torch.allclose(y_prefill.float(), y_full[:, :t].float(), atol=tol, rtol=tol)
+    assert torch.allclose(y_step.float(), y_full[:, t:].float(), atol=tol, rtol=tol)
+    # top-2 of the 5 prompt blocks: the selection must be what the oracle selects on the same K
+    mod.reset_cache()
+    mod.top_k = 2
+    mod(x[:, :t])
+    y_sparse = mod(x[:, t:t + 1])
+    st = mod._state
+    idx = st["step"].sel_idx.cpu()
+    assert int(st["step"].sel_count.min()) == 2 and idx.shape[-1] >= 2
+    assert not torch.allclose(y_sparse.float(), y_full[:, t:].float(), atol=tol, rtol=tol)
+
+
+def test_generate_with_method_kind_b200_batch_1_and_batched():
+    pytest.importorskip("transformers")
+    from types import SimpleNamespace
+    from interattn_b200 import caller_surface as cs, llama_decode
+    api = _api()
+    model = llama_decode.build_random_llama("tiny", dtype=torch.float32, device=DEV, seed=5)
+    ids = torch.randint(0, 512, (3, 200), generator=torch.Generator().manual_seed(6)).to(DEV)
+    method = SimpleNamespace(kind=cs.METHOD_KIND, condition_delta_mode="range_bound", max_new_tokens=6,
+                             full_attention_layers=0, condition_block_size=64, condition_eps=0.0, condition_top_k=2,
+                             condition_rep_mode="sparse_only")
+    one, meta1 = cs.generate_with_method(model, None, ids[:1], torch.ones_like(ids[:1]), method, DEV)
+    want, _ = api.generate_condition_block_cached(model=model, tokenizer=None, input_ids=ids[:1],
+                                                  attention_mask=torch.ones_like(ids[:1]), method=method, device=DEV)
+    assert torch.equal(one, want)
+    many, meta = cs.generate_with_method(model, None, ids, torch.ones_like(ids), method, DEV)
+    assert many.shape == (3, 6) and meta["batched"] and meta["method"] == cs.METHOD_KIND
+    assert torch.equal(many[:1], one)
