@@ -58,6 +58,11 @@ typedef enum ia_status {
 
 typedef enum ia_dtype { IA_F32 = 0, IA_BF16 = 1 } ia_dtype;
 typedef enum ia_select_mode { IA_SELECT_TOPK = 0, IA_SELECT_EPS = 1 } ia_select_mode;
+/* Score variant, OR-ed into the mode argument: the first term of the block score becomes
+ * 2 b_all softmax(z + delta) instead of 2 b_all softmax(z) (cosh(delta) - 1) / sum(softmax(z) cosh(delta)) -
+ * the reference's term1_mass_exp (IMPL/core.py:798-803 and 893-896;
+ * GEN/methods/condition_block_triton_term1_softmax.py). */
+#define IA_SELECT_TERM1_MASS_EXP 0x100
 typedef enum ia_rep_mode {
   IA_REP_SPARSE_ONLY = 0, /* selected blocks + suffix */
   IA_REP_HYBRID = 1       /* + one (z, v_bar) representative per unselected block */

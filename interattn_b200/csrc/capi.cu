@@ -155,7 +155,10 @@ int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefi
   if (int s = check_geom(geom)) return s;
   if (int s = check_summaries(summaries)) return s;
   if (!q || !prefix_lens || !sel_idx || !sel_count) return fail(IA_ERR_BAD_ARG, "select: null argument");
-  if (mode != IA_SELECT_TOPK && mode != IA_SELECT_EPS) return fail(IA_ERR_BAD_ARG, "select: mode %d", mode);
+  const int full_mode = mode;
+  mode &= 0xff;  // the high bits carry the score variant (IA_SELECT_TERM1_MASS_EXP)
+  if ((mode != IA_SELECT_TOPK && mode != IA_SELECT_EPS) || (full_mode & ~(0xff | IA_SELECT_TERM1_MASS_EXP)))
+    return fail(IA_ERR_BAD_ARG, "select: mode %d", full_mode);
   if (max_sel <= 0) return fail(IA_ERR_BAD_ARG, "select: max_sel %d", max_sel);
   if (mode == IA_SELECT_TOPK && (top_k < 0 || top_k > max_sel))
     return fail(IA_ERR_BAD_ARG, "select: top_k %d outside [0, max_sel %d]", top_k, max_sel);
@@ -163,7 +166,7 @@ int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefi
     return fail(IA_ERR_BAD_ARG, "select: epsilon mode may keep every block: max_sel %d < max_blocks %d", max_sel,
                 geom->max_blocks);
   ia_select_aux none{};
-  return launch_select(q, *summaries, prefix_lens, *geom, mode, top_k, eps, max_sel, sel_idx, sel_count,
+  return launch_select(q, *summaries, prefix_lens, *geom, full_mode, top_k, eps, max_sel, sel_idx, sel_count,
                        aux ? *aux : none, nullptr, (cudaStream_t)stream);
 }
 
@@ -274,7 +277,10 @@ static int decode_attention_impl(const void* q, const void* k_pool, const void* 
     return fail(IA_ERR_BAD_ARG, "decode_attention: null argument");
   if (!aligned16(k_pool) || !aligned16(v_pool) || !aligned16(q))
     return fail(IA_ERR_BAD_ARG, "decode_attention: q and pools must be 16-byte aligned");
-  if (mode != IA_SELECT_TOPK && mode != IA_SELECT_EPS) return fail(IA_ERR_BAD_ARG, "decode_attention: mode %d", mode);
+  const int full_mode = mode;
+  mode &= 0xff;  // the high bits carry the score variant (IA_SELECT_TERM1_MASS_EXP)
+  if ((mode != IA_SELECT_TOPK && mode != IA_SELECT_EPS) || (full_mode & ~(0xff | IA_SELECT_TERM1_MASS_EXP)))
+    return fail(IA_ERR_BAD_ARG, "decode_attention: mode %d", full_mode);
   if (mode == IA_SELECT_TOPK && (top_k < 0 || top_k > max_sel))
     return fail(IA_ERR_BAD_ARG, "decode_attention: top_k %d outside [0, max_sel %d]", top_k, max_sel);
   if (mode == IA_SELECT_EPS && max_sel < geom->max_blocks)
@@ -284,7 +290,7 @@ static int decode_attention_impl(const void* q, const void* k_pool, const void* 
     return fail(IA_ERR_BAD_ARG, "decode_attention: rep_mode %d", rep_mode);
   if (n_splits > 64) return fail(IA_ERR_BAD_ARG, "decode_attention: n_splits %d outside [1, 64]", n_splits);
   mark(0);
-  if (int s = launch_select(q, *summaries, prefix_lens, *geom, mode, top_k, eps, max_sel, idx, cnt, aux,
+  if (int s = launch_select(q, *summaries, prefix_lens, *geom, full_mode, top_k, eps, max_sel, idx, cnt, aux,
                             w.split_counters, st))
     return s;
   mark(1);

@@ -101,6 +101,7 @@ struct SelectParams {
   const int32_t* prefix_lens;
   int n_kv_heads, max_blocks, block_size;
   int mode, top_k, max_sel;
+  int mass_exp;  // score variant: first term 2 b_all softmax(z + delta) (IA_SELECT_TERM1_MASS_EXP)
   float eps;
   int32_t* sel_idx;
   int32_t* sel_count;
@@ -199,10 +200,12 @@ __device__ __forceinline__ void norm_merge(RowNorm& a, float bm, float bl, float
 }
 // What the score needs from delta, and the block's contribution to the normalisers:
 //   A = cosh(delta) - 1,  th = tanh(delta / 2)
-__device__ __forceinline__ void delta_terms(float delta, float& ch, float& a_term, float& th) {
+// With mass_exp the first term is 2 b_all softmax(z + delta) (IMPL/core.py:798-803, 893-896):
+// e^delta takes the place of cosh(delta) in the normaliser and of cosh(delta) - 1 in the term.
+__device__ __forceinline__ void delta_terms(float delta, int mass_exp, float& ch, float& a_term, float& th) {
   const float e = expf(delta);
-  ch = 0.5f * (e + 1.f / e);
-  a_term = ch - 1.f;
+  ch = mass_exp ? e : 0.5f * (e + 1.f / e);
+  a_term = mass_exp ? e : ch - 1.f;
   th = 1.f - 2.f / (e + 1.f);
 }
 
@@ -498,7 +501,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           const float delta = fmaxf(fabsf(upper - s), fabsf(lower - s));
           const float z = (count == p.block_size ? log_full : logf((float)count)) + s;
           float ch, a_term, th;
-          delta_terms(delta, ch, a_term, th);
+          delta_terms(delta, p.mass_exp, ch, a_term, th);
           norm_absorb(acc, z, ch);
           z_s[g * nbl + b - b_lo] = z;
           a_s[g * nbl + b - b_lo] = a_term;
@@ -637,7 +640,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           const float delta = fmaxf(fabsf(upper - s), fabsf(lower - s));
           const float z = logc + s;
           float ch, a_term, th;
-          delta_terms(delta, ch, a_term, th);
+          delta_terms(delta, p.mass_exp, ch, a_term, th);
           norm_absorb(rn[g / kGroupWarps], z, ch);
           z_s[g * nbl + b - b_lo] = z;
           a_s[g * nbl + b - b_lo] = a_term;
@@ -1003,7 +1006,8 @@ int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_le
   p.q = q; p.k_bar = s.k_bar; p.k_max = s.k_max; p.k_min = s.k_min; p.v_norm_max = s.v_norm_max;
   p.prefix_lens = prefix_lens;
   p.n_kv_heads = g.n_kv_heads; p.max_blocks = g.max_blocks; p.block_size = g.block_size;
-  p.mode = mode; p.top_k = top_k; p.max_sel = max_sel; p.eps = eps;
+  p.mode = mode & 0xff; p.mass_exp = (mode & IA_SELECT_TERM1_MASS_EXP) != 0;
+  p.top_k = top_k; p.max_sel = max_sel; p.eps = eps;
   p.sel_idx = sel_idx; p.sel_count = sel_count; p.aux = aux; p.split_counters = split_counters;
   const int n_pairs = g.batch * g.n_kv_heads;
   if (n_pairs <= 0) return IA_OK;

@@ -173,9 +173,12 @@ def select_blocks(
     q: torch.Tensor, summ: BlockSummaries, prefix_lens: torch.Tensor, *,
     top_k: Optional[int] = None, eps: Optional[float] = None, max_sel: Optional[int] = None,
     want: Sequence[str] = (), out_idx: Optional[torch.Tensor] = None, out_count: Optional[torch.Tensor] = None,
-    aux_buffers: Optional[Dict[str, torch.Tensor]] = None,
+    aux_buffers: Optional[Dict[str, torch.Tensor]] = None, term1_mass_exp: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor, Dict[str, torch.Tensor]]:
     """Score every block and route.
+
+    ``term1_mass_exp`` switches the first term of the score to ``2 b_all softmax(z + delta)``
+    (the reference's variant of the same name, ``core.py:798-803``).
 
     Exactly one of ``top_k`` (k best blocks per (sequence, kv head); ties go to
     the lower block index) and ``eps`` (the reference rule ``score > eps``) is
@@ -195,6 +198,8 @@ def select_blocks(
     if max_sel is None:
         max_sel = int(top_k) if mode == IA_SELECT_TOPK else nb
         max_sel = max(max_sel, 1)
+    if term1_mass_exp:
+        mode |= _lib.IA_SELECT_TERM1_MASS_EXP
     rows = hkv * group
     dev = q.device
     idx = out_idx if out_idx is not None else torch.empty((b, hkv, max_sel), device=dev, dtype=torch.int32)
@@ -295,7 +300,8 @@ class DecodeAttention:
 
     def __init__(self, kv: PagedKV, summ: BlockSummaries, n_q_heads: int, *, top_k: Optional[int] = None,
                  eps: Optional[float] = None, rep_mode: str = "sparse_only", n_splits: Optional[int] = None,
-                 max_sel: Optional[int] = None, expected_blocks: Optional[int] = None):
+                 max_sel: Optional[int] = None, expected_blocks: Optional[int] = None,
+                 term1_mass_exp: bool = False):
         self.lib = _lib.load()
         if (top_k is None) == (eps is None):
             raise ValueError("give exactly one of top_k and eps")
@@ -306,6 +312,8 @@ class DecodeAttention:
         self.kv, self.summ = kv, summ
         self.group = n_q_heads // kv.n_kv_heads
         self.mode = IA_SELECT_TOPK if top_k is not None else IA_SELECT_EPS
+        if term1_mass_exp:
+            self.mode |= _lib.IA_SELECT_TERM1_MASS_EXP
         self.top_k, self.eps = int(top_k or 0), float(eps or 0.0)
         nb = summ.max_blocks
         self.max_sel = int(max_sel) if max_sel is not None else (max(self.top_k, 1) if top_k is not None else nb)

@@ -207,9 +207,8 @@ def _run_condition_block_selection_stats(q_grouped, prefix, workspace=None, redu
     """-> (q [rows,D], s_cache [rows,nb], delta_cache [rows,nb], partial [4,rows,1],
     global_stats [4,rows] | None, n_blocks, n_chunks).  The kernel normalises in
     one piece, so there is a single chunk and ``partial`` equals the globals:
-    (z_m, z_l) and a pair (c_m, c_l) with c_l e^{c_m} = sum_b e^{z_b} cosh(delta_b)."""
-    if term1_mass_exp:
-        raise ValueError("the term1-softmax score variant is not built")
+    (z_m, z_l) and a pair (c_m, c_l) with c_l e^{c_m} = sum_b e^{z_b} cosh(delta_b)
+    (e^{delta_b} in place of the cosh with ``term1_mass_exp``)."""
     h = _handle(prefix)
     hkv, d = int(h.k_all.shape[0]), int(h.k_all.shape[2])
     group, q = _check_q(q_grouped.to(h.k_all.dtype), hkv, d)
@@ -224,7 +223,7 @@ def _run_condition_block_selection_stats(q_grouped, prefix, workspace=None, redu
             ws["b200_" + name] = t
         bufs[name] = t
     ops.select_blocks(q, h.summ, h.geometry.prefix_lens, eps=float("inf"), max_sel=max(nb, 1),
-                      want=("s", "delta", "globals"), aux_buffers=bufs)
+                      want=("s", "delta", "globals"), aux_buffers=bufs, term1_mass_exp=bool(term1_mass_exp))
     globals_ = bufs["globals"][0]
     partial = globals_.reshape(4, rows, 1)
     return (q[0], bufs["s"][0], bufs["delta"][0], partial, globals_ if reduce_globals else None, nb, 1)
@@ -280,8 +279,6 @@ def _condition_block_decode_output_fused_triton(
     current full cache explicitly (a dynamic cache is re-allocated every step).
     Any other suffix tensor is supported through a slow path that copies prefix
     and suffix into one contiguous cache first."""
-    if term1_mass_exp:
-        raise ValueError("the term1-softmax score variant is not built")
     if rep_mode not in _REP:
         raise ValueError(f"rep_mode must be one of {sorted(_REP)}")
     lib = _lib.load()
@@ -308,6 +305,8 @@ def _condition_block_decode_output_fused_triton(
     torch.add(geo.prefix_lens, suffix_len_dev.reshape(1).to(torch.int32), out=geo.seq_lens)
 
     mode = IA_SELECT_TOPK if top_k is not None else IA_SELECT_EPS
+    if term1_mass_exp:
+        mode |= _lib.IA_SELECT_TERM1_MASS_EXP
     max_sel = max(nb, 1)
     g = geo.geom(k_all, group, h.block_size, nb)
     ws_dict = workspace if workspace is not None else {}
@@ -366,8 +365,7 @@ class ConditionBlockDecodeRunner:
     def __init__(self, *, model=None, model_config=None, layer_idx_list=None, full_attention_layers=0,
                  block_size=64, eps=0.0, prompt_len, pos=None, prompt_prefix_cache=None, term1_mass_exp=False,
                  top_k: Optional[int] = None, rep_mode: str = "hybrid", device=None):
-        if term1_mass_exp:
-            raise ValueError("the term1-softmax score variant is not built")
+        self.term1_mass_exp = bool(term1_mass_exp)
         self.model_config = model_config
         self.module_to_layer_idx = {}
         if model is not None:
@@ -421,7 +419,7 @@ class ConditionBlockDecodeRunner:
             v_suffix=v_all[:, self.prompt_len:], suffix_len_dev=self.suffix_len_dev, eps=self.eps,
             page_size=self.block_size, store_selected=False, output_dtype=query.dtype,
             workspace=self.workspace_by_layer.setdefault(int(layer_idx), {}), top_k=self.top_k,
-            rep_mode=self.rep_mode, kv_cache=(k_all, v_all))
+            rep_mode=self.rep_mode, kv_cache=(k_all, v_all), term1_mass_exp=self.term1_mass_exp)
         out = out.reshape(n_heads, 1, d).permute(1, 0, 2).unsqueeze(0)
         return out.to(query.dtype), None
 
@@ -441,8 +439,6 @@ def generate_condition_block_cached(*, model, tokenizer, input_ids, attention_ma
         raise ValueError("condition_block only supports delta_mode='range_bound'.")
     if int(input_ids.shape[0]) != 1:
         raise ValueError("condition_block generate currently expects batch_size=1.")
-    if term1_mass_exp:
-        raise ValueError("the term1-softmax score variant is not built")
     prompt_len = int(input_ids.shape[1])
     budget = int(method.max_new_tokens)
     meta = {"method": "condition_block_b200", "prompt_len": prompt_len, "decode_steps": 0}
@@ -461,7 +457,8 @@ def generate_condition_block_cached(*, model, tokenizer, input_ids, attention_ma
     runner = ConditionBlockDecodeRunner(
         model=model, model_config=model.config, full_attention_layers=method.full_attention_layers,
         block_size=method.condition_block_size, eps=method.condition_eps, prompt_len=prompt_len,
-        top_k=getattr(method, "condition_top_k", None), rep_mode=getattr(method, "condition_rep_mode", "hybrid"))
+        top_k=getattr(method, "condition_top_k", None), rep_mode=getattr(method, "condition_rep_mode", "hybrid"),
+        term1_mass_exp=term1_mass_exp)
     total = prompt_len + 1
     with condition_block_decode_context(runner):
         while len(tokens) < budget and int(token) not in stop:

@@ -31,6 +31,9 @@ Parity status: pinned.  ``tests/test_oracle_vs_reference.py`` checks these
 functions against the reference's own functions when the reference tree is
 importable, and ``tests/test_oracle_golden.py`` checks them against vectors
 produced by the reference and committed under ``tests/golden/``.
+One exception - parity unpinned: the ``term1_mass_exp`` branch of
+``score_from_stats`` restates a variant the reference has only as a Triton
+kernel (IMPL/core.py:798-803, 893-896), which cannot run where the pins run.
 
 The reference handles one sequence at a time; so does every function here
 (``*_batch`` helpers loop).  Physical paging is not a reference concept: pages
@@ -143,9 +146,21 @@ def block_summaries(
 # condition score
 # --------------------------------------------------------------------------
 
-def score_from_stats(p: torch.Tensor, delta: torch.Tensor, b_c: torch.Tensor, b_all: torch.Tensor) -> torch.Tensor:
+def score_from_stats(p: torch.Tensor, delta: torch.Tensor, b_c: torch.Tensor, b_all: torch.Tensor,
+                     term1_mass_exp: bool = False) -> torch.Tensor:
     """Two-term block condition given softmax mass p, range bound delta and the
-    value-norm bounds (per block b_c, global b_all)."""
+    value-norm bounds (per block b_c, global b_all).
+
+    ``term1_mass_exp``: the first term is ``2 b_all softmax(z + delta)`` - the variant the
+    reference has only as a Triton kernel (core.py:798-803 forms ``zc = z + delta``,
+    core.py:893-896 ``term1 = 2 b_all exp(z + delta - c_m) / c_l``), restated here from those
+    lines; no CPU implementation of it exists in the reference, so this variant's parity is
+    unpinned."""
+    if term1_mass_exp:
+        e = torch.exp(delta)
+        norm = (p * e).sum(dim=-1).clamp_min(1e-30)
+        first = 2.0 * b_all.unsqueeze(-1) * e / norm.unsqueeze(-1)
+        return p * (first + 2.0 * b_c * torch.tanh(delta / 2.0))
     ch = torch.cosh(delta)
     norm = (p * ch).sum(dim=-1).clamp_min(1e-30)
     first = 2.0 * b_all.unsqueeze(-1) * (ch - 1.0) / norm.unsqueeze(-1)
@@ -153,7 +168,7 @@ def score_from_stats(p: torch.Tensor, delta: torch.Tensor, b_c: torch.Tensor, b_
     return p * (first + second)
 
 
-def condition_terms(q_grouped: torch.Tensor, summ: Summaries) -> Dict[str, torch.Tensor]:
+def condition_terms(q_grouped: torch.Tensor, summ: Summaries, term1_mass_exp: bool = False) -> Dict[str, torch.Tensor]:
     """q_grouped [Hkv, G, D] -> per-row and per-head quantities of the score.
 
     Returns ``s`` (q.k_bar/sqrt(D)), ``delta`` (range bound), ``z`` (s + log
@@ -182,7 +197,7 @@ def condition_terms(q_grouped: torch.Tensor, summ: Summaries) -> Dict[str, torch
     z = torch.log(summ.counts.clamp_min(1).float()).view(1, 1, -1) + s
     z = z.masked_fill(~exists, float("-inf"))
     p = torch.softmax(z, dim=-1)
-    cond = score_from_stats(p, delta, b_c, b_all)
+    cond = score_from_stats(p, delta, b_c, b_all, term1_mass_exp)
     return {"s": s, "delta": delta, "z": z, "p": p, "cond": cond, "score": cond.mean(dim=1)}
 
 

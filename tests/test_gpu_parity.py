@@ -109,6 +109,37 @@ def test_topk_indices_bit_exact(bundle):
                 f"{rank_gap(terms['score'][h], len(want)):.3e}")
 
 
+def test_term1_mass_exp_variant(bundle):
+    """Score variant with the first term 2 b_all softmax(z + delta): scores, top-k indices and the
+    one-call step against the oracle's restatement of the variant.  The query is scaled down so that
+    delta is small - for large delta the two forms of the first term coincide."""
+    ops = _ops()
+    cfg, case, q, kv, summ = bundle
+    q = (q.float() * 0.04).to(q.dtype)
+    idx, cnt, aux = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, want=("score",),
+                                      term1_mass_exp=True)
+    plain = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, want=("score",))[2]["score"]
+    idx, cnt = idx.cpu(), cnt.cpu()
+    differs = False
+    for b in range(cfg.batch):
+        plen = int(case["prefix_lens"][b])
+        osum = oracle_summaries_from_gpu(summ, b, plen)
+        qg = q[b].cpu().reshape(cfg.n_kv_heads, cfg.group_size, cfg.head_dim).float()
+        terms = orc.condition_terms(qg, osum, term1_mass_exp=True)
+        ranked, _ = orc.select_topk(terms["score"], osum.counts, cfg.top_k)
+        nb = osum.n_blocks
+        score = aux["score"][b, :, :nb].cpu()
+        assert torch.allclose(score, terms["score"], rtol=2e-4, atol=1e-8)
+        differs |= not torch.allclose(score, plain[b, :, :nb].cpu(), rtol=1e-2, atol=1e-8)
+        for h in range(cfg.n_kv_heads):
+            n = int(cnt[b, h])
+            assert idx[b, h, :n].tolist() == sorted(ranked[h])
+    assert differs, "the variant must change the score"
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, term1_mass_exp=True)
+    step.step(q)
+    assert torch.equal(step.sel_idx.cpu()[:, :, :idx.shape[2]], idx)
+
+
 def test_eps_selection(bundle):
     ops = _ops()
     cfg, case, q, kv, summ = bundle

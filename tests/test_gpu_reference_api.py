@@ -105,8 +105,12 @@ def test_select_and_stats_shims():
     gl = glob.cpu().double()
     assert torch.allclose(gl[0] + torch.log(gl[1]), lse_z, rtol=1e-5, atol=1e-5)
     assert torch.allclose(gl[2] + torch.log(gl[3]), lse_c, rtol=1e-5, atol=1e-4)
-    with pytest.raises(ValueError):
-        api._run_condition_block_selection_stats(q.to(DEV), prefix, term1_mass_exp=True)
+    # the term1-softmax variant: same s / delta, the second normaliser pair sums e^{z + delta}
+    _, s2, d2, _, glob2, _, _ = api._run_condition_block_selection_stats(q.to(DEV), prefix, term1_mass_exp=True)
+    assert torch.equal(s2, s_cache) and torch.equal(d2, d_cache)
+    gl2 = glob2.cpu().double()
+    lse_e = torch.logsumexp(z + terms["delta"].reshape(hkv * g, nb).double(), dim=1)
+    assert torch.allclose(gl2[2] + torch.log(gl2[3]), lse_e, rtol=1e-5, atol=1e-4)
     with pytest.raises(ValueError):
         api._select_prompt_blocks(q.to(DEV), {"k_bar": None}, 0.1)
 
