@@ -57,6 +57,7 @@ def parse_args():
     ap.add_argument("--workload", default=WORKLOAD)
     ap.add_argument("--cpu-sample-seqs", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="split-KV arm: launch the step eagerly")
     ap.add_argument("--llama-steps", type=int, default=48,
                     help="greedy decode steps of the full Llama-3-8B-architecture model (batch 32, 8192-token "
                          "prompts, random weights) timed after the layer-step, 1 GPU only; 0 skips it")
@@ -406,7 +407,9 @@ def run_split_kv_arm(args):
     """Long-context split-KV (strong scaling): the blocks of every sequence are cut
     into contiguous ranges, one per rank; every rank selects globally from the
     replicated summaries, attends over its range and the ranks all-gather (o, lse)
-    over NCCL before the merge.  A step is the whole exchange."""
+    over NCCL before the merge.  A step is the whole exchange: four launches with
+    preallocated buffers, captured per layer pool into a CUDA graph (the all-gather
+    included) unless --no-graph is given or the capture fails."""
     import torch
     import torch.distributed as dist
     from interattn_b200 import ops, partition
@@ -417,7 +420,8 @@ def run_split_kv_arm(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", device_id=device)
+    from datetime import timedelta
+    dist.init_process_group("nccl", device_id=device, timeout=timedelta(seconds=120))
     cfg = CONFIGS[args.workload]
     nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
     n_pools = max(1, args.layer_pools)
@@ -427,9 +431,35 @@ def run_split_kv_arm(args):
         summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb)
         g = torch.Generator(device=device).manual_seed(77 + l)
         q = torch.randn((cfg.batch, cfg.n_q_heads, cfg.head_dim), generator=g, device=device).to(cfg.torch_dtype)
-        steps_obj.append(partition.cuda_split_kv_step(q, kv, summ, top_k=cfg.top_k, rep_mode=args.rep_mode,
-                                                      n_splits=args.n_splits or 4))
+        step = partition.SplitKVDecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=args.rep_mode,
+                                                n_splits=args.n_splits or 4)
+        steps_obj.append((step, q))
     K, W = args.steps, args.warmup
+    for step, q in steps_obj:          # communicator set-up and first launches outside any capture
+        step.step(q)
+    torch.cuda.synchronize()
+    graphs = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for step, q in steps_obj:
+                    step.step(q)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graphs = []
+            for step, q in steps_obj:
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, capture_error_mode="thread_local"):
+                    step.step(q)
+                graphs.append(g_)
+        except Exception as e:   # every rank runs the same code, so every rank falls back together
+            print(f"[bench] graph capture of the split-KV step failed ({type(e).__name__}: {e}); running eagerly",
+                  file=sys.stderr, flush=True)
+            graphs = None
+    run_step = (lambda i: graphs[i % n_pools].replay()) if graphs is not None else (
+        lambda i: steps_obj[i % n_pools][0].step(steps_obj[i % n_pools][1]))
 
     def sync_all():
         torch.cuda.synchronize()
@@ -439,12 +469,12 @@ def run_split_kv_arm(args):
     sampler = ClockSampler(local_rank)
     sampler.start()
     for i in range(W):
-        steps_obj[i % n_pools].run(nb)
+        run_step(i)
     sync_all()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for i in range(K):
-        out = steps_obj[i % n_pools].run(nb)
+        run_step(i)
     t1.record()
     sync_all()
     clocks = sampler.stop()
@@ -458,10 +488,18 @@ def run_split_kv_arm(args):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "batch": cfg.batch, "context": max(cfg.prefix_lens),
                        "top_k": cfg.top_k, "rep_mode": args.rep_mode, "parallelism": f"split-kv x{world}",
-                       "exchange": "all_gather of (o, lse) partials, selection replicated"},
-            "us_per_layer": 1e3 * ms / K, "gpu_launches": 5 * K, "clocks": clocks,
+                       "exchange": "all_gather of (o, lse) partials, selection replicated",
+                       "cuda_graph": graphs is not None},
+            "us_per_layer": 1e3 * ms / K, "gpu_launches": 3 * K, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    if graphs is not None:
+        # the captured graphs hold the communicator's kernels; destroying the communicator under them
+        # did not return on two GPUs - drop the graphs, drain the device and leave without the teardown
+        del graphs, run_step
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
     dist.destroy_process_group()
 
 

@@ -170,6 +170,14 @@ int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, in
                 int head_dim, void* out, int out_dtype, float* out_lse, ia_stream_t stream);
 
 /* Scratch needed by ia_decode_attention, in bytes. */
+/* The merge after an all-gather of split-KV partials across GPUs (the reference runs on one
+ * GPU; its merge of chunk partials is the same arithmetic, IMPL/legacy.py:781-793).
+ * `gathered` holds n_ranks chunks, rank_stride floats apart; a chunk is what one rank's
+ * ia_sparse_decode wrote when its o_partial [n_rows, n_parts, head_dim] and lse_partial
+ * [n_rows, n_parts] are adjacent in one buffer (o first).  out [n_rows, head_dim]. */
+int ia_finalize_gathered(const float* gathered, int n_ranks, int64_t rank_stride, int n_rows, int n_parts,
+                         int head_dim, void* out, int out_dtype, ia_stream_t stream);
+
 int64_t ia_workspace_bytes(const ia_geom* geom, int max_sel, int n_splits, int rep_mode);
 
 /* A good n_splits for ia_sparse_decode / ia_decode_attention on the current

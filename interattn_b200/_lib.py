@@ -75,6 +75,7 @@ SIGNATURES = {
     "ia_decode_attention_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             POINTER(Summaries), POINTER(Geom), c_int, c_int, c_float, c_int, c_int,
                                             c_int, c_void_p, c_void_p]),
+    "ia_finalize_gathered": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "ia_llama_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
     "ia_llama_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int64, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),

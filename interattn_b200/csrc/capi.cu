@@ -204,6 +204,20 @@ int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, in
                          (cudaStream_t)stream);
 }
 
+int ia_finalize_gathered(const float* gathered, int n_ranks, int64_t rank_stride, int n_rows, int n_parts,
+                         int head_dim, void* out, int out_dtype, ia_stream_t stream) {
+  if (!gathered || !out) return fail(IA_ERR_BAD_ARG, "finalize_gathered: null argument");
+  if (n_ranks <= 0 || n_rows < 0 || n_parts <= 0 || head_dim <= 0)
+    return fail(IA_ERR_BAD_ARG, "finalize_gathered: %d ranks, %d rows, %d parts", n_ranks, n_rows, n_parts);
+  const int64_t chunk = (int64_t)n_rows * n_parts * (head_dim + 1);
+  if (rank_stride < chunk || rank_stride % 4 != 0)
+    return fail(IA_ERR_BAD_ARG, "finalize_gathered: rank stride %lld floats (at least %lld, a multiple of 4)",
+                (long long)rank_stride, (long long)chunk);
+  if (!aligned16(gathered)) return fail(IA_ERR_BAD_ARG, "finalize_gathered: the buffer must be 16-byte aligned");
+  return launch_finalize_groups(gathered, gathered + (int64_t)n_rows * n_parts * head_dim, n_rows, n_parts, n_ranks,
+                                rank_stride, head_dim, out, out_dtype, nullptr, (cudaStream_t)stream);
+}
+
 int64_t ia_workspace_bytes(const ia_geom* geom, int max_sel, int n_splits, int rep_mode) {
   if (check_geom(geom) != IA_OK || max_sel <= 0 || n_splits <= 0) return -1;
   return carve(*geom, max_sel, n_splits, rep_mode, nullptr).bytes;

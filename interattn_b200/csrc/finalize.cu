@@ -8,6 +8,10 @@
 // are all empty gives 0 (the reference clamps the denominator to 1e-30).
 // One warp per output row; the partials are a few hundred bytes per row, so
 // this kernel is launch-latency bound.
+//
+// The partials may come in n_groups chunks of the same shape, group_stride
+// floats apart (one chunk per GPU after an all-gather of the split-KV
+// partials): part (w, s) of a row is then chunk w's part s.
 #include "ia_common.cuh"
 
 namespace ia {
@@ -16,14 +20,16 @@ template <typename TOut, int D>
 __global__ void __launch_bounds__(128)
 condition_block_stage2_reduce_kernel(const float* __restrict__ o_partial,
                                      const float* __restrict__ lse_partial, int n_rows, int n_parts,
-                                     TOut* __restrict__ out, float* __restrict__ out_lse) {
+                                     int n_groups, int64_t group_stride, TOut* __restrict__ out,
+                                     float* __restrict__ out_lse) {
   constexpr int VEC = D / 32;
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   const float* lse = lse_partial + (int64_t)row * n_parts;
   float top = -INFINITY;
-  for (int s = lane; s < n_parts; s += 32) top = fmaxf(top, lse[s]);
+  for (int w = 0; w < n_groups; ++w)
+    for (int s = lane; s < n_parts; s += 32) top = fmaxf(top, lse[w * group_stride + s]);
   top = warp_max(top);
   const float ref = (top == -INFINITY) ? 0.f : top;
 
@@ -32,14 +38,15 @@ condition_block_stage2_reduce_kernel(const float* __restrict__ o_partial,
   for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
   float den = 0.f;
   const float* o = o_partial + (int64_t)row * n_parts * D + lane * VEC;
-  for (int s = 0; s < n_parts; ++s) {
-    const float w = expf(lse[s] - ref);  // exp(-inf) = 0 for an empty part
-    float v[VEC];
-    load_vec<VEC>(o + (int64_t)s * D, v);
-    den += w;
+  for (int g = 0; g < n_groups; ++g)
+    for (int s = 0; s < n_parts; ++s) {
+      const float w = expf(lse[g * group_stride + s] - ref);  // exp(-inf) = 0 for an empty part
+      float v[VEC];
+      load_vec<VEC>(o + g * group_stride + (int64_t)s * D, v);
+      den += w;
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(w, v[i], acc[i]);
-  }
+      for (int i = 0; i < VEC; ++i) acc[i] = fmaf(w, v[i], acc[i]);
+    }
   const float inv = 1.f / fmaxf(den, 1e-30f);
 #pragma unroll
   for (int i = 0; i < VEC; ++i) acc[i] *= inv;
@@ -48,24 +55,31 @@ condition_block_stage2_reduce_kernel(const float* __restrict__ o_partial,
 }
 
 template <typename TOut, int D>
-static int launch_typed(const float* o_partial, const float* lse_partial, int n_rows, int n_parts,
-                        void* out, float* out_lse, cudaStream_t stream) {
+static int launch_typed(const float* o_partial, const float* lse_partial, int n_rows, int n_parts, int n_groups,
+                        int64_t group_stride, void* out, float* out_lse, cudaStream_t stream) {
   const int warps = 4;
   const int grid = (n_rows + warps - 1) / warps;
   condition_block_stage2_reduce_kernel<TOut, D><<<grid, warps * 32, 0, stream>>>(
-      o_partial, lse_partial, n_rows, n_parts, static_cast<TOut*>(out), out_lse);
+      o_partial, lse_partial, n_rows, n_parts, n_groups, group_stride, static_cast<TOut*>(out), out_lse);
   return check_launch("condition_block_stage2_reduce_kernel");
 }
 
 int launch_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts,
                     int head_dim, void* out, int out_dtype, float* out_lse, cudaStream_t stream) {
+  return launch_finalize_groups(o_partial, lse_partial, n_rows, n_parts, 1, 0, head_dim, out, out_dtype, out_lse,
+                                stream);
+}
+
+int launch_finalize_groups(const float* o_partial, const float* lse_partial, int n_rows, int n_parts, int n_groups,
+                           int64_t group_stride, int head_dim, void* out, int out_dtype, float* out_lse,
+                           cudaStream_t stream) {
   if (n_rows <= 0) return IA_OK;
   if (out_dtype == IA_BF16) {
-    if (head_dim == 128) return launch_typed<__nv_bfloat16, 128>(o_partial, lse_partial, n_rows, n_parts, out, out_lse, stream);
-    if (head_dim == 64) return launch_typed<__nv_bfloat16, 64>(o_partial, lse_partial, n_rows, n_parts, out, out_lse, stream);
+    if (head_dim == 128) return launch_typed<__nv_bfloat16, 128>(o_partial, lse_partial, n_rows, n_parts, n_groups, group_stride, out, out_lse, stream);
+    if (head_dim == 64) return launch_typed<__nv_bfloat16, 64>(o_partial, lse_partial, n_rows, n_parts, n_groups, group_stride, out, out_lse, stream);
   } else if (out_dtype == IA_F32) {
-    if (head_dim == 128) return launch_typed<float, 128>(o_partial, lse_partial, n_rows, n_parts, out, out_lse, stream);
-    if (head_dim == 64) return launch_typed<float, 64>(o_partial, lse_partial, n_rows, n_parts, out, out_lse, stream);
+    if (head_dim == 128) return launch_typed<float, 128>(o_partial, lse_partial, n_rows, n_parts, n_groups, group_stride, out, out_lse, stream);
+    if (head_dim == 64) return launch_typed<float, 64>(o_partial, lse_partial, n_rows, n_parts, n_groups, group_stride, out, out_lse, stream);
   }
   return fail(IA_ERR_UNSUPPORTED, "finalize: head_dim %d / out dtype %d not built", head_dim, out_dtype);
 }

@@ -168,5 +168,9 @@ int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
                          float* o_partial, float* lse_partial, const FusedFinalize* fused, cudaStream_t stream);
 int launch_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts,
                     int head_dim, void* out, int out_dtype, float* out_lse, cudaStream_t stream);
+// the same merge over n_groups chunks of partials, group_stride floats apart (one chunk per GPU)
+int launch_finalize_groups(const float* o_partial, const float* lse_partial, int n_rows, int n_parts, int n_groups,
+                           int64_t group_stride, int head_dim, void* out, int out_dtype, float* out_lse,
+                           cudaStream_t stream);
 
 }  // namespace ia

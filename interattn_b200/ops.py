@@ -286,6 +286,23 @@ def finalize(o_partial: torch.Tensor, lse_partial: torch.Tensor, out_dtype: torc
     return (out, lse) if return_lse else out
 
 
+def finalize_gathered(gathered: torch.Tensor, n_ranks: int, rank_stride: int, n_rows: int, n_parts: int,
+                      head_dim: int, out: torch.Tensor) -> torch.Tensor:
+    """Merge the split-KV partials of ``n_ranks`` GPUs read in place from an all-gather buffer:
+    chunk ``w`` starts ``w * rank_stride`` floats in and holds ``o [n_rows, n_parts, head_dim]``
+    followed by ``lse [n_rows, n_parts]``.  ``out`` (``n_rows * head_dim`` elements) is written."""
+    _need_cuda(gathered, out)
+    if gathered.dtype != torch.float32 or not gathered.is_contiguous() or not out.is_contiguous():
+        raise ValueError("gathered is a contiguous float32 buffer, out a contiguous tensor")
+    if gathered.numel() < (n_ranks - 1) * rank_stride + n_rows * n_parts * (head_dim + 1):
+        raise ValueError("the gathered buffer is too small")
+    if out.numel() != n_rows * head_dim or out.dtype not in _DTYPES:
+        raise ValueError("out holds n_rows * head_dim float32 or bfloat16 elements")
+    check(_lib.load().ia_finalize_gathered(_ptr(gathered), int(n_ranks), int(rank_stride), int(n_rows), int(n_parts),
+                                           int(head_dim), _ptr(out), _DTYPES[out.dtype], _stream()))
+    return out
+
+
 class DecodeAttention:
     """One decode-attention layer-step behind a single call, with all scratch
     preallocated: selection -> sparse attention -> finalize.

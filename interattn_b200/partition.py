@@ -150,3 +150,58 @@ def cuda_split_kv_step(q, kv, summ, *, top_k=None, eps=None, rep_mode="sparse_on
         return ops.finalize(all_o, all_lse, out_dtype).reshape(q.shape)
 
     return SplitKVStep(select, attend, merge)
+
+
+class SplitKVDecodeAttention:
+    """One rank's split-KV layer-step with every buffer preallocated: four launches
+    (selection, attention over this rank's block range, one NCCL all-gather of the
+    partials, merge), nothing allocated per step, so the step can be captured into a
+    CUDA graph together with its collective.
+
+    ``kv`` needs valid pages only for this rank's block range (and the suffix on the
+    last rank); ``summ`` holds the summaries of all blocks (replicated), so every rank
+    computes the same global selection without an exchange.  The all-gather moves each
+    rank's split partials as they are (``[rows, n_splits, D]`` values and ``[rows,
+    n_splits]`` log-sum-exps, adjacent in one buffer) and the merge reads the gathered
+    chunks in place (``ia_finalize_gathered``)."""
+
+    def __init__(self, kv, summ, n_q_heads: int, *, top_k=None, eps=None, rep_mode: str = "sparse_only",
+                 n_splits: int = 4, group=None):
+        from . import ops
+        self.ops, self.kv, self.summ, self.group = ops, kv, summ, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.top_k, self.eps, self.rep_mode, self.n_splits = top_k, eps, rep_mode, int(n_splits)
+        nb = summ.max_blocks
+        self.block_range = plan_block_ranges(nb, self.world)[self.rank]
+        self.with_suffix = self.rank == self.world - 1
+        b, d = kv.batch, kv.head_dim
+        self.rows = b * int(n_q_heads)
+        dev = kv.k_pool.device
+        max_sel = max(int(top_k), 1) if top_k is not None else nb
+        self.sel_idx = torch.empty((b, kv.n_kv_heads, max_sel), device=dev, dtype=torch.int32)
+        self.sel_count = torch.empty((b, kv.n_kv_heads), device=dev, dtype=torch.int32)
+        self.aux = {}
+        if rep_mode == "hybrid":
+            self.aux["z"] = torch.full((b, int(n_q_heads), nb), float("-inf"), device=dev, dtype=torch.float32)
+        n_o = self.rows * self.n_splits * d
+        self.chunk = (n_o + self.rows * self.n_splits + 3) // 4 * 4          # floats per rank, 16-byte multiple
+        self.mine = torch.zeros((self.chunk,), device=dev, dtype=torch.float32)
+        self.o_part = self.mine[:n_o].view(b, int(n_q_heads), self.n_splits, d)
+        self.lse_part = self.mine[n_o:n_o + self.rows * self.n_splits].view(b, int(n_q_heads), self.n_splits)
+        self.gathered = torch.empty((self.world * self.chunk,), device=dev, dtype=torch.float32)
+        self.out = torch.empty((b, int(n_q_heads), d), device=dev, dtype=kv.k_pool.dtype)
+        self.n_q_heads = int(n_q_heads)
+
+    def step(self, q: torch.Tensor) -> torch.Tensor:
+        ops = self.ops
+        kw = dict(top_k=self.top_k) if self.top_k is not None else dict(eps=self.eps)
+        ops.select_blocks(q, self.summ, self.kv.prefix_lens, out_idx=self.sel_idx, out_count=self.sel_count,
+                          max_sel=int(self.sel_idx.shape[-1]), want=tuple(self.aux), aux_buffers=self.aux, **kw)
+        ops.sparse_decode(q, self.kv, self.sel_idx, self.sel_count, block_size=self.summ.block_size,
+                          max_blocks=self.summ.max_blocks, rep_mode=self.rep_mode, summ=self.summ,
+                          z=self.aux.get("z"), n_splits=self.n_splits, block_range=self.block_range,
+                          with_suffix=self.with_suffix, out=(self.o_part, self.lse_part))
+        dist.all_gather_into_tensor(self.gathered, self.mine, group=self.group)
+        ops.finalize_gathered(self.gathered, self.world, self.chunk, self.rows, self.n_splits, self.kv.head_dim,
+                              self.out)
+        return self.out

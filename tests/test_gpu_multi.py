@@ -1,10 +1,12 @@
 """Split-KV across real GPUs (one process per GPU, NCCL): every rank holds only
 the K/V pages of its own block range, selects globally from replicated
 summaries, attends over its share and all-gathers (o, lse); the merged output
-must equal the single-GPU layer-step.  Skipped on boxes with one GPU."""
+must equal the single-GPU layer-step.  The multi-rank tests are skipped on boxes with
+one GPU; the same code runs there as a process group of one rank."""
 
 import os
 import socket
+from datetime import timedelta
 
 import pytest
 import torch
@@ -25,7 +27,8 @@ def _rank_main(rank, world, port, rep_mode, result_path):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    # a short collective timeout: a rank that failed must not leave the others waiting for the job's limit
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=timedelta(seconds=90))
     try:
         cfg = scaled(CONFIGS["cfg4_longctx_128k"], batch=2, max_len=6000, suffix=11, top_k=12)
         case = make_case(cfg)
@@ -59,12 +62,39 @@ def _rank_main(rank, world, port, rep_mode, result_path):
         torch.cuda.synchronize()
         ok = bool(torch.isfinite(out.float()).all())
         ok = ok and torch.allclose(out.float(), whole.float(), rtol=1e-2, atol=3e-3)
+        # the preallocated form of the same step: eager, then captured with its all-gather and replayed
+        fast = partition.SplitKVDecodeAttention(local, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode,
+                                                n_splits=3)
+        eager = fast.step(q).clone()
+        torch.cuda.synchronize()
+        ok = ok and torch.allclose(eager.float(), whole.float(), rtol=1e-2, atol=3e-3)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fast.step(q)                                  # warm-up on the capture stream
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        # thread_local: the process group's watchdog thread polls events while this thread captures
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            fast.step(q)
+        fast.out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(fast.out, eager)
         with open(f"{result_path}.{rank}", "w") as f:
-            f.write("ok" if ok else f"mismatch {float((out.float() - whole.float()).abs().max())}")
-    finally:
-        dist.destroy_process_group()
+            f.write("ok" if ok else f"mismatch {float((out.float() - whole.float()).abs().max())} "
+                                    f"{float((eager.float() - whole.float()).abs().max())}")
+    except Exception as e:   # report and leave at once; tearing the group down could wait on the peers
+        with open(f"{result_path}.{rank}", "w") as f:
+            f.write(f"error {type(e).__name__}: {e}"[:500])
+    # Leave without tearing the communicator down: destroying it while a captured graph still
+    # holds its collective kernels did not return on two GPUs.
+    torch.cuda.synchronize()
+    os._exit(0)
 
 
+@pytest.mark.timeout(300)
 @pytest.mark.parametrize("rep_mode", ["sparse_only", "hybrid"])
 def test_split_kv_over_nccl(tmp_path, rep_mode):
     import torch.multiprocessing as mp
@@ -75,3 +105,14 @@ def test_split_kv_over_nccl(tmp_path, rep_mode):
     mp.spawn(_rank_main, args=(world, _free_port(), rep_mode, result), nprocs=world, join=True)
     for r in range(world):
         assert open(f"{result}.{r}").read() == "ok"
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("rep_mode", ["sparse_only", "hybrid"])
+def test_split_kv_step_as_a_group_of_one(tmp_path, rep_mode):
+    """One rank owns every block: the preallocated split-KV step (selection, ranged attention,
+    all-gather, gathered merge; eager and captured) must reproduce the one-call layer-step."""
+    import torch.multiprocessing as mp
+    result = str(tmp_path / "result")
+    mp.spawn(_rank_main, args=(1, _free_port(), rep_mode, result), nprocs=1, join=True)
+    assert open(f"{result}.0").read() == "ok"
