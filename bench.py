@@ -58,6 +58,9 @@ def parse_args():
     ap.add_argument("--cpu-sample-seqs", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="split-KV arm: launch the step eagerly")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="split-KV arm: partials stored into the peers' buffers by the attention kernel (p2p) "
+                         "or an NCCL all-gather after it (nccl)")
     ap.add_argument("--llama-steps", type=int, default=48,
                     help="greedy decode steps of the full Llama-3-8B-architecture model (batch 32, 8192-token "
                          "prompts, random weights) timed after the layer-step, 1 GPU only; 0 skips it")
@@ -431,8 +434,8 @@ def run_split_kv_arm(args):
         summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb)
         g = torch.Generator(device=device).manual_seed(77 + l)
         q = torch.randn((cfg.batch, cfg.n_q_heads, cfg.head_dim), generator=g, device=device).to(cfg.torch_dtype)
-        step = partition.SplitKVDecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=args.rep_mode,
-                                                n_splits=args.n_splits or 4)
+        cls = partition.SplitKVDecodeAttentionP2P if args.exchange == "p2p" else partition.SplitKVDecodeAttention
+        step = cls(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=args.rep_mode, n_splits=args.n_splits or 4)
         steps_obj.append((step, q))
     K, W = args.steps, args.warmup
     for step, q in steps_obj:          # communicator set-up and first launches outside any capture
@@ -488,9 +491,11 @@ def run_split_kv_arm(args):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "batch": cfg.batch, "context": max(cfg.prefix_lens),
                        "top_k": cfg.top_k, "rep_mode": args.rep_mode, "parallelism": f"split-kv x{world}",
-                       "exchange": "all_gather of (o, lse) partials, selection replicated",
+                       "exchange": ("peer stores of the (o, lse) partials from the attention kernel + flags"
+                                    if args.exchange == "p2p" else "NCCL all_gather of the (o, lse) partials")
+                                   + ", selection replicated",
                        "cuda_graph": graphs is not None},
-            "us_per_layer": 1e3 * ms / K, "gpu_launches": 3 * K, "clocks": clocks,
+            "us_per_layer": 1e3 * ms / K, "gpu_launches": 3 * K, "clocks": clocks, "device_status": ops.device_status(),
         }
         print(json.dumps(line), flush=True)
     if graphs is not None:

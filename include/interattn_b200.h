@@ -170,6 +170,36 @@ int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, in
                 int head_dim, void* out, int out_dtype, float* out_lse, ia_stream_t stream);
 
 /* Scratch needed by ia_decode_attention, in bytes. */
+/* ---- split-KV across GPUs with the exchange inside the kernels -------------------------
+ * No counterpart in the reference (one GPU).  Instead of an all-gather after the attention
+ * kernel, the kernel stores every partial into the gather buffer of every rank through
+ * peer pointers (NVLink stores), and its last CTA publishes the rank's step number in a
+ * flag on every rank; the merge kernel of a rank waits - bounded - until the flags of all
+ * ranks carry the step, then merges the chunks in place.
+ *   gather[w]  rank w's buffer, float [2][n_ranks][chunk_floats] (two step parities; a chunk
+ *              is o [n_rows, n_parts, head_dim] followed, lse_offset floats in, by lse
+ *              [n_rows, n_parts]); flags[w]  rank w's int32 [2][n_ranks], zero at start.
+ *              Entry my_rank is this rank's own memory, the others are peer mappings of
+ *              the same allocations (CUDA IPC or symmetric memory).
+ *   step_counter, grid_counter  this rank's own int32 words, zero at start.
+ * A wait that runs out sets bit 4 of the device status word (ia_read_device_status) and
+ * the kernel carries on; nothing spins without a limit. */
+typedef struct ia_peer_exchange {
+  int32_t n_ranks, my_rank;
+  float* gather[8];
+  int32_t* flags[8];
+  int64_t chunk_floats, lse_offset;
+  int32_t* step_counter;
+  int32_t* grid_counter;
+} ia_peer_exchange;
+int ia_sparse_decode_exchange(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                              const int32_t* prefix_lens, const int32_t* seq_lens, const int32_t* sel_idx,
+                              const int32_t* sel_count, int max_sel, const ia_summaries* summaries, const float* z,
+                              const ia_geom* geom, int rep_mode, int n_splits, int block_lo, int block_hi,
+                              int with_suffix, const ia_peer_exchange* exchange, ia_stream_t stream);
+int ia_finalize_exchange(const ia_peer_exchange* exchange, int n_rows, int n_parts, int head_dim, void* out,
+                         int out_dtype, ia_stream_t stream);
+
 /* The merge after an all-gather of split-KV partials across GPUs (the reference runs on one
  * GPU; its merge of chunk partials is the same arithmetic, IMPL/legacy.py:781-793).
  * `gathered` holds n_ranks chunks, rank_stride floats apart; a chunk is what one rank's

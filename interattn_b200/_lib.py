@@ -45,6 +45,12 @@ class SelectAux(Structure):
                 ("globals", c_void_p)]
 
 
+class PeerExchange(Structure):
+    _fields_ = [("n_ranks", c_int32), ("my_rank", c_int32), ("gather", c_void_p * 8), ("flags", c_void_p * 8),
+                ("chunk_floats", c_int64), ("lse_offset", c_int64), ("step_counter", c_void_p),
+                ("grid_counter", c_void_p)]
+
+
 # name -> (restype, argtypes); mirrors include/interattn_b200.h one to one
 SIGNATURES = {
     "ia_abi_version": (c_int, []),
@@ -75,6 +81,10 @@ SIGNATURES = {
     "ia_decode_attention_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             POINTER(Summaries), POINTER(Geom), c_int, c_int, c_float, c_int, c_int,
                                             c_int, c_void_p, c_void_p]),
+    "ia_sparse_decode_exchange": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_int, POINTER(Summaries), c_void_p, POINTER(Geom), c_int, c_int,
+                                          c_int, c_int, c_int, POINTER(PeerExchange), c_void_p]),
+    "ia_finalize_exchange": (c_int, [POINTER(PeerExchange), c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "ia_finalize_gathered": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "ia_llama_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
     "ia_llama_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64,

@@ -170,15 +170,34 @@ int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefi
                        aux ? *aux : none, nullptr, (cudaStream_t)stream);
 }
 
-int ia_sparse_decode(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
-                     const int32_t* prefix_lens, const int32_t* seq_lens, const int32_t* sel_idx,
-                     const int32_t* sel_count, int max_sel, const ia_summaries* summaries, const float* z,
-                     const ia_geom* geom, int rep_mode, int n_splits, int block_lo, int block_hi,
-                     int with_suffix, float* o_partial, float* lse_partial, ia_stream_t stream) {
+static int check_exchange(const ia_peer_exchange* px, int64_t n_rows, int n_parts, int head_dim) {
+  if (!px) return fail(IA_ERR_BAD_ARG, "exchange: null argument");
+  if (px->n_ranks < 1 || px->n_ranks > 8 || px->my_rank < 0 || px->my_rank >= px->n_ranks)
+    return fail(IA_ERR_BAD_ARG, "exchange: rank %d of %d (at most 8)", px->my_rank, px->n_ranks);
+  for (int w = 0; w < px->n_ranks; ++w)
+    if (!px->gather[w] || !px->flags[w]) return fail(IA_ERR_BAD_ARG, "exchange: null buffer of rank %d", w);
+  if (!px->step_counter || !px->grid_counter) return fail(IA_ERR_BAD_ARG, "exchange: null counter");
+  const int64_t n_o = n_rows * n_parts * head_dim;
+  if (px->lse_offset < n_o || px->chunk_floats < px->lse_offset + n_rows * n_parts)
+    return fail(IA_ERR_BAD_ARG, "exchange: chunk of %lld floats, lse at %lld, need %lld + %lld",
+                (long long)px->chunk_floats, (long long)px->lse_offset, (long long)n_o, (long long)(n_rows * n_parts));
+  return IA_OK;
+}
+
+static int sparse_decode_impl(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                              const int32_t* prefix_lens, const int32_t* seq_lens, const int32_t* sel_idx,
+                              const int32_t* sel_count, int max_sel, const ia_summaries* summaries, const float* z,
+                              const ia_geom* geom, int rep_mode, int n_splits, int block_lo, int block_hi,
+                              int with_suffix, float* o_partial, float* lse_partial,
+                              const ia_peer_exchange* exchange, ia_stream_t stream) {
   if (int s = check_geom(geom)) return s;
   if (!q || !k_pool || !v_pool || !block_table || !prefix_lens || !seq_lens || !sel_idx || !sel_count ||
-      !o_partial || !lse_partial)
+      (exchange == nullptr && (!o_partial || !lse_partial)))
     return fail(IA_ERR_BAD_ARG, "sparse_decode: null argument");
+  if (exchange != nullptr) {
+    const int64_t rows = (int64_t)geom->batch * geom->n_kv_heads * geom->group_size;
+    if (int s = check_exchange(exchange, rows, n_splits, geom->head_dim)) return s;
+  }
   if (!aligned16(k_pool) || !aligned16(v_pool) || !aligned16(q))
     return fail(IA_ERR_BAD_ARG, "sparse_decode: q and pools must be 16-byte aligned");
   if (rep_mode != IA_REP_SPARSE_ONLY && rep_mode != IA_REP_HYBRID)
@@ -193,7 +212,39 @@ int ia_sparse_decode(const void* q, const void* k_pool, const void* v_pool, cons
   if (block_lo < 0 || block_hi < block_lo) return fail(IA_ERR_BAD_ARG, "sparse_decode: block range [%d, %d)", block_lo, block_hi);
   return launch_sparse_decode(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, sel_idx, sel_count, max_sel,
                               summaries, z, *geom, rep_mode, n_splits, block_lo, block_hi, with_suffix, o_partial,
-                              lse_partial, nullptr, (cudaStream_t)stream);
+                              lse_partial, nullptr, (cudaStream_t)stream, exchange);
+}
+
+int ia_sparse_decode(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                     const int32_t* prefix_lens, const int32_t* seq_lens, const int32_t* sel_idx,
+                     const int32_t* sel_count, int max_sel, const ia_summaries* summaries, const float* z,
+                     const ia_geom* geom, int rep_mode, int n_splits, int block_lo, int block_hi,
+                     int with_suffix, float* o_partial, float* lse_partial, ia_stream_t stream) {
+  return sparse_decode_impl(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, sel_idx, sel_count, max_sel,
+                            summaries, z, geom, rep_mode, n_splits, block_lo, block_hi, with_suffix, o_partial,
+                            lse_partial, nullptr, stream);
+}
+
+int ia_sparse_decode_exchange(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                              const int32_t* prefix_lens, const int32_t* seq_lens, const int32_t* sel_idx,
+                              const int32_t* sel_count, int max_sel, const ia_summaries* summaries, const float* z,
+                              const ia_geom* geom, int rep_mode, int n_splits, int block_lo, int block_hi,
+                              int with_suffix, const ia_peer_exchange* exchange, ia_stream_t stream) {
+  if (!exchange) return fail(IA_ERR_BAD_ARG, "sparse_decode_exchange: null exchange");
+  return sparse_decode_impl(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, sel_idx, sel_count, max_sel,
+                            summaries, z, geom, rep_mode, n_splits, block_lo, block_hi, with_suffix, nullptr, nullptr,
+                            exchange, stream);
+}
+
+int ia_finalize_exchange(const ia_peer_exchange* exchange, int n_rows, int n_parts, int head_dim, void* out,
+                         int out_dtype, ia_stream_t stream) {
+  if (!out) return fail(IA_ERR_BAD_ARG, "finalize_exchange: null out");
+  if (n_rows < 0 || n_parts <= 0 || head_dim <= 0)
+    return fail(IA_ERR_BAD_ARG, "finalize_exchange: %d rows, %d parts", n_rows, n_parts);
+  if (int s = check_exchange(exchange, n_rows, n_parts, head_dim)) return s;
+  int* status = device_status_address();
+  if (status == nullptr) return IA_ERR_LAUNCH;
+  return launch_finalize_exchange(*exchange, n_rows, n_parts, head_dim, out, out_dtype, status, (cudaStream_t)stream);
 }
 
 int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts, int head_dim,

@@ -32,6 +32,10 @@ struct DecodeParams {
   void* final_out;      // null: partials only
   int* split_counters;  // [batch * kv heads], zero at launch; reset by the merging CTA
   int final_dtype;      // ia_dtype of final_out
+  // optional exchange with peer GPUs (split-KV across GPUs): instead of o_partial / lse_partial every
+  // partial is stored into the gather buffer of every rank - this one's included - over peer pointers,
+  // and the last CTA of the grid publishes this rank's step number on every rank
+  ia_peer_exchange px;  // n_ranks == 0: no exchange
   int64_t page_stride, head_stride;
   int n_kv_heads, group_size, page_size, block_size, max_pages, max_blocks, max_sel;
   int rep_mode, n_splits, block_lo, block_hi, with_suffix;
@@ -126,6 +130,44 @@ __device__ __forceinline__ void resolve_items(const DecodeParams& p, const ItemR
     items_s[i - chunk_begin] = it;
   }
   __syncthreads();
+}
+
+// ---- exchange of the partials with peer GPUs ---------------------------------------
+// Gather buffer of a rank: [2 (step parity)][n_ranks][chunk_floats]; a chunk is o [rows, n_splits, D]
+// followed by lse [rows, n_splits].  Flags of a rank: [2][n_ranks] step numbers.  Two parities are
+// enough: a rank can run at most one step ahead of a peer, because its next merge needs that peer's
+// next partials.
+struct ExchangeView {
+  int step, parity;
+};
+__device__ __forceinline__ ExchangeView exchange_view(const DecodeParams& p) {
+  ExchangeView v;
+  v.step = *p.px.step_counter + 1;  // changed only by the last CTA of this kernel, after every CTA has read it
+  v.parity = v.step & 1;
+  return v;
+}
+// one float of this rank's chunk (element offset inside the chunk), stored on every rank
+__device__ __forceinline__ void exchange_store(const DecodeParams& p, const ExchangeView& v, int64_t offset,
+                                               float value) {
+  const int64_t at = ((int64_t)v.parity * p.px.n_ranks + p.px.my_rank) * p.px.chunk_floats + offset;
+  for (int w = 0; w < p.px.n_ranks; ++w) p.px.gather[w][at] = value;
+}
+// Called by every thread of a CTA after its exchange_store calls.  `flag`: one int of shared memory.
+__device__ __forceinline__ void exchange_publish(const DecodeParams& p, const ExchangeView& v) {
+  __syncthreads();  // every thread's peer stores are issued
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // cumulative: the CTA's stores are visible system-wide before the count
+    const unsigned done = atomicAdd(reinterpret_cast<unsigned*>(p.px.grid_counter), 1u);
+    if (done == gridDim.x - 1) {  // every CTA of this rank has stored and fenced
+      *p.px.grid_counter = 0;
+      __threadfence_system();
+      for (int w = 0; w < p.px.n_ranks; ++w) {
+        volatile int32_t* f = p.px.flags[w] + v.parity * p.px.n_ranks + p.px.my_rank;
+        *f = v.step;
+      }
+      *p.px.step_counter = v.step;
+    }
+  }
 }
 
 // Fused split-KV finalize (same arithmetic as condition_block_stage2_reduce_kernel).

@@ -21,7 +21,8 @@ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // Bit set by a kernel whose bounded wait (mbarrier) ran out; read with
 // ia_read_device_status().  Waiting is always bounded so that a programming
 // error shows up as a status bit instead of a hung GPU.
-enum : int { DEV_STATUS_SELECT_WAIT_TIMEOUT = 1, DEV_STATUS_GEMM_WAIT_TIMEOUT = 2 };
+enum : int { DEV_STATUS_SELECT_WAIT_TIMEOUT = 1, DEV_STATUS_GEMM_WAIT_TIMEOUT = 2, DEV_STATUS_PEER_WAIT_TIMEOUT = 4 };
+int* device_status_address();  // device address of the status word on the current device
 int read_and_clear_device_status(int* out);  // defined next to the kernel that owns the word
 
 // ---- dtype traits ---------------------------------------------------------------
@@ -165,7 +166,11 @@ int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* seq_lens, const int32_t* sel_idx, const int32_t* sel_count,
                          int max_sel, const ia_summaries* summaries, const float* z, const ia_geom& g,
                          int rep_mode, int n_splits, int block_lo, int block_hi, int with_suffix,
-                         float* o_partial, float* lse_partial, const FusedFinalize* fused, cudaStream_t stream);
+                         float* o_partial, float* lse_partial, const FusedFinalize* fused, cudaStream_t stream,
+                         const ia_peer_exchange* exchange = nullptr);
+// merge of the partials the ranks stored into this rank's gather buffer, after a bounded wait for their flags
+int launch_finalize_exchange(const ia_peer_exchange& px, int n_rows, int n_parts, int head_dim, void* out,
+                             int out_dtype, int* status, cudaStream_t stream);
 int launch_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts,
                     int head_dim, void* out, int out_dtype, float* out_lse, cudaStream_t stream);
 // the same merge over n_groups chunks of partials, group_stride floats apart (one chunk per GPU)

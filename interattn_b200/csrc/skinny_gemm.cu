@@ -32,8 +32,6 @@
 #include "ia_common.cuh"
 
 namespace ia {
-int* device_status_address();  // the status word lives next to the selection kernel
-
 namespace {
 
 constexpr int kBM = 32, kBN = 128, kBK = 64;

@@ -35,6 +35,8 @@ condition_block_finalize_attention_fma_kernel(DecodeParams p) {
   const int head = pair % p.n_kv_heads, seq = pair / p.n_kv_heads;
   const int rows = p.n_kv_heads * G;
 
+  ExchangeView xv{};
+  if (p.px.n_ranks > 0) xv = exchange_view(p);
   const ItemRange r = item_range(p, seq, head, split, scratch);
   if (p.rep_mode == IA_REP_HYBRID) {
     const int words = (p.max_blocks + 31) / 32;
@@ -136,8 +138,19 @@ condition_block_finalize_attention_fma_kernel(DecodeParams p) {
       }
     }
     const int64_t orow = ((int64_t)seq * rows + head * G + g) * p.n_splits + split;
-    p.o_partial[orow * D + d] = den > 0.f ? num / den : 0.f;
-    if (d == 0) p.lse_partial[orow] = den > 0.f ? top + logf(den) : -INFINITY;
+    const float ov = den > 0.f ? num / den : 0.f;
+    const float lv = den > 0.f ? top + logf(den) : -INFINITY;
+    if (p.px.n_ranks > 0) {
+      exchange_store(p, xv, orow * D + d, ov);
+      if (d == 0) exchange_store(p, xv, p.px.lse_offset + orow, lv);
+    } else {
+      p.o_partial[orow * D + d] = ov;
+      if (d == 0) p.lse_partial[orow] = lv;
+    }
+  }
+  if (p.px.n_ranks > 0) {
+    exchange_publish(p, xv);
+    return;
   }
   finish_pair<D>(p, seq, head, G, scratch);
 }
@@ -169,8 +182,10 @@ int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* seq_lens, const int32_t* sel_idx, const int32_t* sel_count,
                          int max_sel, const ia_summaries* summaries, const float* z, const ia_geom& g,
                          int rep_mode, int n_splits, int block_lo, int block_hi, int with_suffix,
-                         float* o_partial, float* lse_partial, const FusedFinalize* fused, cudaStream_t stream) {
+                         float* o_partial, float* lse_partial, const FusedFinalize* fused, cudaStream_t stream,
+                         const ia_peer_exchange* exchange) {
   DecodeParams p{};
+  if (exchange != nullptr) p.px = *exchange;
   if (fused != nullptr) {
     p.final_out = fused->out;
     p.split_counters = fused->split_counters;

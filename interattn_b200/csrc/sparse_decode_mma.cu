@@ -96,6 +96,8 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
   // for the selection kernel: everything below reads what it wrote.
   grid_launch_dependents();
   grid_dependency_wait();
+  ExchangeView xv{};
+  if (p.px.n_ranks > 0) xv = exchange_view(p);
   const ItemRange r = item_range(p, seq, head, split, scratch);
   if (p.rep_mode == IA_REP_HYBRID) {
     const int words = (p.max_blocks + 31) / 32;
@@ -316,8 +318,19 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
       }
     }
     const int64_t orow = ((int64_t)seq * rows + head * G + g) * p.n_splits + split;
-    p.o_partial[orow * D + d] = den > 0.f ? num / den : 0.f;
-    if (d == 0) p.lse_partial[orow] = den > 0.f ? (top + log2f(den)) * kLn2 : -INFINITY;
+    const float ov = den > 0.f ? num / den : 0.f;
+    const float lv = den > 0.f ? (top + log2f(den)) * kLn2 : -INFINITY;
+    if (p.px.n_ranks > 0) {
+      exchange_store(p, xv, orow * D + d, ov);
+      if (d == 0) exchange_store(p, xv, p.px.lse_offset + orow, lv);
+    } else {
+      p.o_partial[orow * D + d] = ov;
+      if (d == 0) p.lse_partial[orow] = lv;
+    }
+  }
+  if (p.px.n_ranks > 0) {
+    exchange_publish(p, xv);
+    return;
   }
   finish_pair<D>(p, seq, head, G, scratch);
 }

@@ -205,3 +205,80 @@ class SplitKVDecodeAttention:
         ops.finalize_gathered(self.gathered, self.world, self.chunk, self.rows, self.n_splits, self.kv.head_dim,
                               self.out)
         return self.out
+
+
+class SplitKVDecodeAttentionP2P:
+    """The split-KV layer-step with the exchange inside the kernels: three launches
+    (selection, attention, merge) and no collective call.
+
+    The attention kernel stores every partial into the gather buffer of every rank through
+    peer pointers (NVLink stores) and its last CTA publishes the step number in a flag on
+    every rank; the merge kernel waits - bounded, about a second - for the flags of all
+    ranks and merges the chunks in place.  The buffers are symmetric memory
+    (``torch.distributed._symmetric_memory``), mapped once at construction; a step
+    allocates nothing and keeps its step counter on the device, so it can be captured into a
+    CUDA graph.  Plain peer stores only - no multicast.  Every rank must construct the
+    object (a collective) and run the same number of steps."""
+
+    def __init__(self, kv, summ, n_q_heads: int, *, top_k=None, eps=None, rep_mode: str = "sparse_only",
+                 n_splits: int = 4, group=None):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib, ops
+        self.ops, self.lib, self.kv, self.summ = ops, _lib.load(), kv, summ
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        self.top_k, self.eps, self.rep_mode, self.n_splits = top_k, eps, rep_mode, int(n_splits)
+        nb = summ.max_blocks
+        self.block_range = plan_block_ranges(nb, self.world)[self.rank]
+        self.with_suffix = self.rank == self.world - 1
+        b, d = kv.batch, kv.head_dim
+        self.n_q_heads, self.rows = int(n_q_heads), b * int(n_q_heads)
+        dev = kv.k_pool.device
+        max_sel = max(int(top_k), 1) if top_k is not None else nb
+        self.sel_idx = torch.empty((b, kv.n_kv_heads, max_sel), device=dev, dtype=torch.int32)
+        self.sel_count = torch.empty((b, kv.n_kv_heads), device=dev, dtype=torch.int32)
+        self.aux = {}
+        if rep_mode == "hybrid":
+            self.aux["z"] = torch.full((b, self.n_q_heads, nb), float("-inf"), device=dev, dtype=torch.float32)
+        n_o = self.rows * self.n_splits * d
+        chunk = (n_o + self.rows * self.n_splits + 3) // 4 * 4
+        flag_floats = 64                                   # flags [2][world] int32 at the tail, 256-byte slot
+        self.buf = symm_mem.empty(2 * self.world * chunk + flag_floats, dtype=torch.float32, device=dev)
+        self.buf.zero_()
+        torch.cuda.synchronize(dev)
+        self.handle = symm_mem.rendezvous(self.buf, group=group.group_name)
+        self.counters = torch.zeros(2, device=dev, dtype=torch.int32)       # step counter, grid counter
+        px = _lib.PeerExchange()
+        px.n_ranks, px.my_rank = self.world, self.rank
+        for w in range(self.world):
+            base = int(self.handle.buffer_ptrs[w])
+            px.gather[w] = base
+            px.flags[w] = base + 2 * self.world * chunk * 4
+        px.chunk_floats, px.lse_offset = chunk, n_o
+        px.step_counter = self.counters.data_ptr()
+        px.grid_counter = self.counters.data_ptr() + 4
+        self.px, self._byref = px, ctypes.byref
+        self.out = torch.empty((b, self.n_q_heads, d), device=dev, dtype=kv.k_pool.dtype)
+        self.geom = kv.geom(self.n_q_heads // kv.n_kv_heads, summ.block_size, nb)
+        self.c_summ = summ.c_struct()
+        dist.barrier(group)                                # every rank's buffer is zeroed and mapped
+
+    def step(self, q: torch.Tensor) -> torch.Tensor:
+        from ._lib import check
+        ops, kv = self.ops, self.kv
+        kw = dict(top_k=self.top_k) if self.top_k is not None else dict(eps=self.eps)
+        ops.select_blocks(q, self.summ, kv.prefix_lens, out_idx=self.sel_idx, out_count=self.sel_count,
+                          max_sel=int(self.sel_idx.shape[-1]), want=tuple(self.aux), aux_buffers=self.aux, **kw)
+        p, s = ops._ptr, ops._stream()
+        lo, hi = self.block_range
+        check(self.lib.ia_sparse_decode_exchange(
+            p(q), p(kv.k_pool), p(kv.v_pool), p(kv.block_table), p(kv.prefix_lens), p(kv.seq_lens),
+            p(self.sel_idx), p(self.sel_count), int(self.sel_idx.shape[-1]), self._byref(self.c_summ),
+            p(self.aux.get("z")), self._byref(self.geom), ops._REP[self.rep_mode], self.n_splits, int(lo), int(hi),
+            int(self.with_suffix), self._byref(self.px), s))
+        check(self.lib.ia_finalize_exchange(self._byref(self.px), self.rows, self.n_splits, kv.head_dim,
+                                            p(self.out), ops._DTYPES[self.out.dtype], s))
+        return self.out

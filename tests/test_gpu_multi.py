@@ -82,9 +82,33 @@ def _rank_main(rank, world, port, rep_mode, result_path):
         graph.replay()
         torch.cuda.synchronize()
         ok = ok and torch.equal(fast.out, eager)
+        # the same step with the exchange inside the kernels (peer stores + flags, no collective call)
+        p2p = partition.SplitKVDecodeAttentionP2P(local, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode,
+                                                  n_splits=3)
+        direct = p2p.step(q).clone()
+        torch.cuda.synchronize()
+        ok_p2p = torch.allclose(direct.float(), whole.float(), rtol=1e-2, atol=3e-3)
+        for _ in range(3):                                # consecutive steps alternate the two buffer parities
+            again = p2p.step(q)
+        torch.cuda.synchronize()
+        ok_p2p = ok_p2p and torch.equal(again, direct)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            p2p.step(q)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph2, capture_error_mode="thread_local"):
+            p2p.step(q)
+        for _ in range(2):
+            p2p.out.zero_()
+            graph2.replay()
+        torch.cuda.synchronize()
+        ok_p2p = ok_p2p and torch.equal(p2p.out, direct) and ops.device_status() == 0
         with open(f"{result_path}.{rank}", "w") as f:
-            f.write("ok" if ok else f"mismatch {float((out.float() - whole.float()).abs().max())} "
-                                    f"{float((eager.float() - whole.float()).abs().max())}")
+            f.write("ok" if ok and ok_p2p else f"mismatch {float((out.float() - whole.float()).abs().max())} "
+                                               f"{float((eager.float() - whole.float()).abs().max())} "
+                                               f"p2p {ok_p2p} {float((direct.float() - whole.float()).abs().max())}")
     except Exception as e:   # report and leave at once; tearing the group down could wait on the peers
         with open(f"{result_path}.{rank}", "w") as f:
             f.write(f"error {type(e).__name__}: {e}"[:500])
