@@ -58,6 +58,8 @@ def parse_args():
     ap.add_argument("--cpu-sample-seqs", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="split-KV arm: launch the step eagerly")
+    ap.add_argument("--kbar-bf16", action="store_true",
+                    help="store the block key means in bf16 (the reference's approximate option) instead of fp32")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="split-KV arm: partials stored into the peers' buffers by the attention kernel (p2p) "
                          "or an NCCL all-gather after it (nccl)")
@@ -249,7 +251,8 @@ def run_gpu_arm(args):
     n_pools = max(1, args.layer_pools)
     for l in range(n_pools):
         kv = make_device_layer(cfg, device, seed=1000 * rank + l)
-        summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb)
+        summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb,
+                                   k_bar_dtype=torch.bfloat16 if args.kbar_bf16 else torch.float32)
         layers.append((kv, summ))
         steppers.append(ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=args.rep_mode,
                                             n_splits=n_splits))
@@ -318,7 +321,7 @@ def run_gpu_arm(args):
         suffix_tok = sum(cfg.suffix_lens) * cfg.n_kv_heads
         kv_bytes = (tokens_sel + suffix_tok) * cfg.head_dim * 2 * esz
         sel_bytes = sum((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens) * cfg.n_kv_heads * (
-            cfg.head_dim * 4 + 2 * cfg.head_dim * esz + 4)
+            cfg.head_dim * (2 if args.kbar_bf16 else 4) + 2 * cfg.head_dim * esz + 4)
         peak, peak_src = FALLBACK_HBM_GBS, "fallback"
         try:
             with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -345,7 +348,7 @@ def run_gpu_arm(args):
             "config": {"workload": args.workload, "batch_per_gpu": cfg.batch, "n_q_heads": cfg.n_q_heads,
                        "n_kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim, "context": max(cfg.prefix_lens),
                        "page": cfg.page_size, "block": cfg.block_size, "top_k": cfg.top_k,
-                       "rep_mode": args.rep_mode, "n_splits": n_splits, "parallelism": (f"kv-head shard x{world}" if head_shard else f"batch-shard x{world}"),
+                       "rep_mode": args.rep_mode, "n_splits": n_splits, "k_bar": "bf16" if args.kbar_bf16 else "f32", "parallelism": (f"kv-head shard x{world}" if head_shard else f"batch-shard x{world}"),
                        "l2": f"{n_pools} layer pools rotated, {(kv_bytes + sel_bytes) >> 20} MiB read per step "
                              "(> 126 MB L2), no flush"},
             "us_per_layer": 1e3 * elapsed_ms / K,
@@ -431,7 +434,8 @@ def run_split_kv_arm(args):
     steps_obj = []
     for l in range(n_pools):
         kv = make_device_layer(cfg, device, seed=l)      # same seed on every rank: a rank reads only its range
-        summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb)
+        summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb,
+                                   k_bar_dtype=torch.bfloat16 if args.kbar_bf16 else torch.float32)
         g = torch.Generator(device=device).manual_seed(77 + l)
         q = torch.randn((cfg.batch, cfg.n_q_heads, cfg.head_dim), generator=g, device=device).to(cfg.torch_dtype)
         cls = partition.SplitKVDecodeAttentionP2P if args.exchange == "p2p" else partition.SplitKVDecodeAttention

@@ -78,10 +78,17 @@ typedef struct ia_geom {
   int32_t max_pages;    /* row length of block_table */
   int32_t max_blocks;   /* blocks per (sequence, kv head) in the summary arrays */
   int32_t dtype;        /* ia_dtype of q, pools, k_max/k_min/v_bar */
-  int32_t reserved;
+  int32_t reserved;     /* flags: IA_GEOM_KBAR_BF16, else 0 */
   int64_t pool_page_stride; /* in elements */
   int64_t pool_head_stride; /* in elements */
 } ia_geom;
+
+/* ia_geom.reserved flag: ia_summaries.k_bar holds bf16 values (same shape) instead of fp32 - the
+ * reference's CONDITION_BLOCK_K_BAR_DTYPE=bfloat16 option (IMPL/core.py:428-446, 482; only with
+ * bf16 pools).  The mean is accumulated in fp32 and rounded once; scores computed from it are
+ * approximate with respect to the fp32 k_bar and may rank near-equal blocks differently.  768
+ * instead of 1024 summary bytes per block and kv head at head_dim 128. */
+#define IA_GEOM_KBAR_BF16 1
 
 /* Block summaries, "mixed" storage of the reference (IMPL/core.py:411-446):
  * means accumulated in fp32, k_bar kept in fp32, the rest in the KV dtype

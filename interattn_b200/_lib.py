@@ -22,6 +22,7 @@ IA_ERR_LAUNCH = -3
 IA_F32, IA_BF16 = 0, 1
 IA_SELECT_TOPK, IA_SELECT_EPS = 0, 1
 IA_SELECT_TERM1_MASS_EXP = 0x100   # OR-ed into the mode
+IA_GEOM_KBAR_BF16 = 1              # ia_geom.reserved flag: k_bar stored in bf16
 IA_REP_SPARSE_ONLY, IA_REP_HYBRID = 0, 1
 ABI_VERSION = 1
 

@@ -18,7 +18,7 @@
 // vector leaving the SM.
 //
 // Roofline: HBM.  Algorithmic bytes per block and kv head:
-//   D*4 (k_bar f32) + 2*D*sizeof(T) (k_max, k_min) + 4 (v_norm_max).
+//   D*4 (k_bar f32; D*2 with the bf16 k_bar option) + 2*D*sizeof(T) (k_max, k_min) + 4 (v_norm_max).
 //
 // A ring stage is 32 blocks: every summary vector arrives as TMA boxes of
 // 128 bytes x 32 rows written with the 128-byte swizzle, so both access
@@ -94,7 +94,7 @@ struct SelectParams {
   // (rows = batch * kv heads * max_blocks); box = 128 bytes x 32 rows, 128-byte swizzle
   CUtensorMap tm_kbar, tm_kmax, tm_kmin;
   const void* q;
-  const float* k_bar;
+  const void* k_bar;  // f32, or bf16 with IA_GEOM_KBAR_BF16
   const void* k_max;
   const void* k_min;
   const float* v_norm_max;
@@ -258,14 +258,14 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&o)[8]) {
 // 128-byte swizzle: the 16-byte chunk c of row r lands at chunk c ^ (r & 7).
 // Lane r walking its own row therefore hits eight different bank groups per
 // quarter-warp - no padding, no conflicts.
-template <typename T, int D> struct TileLayout {
+template <typename T, int D, typename KB = float> struct TileLayout {
   static constexpr int box_bytes = 128 * kTileBlocks;
-  static constexpr int kbar_boxes = D * 4 / 128;
+  static constexpr int kbar_boxes = D * (int)sizeof(KB) / 128;
   static constexpr int bnd_boxes = D * (int)sizeof(T) / 128;
   static constexpr int kbar_bytes = kbar_boxes * box_bytes;
   static constexpr int bnd_bytes = bnd_boxes * box_bytes;
   static constexpr int bytes = kbar_bytes + 2 * bnd_bytes;
-  static constexpr int kbar_box_cols = 32;                    // floats per 128 bytes
+  static constexpr int kbar_box_cols = 128 / (int)sizeof(KB);  // k_bar elements per 128 bytes
   static constexpr int bnd_box_cols = 128 / (int)sizeof(T);
 };
 
@@ -295,10 +295,10 @@ template <int D, int G, bool MMA, int NG> struct SmemPlan {
   }
 };
 
-template <typename T, int D, int G, int NG>
+template <typename T, int D, int G, int NG, typename KB>
 __global__ void __launch_bounds__(Shape<NG>::threads, Shape<NG>::min_ctas)
 condition_block_select_kernel(const __grid_constant__ SelectParams p) {
-  using L = TileLayout<T, D>;
+  using L = TileLayout<T, D, KB>;
   using P = SmemPlan<D, G, kUseMma<T, G>, NG>;
   constexpr int kGroups = NG, kConsumerWarps = Shape<NG>::consumer_warps, kWarps = Shape<NG>::warps,
                 kThreads = Shape<NG>::threads;
@@ -325,6 +325,16 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   const int n_my_tiles = t_hi - t_lo;
   const int b_lo = t_lo * kTileBlocks, b_hi = min(t_hi * kTileBlocks, nb);
   const int nbl = p.nb_loc_cap;
+  // Ring geometry.  The consumers of a stage are "slots" (two tensor-core warps, or a group of four
+  // CUDA-core warps) that walk the tiles round robin.  A parity wait can only tell a phase from its
+  // neighbour, so the slot that waits for use u of a stage must know that use u - 1 has completed:
+  // the stage count is cut to a multiple of the slot count, which makes every stage the property of
+  // one slot - the slot that consumed use u - 1 is the one that waits for use u.  (With 8 stages
+  // and 6 slots the owners rotated; a wait then passed on the previous phase, the ring lost step
+  // and a bounded wait ran out.)
+  constexpr int kSlotUnits = kUseMma<T, G> ? kConsumerWarps / 2 : kGroups;
+  const int n_slots = min(kSlotUnits, p.n_stages);
+  const int n_stages = p.n_stages - p.n_stages % n_slots;
 
   // ---- shared memory carve-up -------------------------------------------------
   unsigned char* sp = smem_raw;
@@ -349,7 +359,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       (reinterpret_cast<uintptr_t>(t_s + (size_t)G * nbl) + 1023) & ~uintptr_t(1023));
 
   if (tid == 0) {
-    for (int s = 0; s < p.n_stages; ++s) {
+    for (int s = 0; s < n_stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], kUseMma<T, G> ? 2 : kGroupWarps);
     }
@@ -385,8 +395,8 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     const int row0 = (int)sum_row0;
     for (int lt = 0; lt < n_my_tiles; ++lt) {
       const int t = t_lo + lt;
-      const int stage = lt % p.n_stages;
-      const int use = lt / p.n_stages;
+      const int stage = lt % n_stages;
+      const int use = lt / n_stages;
       if (use > 0 && alive) {
         if (!mbar_wait(&empty_bar[stage], (uint32_t)((use - 1) & 1))) {
           alive = false;
@@ -441,16 +451,11 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     const uint32_t row_off = (uint32_t)(arow * 128);
     const uint32_t row_xor = (uint32_t)(arow & 7);
     RowNorm rn[2] = {{-INFINITY, 0.f, 0.f}, {-INFINITY, 0.f, 0.f}};
-    // A parity wait can only tell a phase from its neighbour: a consumer must
-    // never wait on a stage more than one use ahead of the producer.  With at
-    // most n_stages slots walking the tiles in order that holds (finishing tile
-    // t - n_slots implies every earlier tile, including t - n_stages, was filled).
-    const int n_slots = min(kSlots, p.n_stages);
     bool alive = true;
     for (int lt = slot; slot < n_slots && lt < n_my_tiles; lt += n_slots) {
       const int t = t_lo + lt;
-      const int stage = lt % p.n_stages;
-      const int use = lt / p.n_stages;
+      const int stage = lt % n_stages;
+      const int use = lt / n_stages;
       if (alive && !mbar_wait(&full_bar[stage], (uint32_t)(use & 1))) {
         alive = false;
         if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
@@ -459,21 +464,33 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       float cd[4] = {0.f, 0.f, 0.f, 0.f};
       float xp[4] = {0.f, 0.f, 0.f, 0.f}, xm[4] = {0.f, 0.f, 0.f, 0.f};  // k_max . q+, k_max . q-
       float np_[4] = {0.f, 0.f, 0.f, 0.f}, nm[4] = {0.f, 0.f, 0.f, 0.f};  // k_min . q+, k_min . q-
+      if constexpr (sizeof(KB) == 4) {
 #pragma unroll
-      for (int kk = 0; kk < D / 8; ++kk) {
-        const int byte = (kk * 8 + (lm >> 1) * 4) * 4;
-        uint32_t a[4], hi[4], md[4], lo[4];
-        ldmatrix_x4(st + (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4), a);
+        for (int kk = 0; kk < D / 8; ++kk) {
+          const int byte = (kk * 8 + (lm >> 1) * 4) * 4;
+          uint32_t a[4], hi[4], md[4], lo[4];
+          ldmatrix_x4(st + (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4), a);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          hi[i] = a[i] & 0xffffe000u;
-          const float r1 = __uint_as_float(a[i]) - __uint_as_float(hi[i]);
-          md[i] = __float_as_uint(r1) & 0xffffe000u;
-          lo[i] = __float_as_uint(r1 - __uint_as_float(md[i]));
+          for (int i = 0; i < 4; ++i) {
+            hi[i] = a[i] & 0xffffe000u;
+            const float r1 = __uint_as_float(a[i]) - __uint_as_float(hi[i]);
+            md[i] = __float_as_uint(r1) & 0xffffe000u;
+            lo[i] = __float_as_uint(r1 - __uint_as_float(md[i]));
+          }
+          mma_tf32(cd, hi, bq[kk]);
+          mma_tf32(cd, md, bq[kk]);
+          mma_tf32(cd, lo, bq[kk]);
         }
-        mma_tf32(cd, hi, bq[kk]);
-        mma_tf32(cd, md, bq[kk]);
-        mma_tf32(cd, lo, bq[kk]);
+      } else {
+        // bf16 k_bar: the same exact bf16 products as the bounds, q = q+ + q-
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const int byte = (kk * 16 + (lm >> 1) * 8) * 2;
+          uint32_t a[4];
+          ldmatrix_x4(st + (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4), a);
+          mma_bf16(cd, a, bp[kk]);
+          mma_bf16(cd, a, bm[kk]);
+        }
       }
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
@@ -561,12 +578,12 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     RowNorm rn[kRowsPerWarp];
 #pragma unroll
     for (int r = 0; r < kRowsPerWarp; ++r) rn[r] = RowNorm{-INFINITY, 0.f, 0.f};
-    const int n_groups = min(kGroups, p.n_stages);  // see the note on parity waits above
+    const int n_groups = n_slots;  // see the note on the ring geometry above
     bool alive = true;
     for (int lt = group; group < n_groups && lt < n_my_tiles; lt += n_groups) {
       const int t = t_lo + lt;
-      const int stage = lt % p.n_stages;
-      const int use = lt / p.n_stages;
+      const int stage = lt % n_stages;
+      const int use = lt / n_stages;
       if (alive && !mbar_wait(&full_bar[stage], (uint32_t)(use & 1))) {
         alive = false;
         if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
@@ -584,8 +601,12 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       for (int c = 0; c < DQ; c += 8) {
         const int e0 = wq * DQ + c;  // first of eight head_dim elements
         float kb[8], hi[8], lo[8];
-        load4(swz<float>(kbar_v, lane, e0), kb);
-        load4(swz<float>(kbar_v, lane, e0 + 4), kb + 4);
+        if constexpr (sizeof(KB) == 4) {
+          load4(swz<float>(kbar_v, lane, e0), kb);
+          load4(swz<float>(kbar_v, lane, e0 + 4), kb + 4);
+        } else {
+          load8(swz<__nv_bfloat16>(kbar_v, lane, e0), kb);
+        }
         if constexpr (sizeof(T) == 2) {
           load8(swz<T>(kmax_v, lane, e0), hi);
           load8(swz<T>(kmin_v, lane, e0), lo);
@@ -911,9 +932,9 @@ static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t 
   return IA_OK;
 }
 
-template <typename T, int D, int G, int NG>
+template <typename T, int D, int G, int NG, typename KB>
 static int launch_shaped(const SelectParams& p, int n_pairs, size_t smem, cudaStream_t stream) {
-  auto kern = condition_block_select_kernel<T, D, G, NG>;
+  auto kern = condition_block_select_kernel<T, D, G, NG, KB>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "select: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   e = launch_overlapped(kern, (unsigned)(n_pairs * p.cluster), (unsigned)Shape<NG>::threads, smem, stream, p,
@@ -922,9 +943,9 @@ static int launch_shaped(const SelectParams& p, int n_pairs, size_t smem, cudaSt
   return check_launch("condition_block_select_kernel");
 }
 
-template <typename T, int D, int G>
+template <typename T, int D, int G, typename KB>
 static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stream) {
-  using L = TileLayout<T, D>;
+  using L = TileLayout<T, D, KB>;
   using PW = SmemPlan<D, G, kUseMma<T, G>, kWideGroups>;
   using PN = SmemPlan<D, G, kUseMma<T, G>, kNarrowGroups>;
   SelectParams p = base;
@@ -952,7 +973,7 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   p.nb_loc_cap = (max_tiles / cluster + 1) * kTileBlocks;
   const int64_t rows = (int64_t)n_pairs * p.max_blocks;
   if (rows > 0x7fffffff) return fail(IA_ERR_UNSUPPORTED, "select: %lld summary rows exceed the TMA coordinate range", (long long)rows);
-  if (int s = encode_rows(&p.tm_kbar, p.k_bar, false, rows, D)) return s;
+  if (int s = encode_rows(&p.tm_kbar, p.k_bar, sizeof(KB) == 2, rows, D)) return s;
   if (int s = encode_rows(&p.tm_kmax, p.k_max, sizeof(T) == 2, rows, D)) return s;
   if (int s = encode_rows(&p.tm_kmin, p.k_min, sizeof(T) == 2, rows, D)) return s;
 
@@ -972,7 +993,7 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
       if (stages > max_tiles) stages = max_tiles < 2 ? 2 : max_tiles;
       if (stages > kMaxStages) stages = kMaxStages;
       p.n_stages = stages;
-      return launch_shaped<T, D, G, kNarrowGroups>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
+      return launch_shaped<T, D, G, kNarrowGroups, KB>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
     }
   }
   const size_t fixed = PW::fixed + PW::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
@@ -982,17 +1003,17 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   int stages = (int)(((size_t)max_smem - fixed) / L::bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.n_stages = stages;
-  return launch_shaped<T, D, G, kWideGroups>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
+  return launch_shaped<T, D, G, kWideGroups, KB>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
 }
 
-template <typename T, int D>
+template <typename T, int D, typename KB = float>
 static int launch_group(const SelectParams& p, int n_pairs, int group, cudaStream_t stream) {
   switch (group) {
-    case 1: return launch_typed<T, D, 1>(p, n_pairs, stream);
-    case 2: return launch_typed<T, D, 2>(p, n_pairs, stream);
-    case 4: return launch_typed<T, D, 4>(p, n_pairs, stream);
-    case 8: return launch_typed<T, D, 8>(p, n_pairs, stream);
-    case 16: return launch_typed<T, D, 16>(p, n_pairs, stream);
+    case 1: return launch_typed<T, D, 1, KB>(p, n_pairs, stream);
+    case 2: return launch_typed<T, D, 2, KB>(p, n_pairs, stream);
+    case 4: return launch_typed<T, D, 4, KB>(p, n_pairs, stream);
+    case 8: return launch_typed<T, D, 8, KB>(p, n_pairs, stream);
+    case 16: return launch_typed<T, D, 16, KB>(p, n_pairs, stream);
     default: return fail(IA_ERR_UNSUPPORTED, "select: group_size %d not built (1, 2, 4, 8, 16)", group);
   }
 }
@@ -1011,7 +1032,11 @@ int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_le
   p.sel_idx = sel_idx; p.sel_count = sel_count; p.aux = aux; p.split_counters = split_counters;
   const int n_pairs = g.batch * g.n_kv_heads;
   if (n_pairs <= 0) return IA_OK;
-  if (g.dtype == IA_BF16) {
+  if (g.reserved & IA_GEOM_KBAR_BF16) {  // k_bar stored in bf16: only next to bf16 pools ("mixed" storage)
+    if (g.dtype != IA_BF16) return fail(IA_ERR_UNSUPPORTED, "select: bf16 k_bar needs bf16 pools");
+    if (g.head_dim == 128) return launch_group<__nv_bfloat16, 128, __nv_bfloat16>(p, n_pairs, g.group_size, stream);
+    if (g.head_dim == 64) return launch_group<__nv_bfloat16, 64, __nv_bfloat16>(p, n_pairs, g.group_size, stream);
+  } else if (g.dtype == IA_BF16) {
     if (g.head_dim == 128) return launch_group<__nv_bfloat16, 128>(p, n_pairs, g.group_size, stream);
     if (g.head_dim == 64) return launch_group<__nv_bfloat16, 64>(p, n_pairs, g.group_size, stream);
   } else if (g.dtype == IA_F32) {

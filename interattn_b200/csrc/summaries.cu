@@ -77,7 +77,10 @@ condition_block_build_summaries_kernel(const T* __restrict__ k_pool, const T* __
     kb[i] = ksum[i] / denom;
     vb[i] = vsum[i] / denom;
   }
-  store_vec<VEC>(out.k_bar + row, kb);
+  if (g.reserved & IA_GEOM_KBAR_BF16)  // the reference's bf16 k_bar option: the fp32 mean, rounded once
+    store_vec<VEC>(reinterpret_cast<__nv_bfloat16*>(out.k_bar) + row, kb);
+  else
+    store_vec<VEC>(out.k_bar + row, kb);
   store_vec<VEC>(reinterpret_cast<T*>(out.v_bar) + row, vb);
   store_vec<VEC>(reinterpret_cast<T*>(out.k_max) + row, kmax);
   store_vec<VEC>(reinterpret_cast<T*>(out.k_min) + row, kmin);

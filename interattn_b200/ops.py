@@ -45,6 +45,11 @@ def _need_cuda(*tensors: torch.Tensor) -> None:
             raise ValueError("interattn_b200 operators take CUDA tensors only (there is no CPU path)")
 
 
+def _geom_flags(summ) -> int:
+    """Geometry flags implied by how the summaries are stored (bf16 k_bar: IA_GEOM_KBAR_BF16)."""
+    return _lib.IA_GEOM_KBAR_BF16 if summ is not None and summ.k_bar.dtype == torch.bfloat16 else 0
+
+
 @dataclass
 class PagedKV:
     """A paged KV cache: physical pools + per-sequence page lists + lengths."""
@@ -87,19 +92,20 @@ class PagedKV:
     def head_dim(self) -> int:
         return int(self.k_pool.shape[3])
 
-    def geom(self, group_size: int, block_size: int, max_blocks: int) -> Geom:
+    def geom(self, group_size: int, block_size: int, max_blocks: int, summ: Optional["BlockSummaries"] = None) -> Geom:
         return Geom(
             batch=self.batch, n_kv_heads=self.n_kv_heads, group_size=int(group_size), head_dim=self.head_dim,
             page_size=self.page_size, block_size=int(block_size), max_pages=int(self.block_table.shape[1]),
-            max_blocks=int(max_blocks), dtype=_DTYPES[self.k_pool.dtype], reserved=0,
+            max_blocks=int(max_blocks), dtype=_DTYPES[self.k_pool.dtype], reserved=_geom_flags(summ),
             pool_page_stride=int(self.k_pool.stride(0)), pool_head_stride=int(self.k_pool.stride(1)))
 
 
 @dataclass
 class BlockSummaries:
-    """Per (sequence, kv head, block) statistics: k_bar f32, the rest in the KV dtype."""
+    """Per (sequence, kv head, block) statistics: k_bar f32 (or bf16: the reference's
+    CONDITION_BLOCK_K_BAR_DTYPE=bfloat16 option, approximate), the rest in the KV dtype."""
 
-    k_bar: torch.Tensor       # [B, Hkv, nb, D] f32
+    k_bar: torch.Tensor       # [B, Hkv, nb, D] f32 | bf16
     k_max: torch.Tensor       # [B, Hkv, nb, D]
     k_min: torch.Tensor
     v_bar: torch.Tensor
@@ -116,10 +122,12 @@ class BlockSummaries:
 
     @staticmethod
     def empty(batch: int, n_kv_heads: int, max_blocks: int, head_dim: int, dtype: torch.dtype, device,
-              block_size: int) -> "BlockSummaries":
+              block_size: int, k_bar_dtype: torch.dtype = torch.float32) -> "BlockSummaries":
         shape = (batch, n_kv_heads, max_blocks, head_dim)
+        if k_bar_dtype not in (torch.float32, torch.bfloat16) or (k_bar_dtype != torch.float32 and dtype != torch.bfloat16):
+            raise ValueError("k_bar is float32, or bfloat16 next to bfloat16 pools")
         return BlockSummaries(
-            k_bar=torch.zeros(shape, device=device, dtype=torch.float32),
+            k_bar=torch.zeros(shape, device=device, dtype=k_bar_dtype),
             k_max=torch.zeros(shape, device=device, dtype=dtype),
             k_min=torch.zeros(shape, device=device, dtype=dtype),
             v_bar=torch.zeros(shape, device=device, dtype=dtype),
@@ -129,7 +137,8 @@ class BlockSummaries:
 
 def build_summaries(kv: PagedKV, block_size: int, max_blocks: Optional[int] = None,
                     out: Optional[BlockSummaries] = None,
-                    first_blocks: Optional[torch.Tensor] = None) -> BlockSummaries:
+                    first_blocks: Optional[torch.Tensor] = None,
+                    k_bar_dtype: torch.dtype = torch.float32) -> BlockSummaries:
     """Block summaries of every sequence's prefix (reference: ``_build_prompt_blocks``).
 
     ``first_blocks`` (int32 [B], device; needs ``out``) makes it an incremental
@@ -143,7 +152,7 @@ def build_summaries(kv: PagedKV, block_size: int, max_blocks: Optional[int] = No
         _need_cuda(first_blocks)
         if first_blocks.dtype != torch.int32 or not first_blocks.is_contiguous() or first_blocks.numel() != kv.batch:
             raise ValueError("first_blocks must be a contiguous int32 tensor with one entry per sequence")
-        g = kv.geom(1, block_size, out.max_blocks)
+        g = kv.geom(1, block_size, out.max_blocks, out)
         s = out.c_struct()
         check(lib.ia_update_summaries(_ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),
                                       _ptr(first_blocks), ctypes.byref(g), ctypes.byref(s), _stream()))
@@ -153,8 +162,8 @@ def build_summaries(kv: PagedKV, block_size: int, max_blocks: Optional[int] = No
             1, (int(kv.block_table.shape[1]) * kv.page_size + block_size - 1) // block_size)
     if out is None:
         out = BlockSummaries.empty(kv.batch, kv.n_kv_heads, max_blocks, kv.head_dim, kv.k_pool.dtype,
-                                   kv.k_pool.device, block_size)
-    g = kv.geom(1, block_size, max_blocks)
+                                   kv.k_pool.device, block_size, k_bar_dtype)
+    g = kv.geom(1, block_size, max_blocks, out)
     s = out.c_struct()
     check(lib.ia_build_summaries(_ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),
                                  ctypes.byref(g), ctypes.byref(s), _stream()))
@@ -216,7 +225,7 @@ def select_blocks(
         aux[name] = buf
     c_aux = SelectAux(*[aux[n].data_ptr() if n in aux else None for n in ("score", "z", "s", "delta", "globals")])
     g = Geom(batch=b, n_kv_heads=hkv, group_size=group, head_dim=d, page_size=16, block_size=summ.block_size,
-             max_pages=1, max_blocks=nb, dtype=_DTYPES[q.dtype], reserved=0,
+             max_pages=1, max_blocks=nb, dtype=_DTYPES[q.dtype], reserved=_geom_flags(summ),
              pool_page_stride=16 * d, pool_head_stride=16 * d)
     s = summ.c_struct()
     check(lib.ia_select(_ptr(q), ctypes.byref(s), _ptr(prefix_lens), ctypes.byref(g), mode,
@@ -251,7 +260,7 @@ def sparse_decode(
     else:
         o, lse = out
     lo, hi = (0, max_blocks) if block_range is None else block_range
-    g = kv.geom(group, block_size, max_blocks)
+    g = kv.geom(group, block_size, max_blocks, summ)
     s = summ.c_struct() if summ is not None else None
     check(lib.ia_sparse_decode(
         _ptr(q), _ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens), _ptr(kv.seq_lens),
@@ -334,7 +343,7 @@ class DecodeAttention:
         self.top_k, self.eps = int(top_k or 0), float(eps or 0.0)
         nb = summ.max_blocks
         self.max_sel = int(max_sel) if max_sel is not None else (max(self.top_k, 1) if top_k is not None else nb)
-        self.geom = kv.geom(self.group, summ.block_size, nb)
+        self.geom = kv.geom(self.group, summ.block_size, nb, summ)
         if n_splits is None:   # wave-aware choice for this device
             expect = expected_blocks or (min(self.top_k, nb) if top_k is not None else max(1, nb // 16))
             n_splits = self.lib.ia_suggest_splits(ctypes.byref(self.geom), int(max(1, expect)))
@@ -430,7 +439,7 @@ def decode_attention_noalloc(
     mode = IA_SELECT_TOPK if top_k is not None else IA_SELECT_EPS
     if max_sel is None:
         max_sel = max(int(top_k), 1) if top_k is not None else summ.max_blocks
-    g = kv.geom(group, summ.block_size, summ.max_blocks)
+    g = kv.geom(group, summ.block_size, summ.max_blocks, summ)
     s = summ.c_struct()
     check(lib.ia_decode_attention_noalloc(
         _ptr(q), _ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens), _ptr(kv.seq_lens),

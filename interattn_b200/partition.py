@@ -262,7 +262,7 @@ class SplitKVDecodeAttentionP2P:
         px.grid_counter = self.counters.data_ptr() + 4
         self.px, self._byref = px, ctypes.byref
         self.out = torch.empty((b, self.n_q_heads, d), device=dev, dtype=kv.k_pool.dtype)
-        self.geom = kv.geom(self.n_q_heads // kv.n_kv_heads, summ.block_size, nb)
+        self.geom = kv.geom(self.n_q_heads // kv.n_kv_heads, summ.block_size, nb, summ)
         self.c_summ = summ.c_struct()
         dist.barrier(group)                                # every rank's buffer is zeroed and mapped
 

@@ -73,10 +73,10 @@ class _CacheGeometry:
             self.capacity_pages = max(need, 2 * self.capacity_pages, 64)
             self.table = torch.arange(self.capacity_pages, dtype=torch.int32, device=self.device).view(1, -1)
 
-    def geom(self, k: torch.Tensor, group: int, block_size: int, max_blocks: int) -> Geom:
+    def geom(self, k: torch.Tensor, group: int, block_size: int, max_blocks: int, summ=None) -> Geom:
         return Geom(batch=1, n_kv_heads=int(k.shape[0]), group_size=int(group), head_dim=int(k.shape[2]),
                     page_size=PAGE, block_size=int(block_size), max_pages=self.capacity_pages,
-                    max_blocks=int(max_blocks), dtype=ops._DTYPES[k.dtype], reserved=0,
+                    max_blocks=int(max_blocks), dtype=ops._DTYPES[k.dtype], reserved=ops._geom_flags(summ),
                     pool_page_stride=PAGE * int(k.shape[2]), pool_head_stride=int(k.stride(0)))
 
 
@@ -121,8 +121,14 @@ def _build_prompt_blocks(k_all: torch.Tensor, v_all: torch.Tensor, block_size: i
     geometry = _CacheGeometry(dev, length)
     geometry.prefix_lens.fill_(length)
     geometry.seq_lens.fill_(length)
-    summ = ops.BlockSummaries.empty(1, hkv, nb, d, k_all.dtype, dev, block_size)
-    g = geometry.geom(k_all, 1, block_size, nb)
+    # the reference's switch for the storage of k_bar (core.py:428-446): bf16 only next to bf16 K/V
+    k_bar_name = os.environ.get("CONDITION_BLOCK_K_BAR_DTYPE", "float32")
+    if k_bar_name not in ("float32", "bfloat16"):
+        raise ValueError(f"CONDITION_BLOCK_K_BAR_DTYPE must be float32 or bfloat16, got {k_bar_name!r}.")
+    if k_bar_name != "float32" and k_all.dtype != torch.bfloat16:
+        raise ValueError("CONDITION_BLOCK_K_BAR_DTYPE=bfloat16 needs bfloat16 keys and values.")
+    summ = ops.BlockSummaries.empty(1, hkv, nb, d, k_all.dtype, dev, block_size, getattr(torch, k_bar_name))
+    g = geometry.geom(k_all, 1, block_size, nb, summ)
     s = summ.c_struct()
     check(lib.ia_build_summaries(ctypes.c_void_p(k_all.data_ptr()), ctypes.c_void_p(v_all.data_ptr()),
                                  ctypes.c_void_p(geometry.table.data_ptr()),
@@ -308,7 +314,7 @@ def _condition_block_decode_output_fused_triton(
     if term1_mass_exp:
         mode |= _lib.IA_SELECT_TERM1_MASS_EXP
     max_sel = max(nb, 1)
-    g = geo.geom(k_all, group, h.block_size, nb)
+    g = geo.geom(k_all, group, h.block_size, nb, h.summ)
     ws_dict = workspace if workspace is not None else {}
     n_splits = ws_dict.get("b200_n_splits")
     if n_splits is None:

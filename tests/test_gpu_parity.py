@@ -140,6 +140,39 @@ def test_term1_mass_exp_variant(bundle):
     assert torch.equal(step.sel_idx.cpu()[:, :, :idx.shape[2]], idx)
 
 
+def test_bf16_k_bar_option(bundle):
+    """The reference's bf16 storage of the block key means (CONDITION_BLOCK_K_BAR_DTYPE=bfloat16): the stored
+    mean is the fp32 mean rounded once; selection is identical to the oracle evaluated on those stored
+    means; the layer-step runs on them."""
+    ops = _ops()
+    cfg, case, q, kv, summ = bundle
+    if cfg.dtype != "bfloat16":
+        with pytest.raises(ValueError):
+            ops.build_summaries(kv, cfg.block_size, max_blocks=summ.max_blocks, k_bar_dtype=torch.bfloat16)
+        return
+    low = ops.build_summaries(kv, cfg.block_size, max_blocks=summ.max_blocks, k_bar_dtype=torch.bfloat16)
+    assert low.k_bar.dtype == torch.bfloat16
+    for b in range(cfg.batch):
+        nbv = (int(case["prefix_lens"][b]) + cfg.block_size - 1) // cfg.block_size
+        assert torch.equal(low.k_bar[b, :, :nbv], summ.k_bar[b, :, :nbv].to(torch.bfloat16))
+        assert torch.equal(low.k_max[b, :, :nbv], summ.k_max[b, :, :nbv])
+    idx, cnt, aux = ops.select_blocks(q, low, kv.prefix_lens, top_k=cfg.top_k, want=("score", "s"))
+    assert ops.device_status() == 0
+    idx, cnt = idx.cpu(), cnt.cpu()
+    for b in range(cfg.batch):
+        osum, terms, ranked, _ = _oracle_selection(cfg, case, low, b, cfg.top_k)
+        nb = osum.n_blocks
+        assert torch.allclose(aux["s"][b, :, :nb].cpu().reshape(cfg.n_kv_heads, cfg.group_size, nb), terms["s"],
+                              rtol=1e-5, atol=1e-5)
+        assert torch.allclose(aux["score"][b, :, :nb].cpu(), terms["score"], rtol=2e-4, atol=1e-8)
+        for h in range(cfg.n_kv_heads):
+            assert idx[b, h, :int(cnt[b, h])].tolist() == sorted(ranked[h])
+    step = ops.DecodeAttention(kv, low, cfg.n_q_heads, top_k=cfg.top_k)
+    step.step(q)
+    assert torch.equal(step.sel_idx.cpu()[:, :, :idx.shape[2]], idx)
+    assert bool(torch.isfinite(step.out.float()).all())
+
+
 def test_eps_selection(bundle):
     ops = _ops()
     cfg, case, q, kv, summ = bundle
