@@ -40,6 +40,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -163,6 +166,17 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
       if (ksrc != nullptr) cp_async16(kdst + off, ksrc + srow * D + ch * 8, live ? 16u : 0u);
       cp_async16(vdst + off, vsrc + srow * D + ch * 8, live ? 16u : 0u);
     }
+    if (ksrc == nullptr) {
+      // representatives: their logits z[row][block] ride in the unused K half of the stage as
+      // [16 rows][16 blocks] floats, so that consume() does not wait on global loads
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int id = c * 32 + lane;
+        const int row = id >> 4, tok = id & 15;
+        if (row < G && tok < it.hi)
+          cp_async4(kdst + id * 4, zrow + (int64_t)row * p.max_blocks + it.first + tok);
+      }
+    }
   };
 
   auto consume = [&](const Item& it, int stage) {
@@ -193,7 +207,8 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
         }
       }
     } else {
-      // representatives: logits come from the selection pass (z = s + log count)
+      // representatives: logits come from the selection pass (z = s + log count), staged by issue()
+      const float* zt = reinterpret_cast<const float*>(my_ring + (size_t)stage * STAGE_BYTES);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
 #pragma unroll
@@ -203,7 +218,7 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
           const int b = it.first + tok;
           bool ok = tok < it.hi && row < G;
           if (ok) ok = ((sel_bits[b >> 5] >> (b & 31)) & 1u) == 0u;
-          s[t][e] = ok ? zrow[(int64_t)row * p.max_blocks + b] * kLog2e : -INFINITY;
+          s[t][e] = ok ? zt[row * 16 + tok] * kLog2e : -INFINITY;
         }
       }
     }
