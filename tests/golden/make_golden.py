@@ -134,7 +134,10 @@ SMALL_RAGGED = DecodeConfig(
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    here = os.path.dirname(os.path.abspath(__file__))
+    ap.add_argument("--reference", default=os.environ.get("INTERATTN_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(os.path.dirname(os.path.dirname(here))), "reference"),
+        help="the reference checkout (default: a directory `reference` next to this repository)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     from llama.script.analysis.condition_block_gen.methods import condition_block as pr1

@@ -9,7 +9,9 @@ import sys
 import pytest
 import torch
 
-REF_ROOT = os.environ.get("INTERATTN_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: INTERATTN_REFERENCE_ROOT, else a directory `reference` next to this repository
+REF_ROOT = os.environ.get("INTERATTN_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 pytestmark = pytest.mark.skipif(
     not os.path.isdir(os.path.join(REF_ROOT, "llama")), reason="reference tree not present")
 
