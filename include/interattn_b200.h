@@ -22,7 +22,12 @@
  *                            IMPL/page_attention.py:173-309 (attention half)
  *   ia_finalize         <- _condition_block_stage2_reduce_kernel IMPL/legacy.py:765-794
  *   ia_decode_attention <- _condition_block_decode_output_fused_triton
- *                            IMPL/core.py:1035-1155 (the three launches of one layer-step)
+ *                            IMPL/core.py:1035-1155 (the launches of one layer-step)
+ *   ia_update_summaries <- no counterpart (the reference never re-blocks its suffix)
+ *   ia_sparse_decode_exchange, ia_finalize_exchange, ia_finalize_gathered
+ *                       <- no counterpart (split-KV across GPUs; the reference has one GPU)
+ *   ia_llama_*          <- the Hugging Face modules the reference replays around its hook in
+ *                          the captured decode step, IMPL/core.py:190-316
  *
  * Tensor conventions
  *   q            [batch, n_kv_heads * group_size, head_dim]   dtype; query head = kv * G + g
