@@ -10,7 +10,7 @@
 // online-softmax partials in HBM in between.  Here one CTA owns one
 // (sequence, kv head): it streams the three summary vectors of every block
 // once through a TMA (cp.async.bulk.tensor) + mbarrier shared-memory ring,
-// keeps z = s + log(count), cosh(delta) - 1 and tanh(delta / 2) of all
+// keeps z = s + log(count) and the range bound delta of all
 // G x n_blocks (row, block) pairs in shared memory, forms the global
 // normalisers on the fly, the GQA-mean score and then routes - a radix select
 // for the k best blocks (higher score first, lower block index first among
@@ -291,7 +291,7 @@ template <int D, int G, bool MMA, int NG> struct SmemPlan {
   static constexpr size_t xch = 8 * 16 * 3 * 4;  // [cluster rank][row][m, l, d]
   static constexpr size_t fixed = bars + hist + scan + red + norm + state + qrows + part + xch;
   static size_t per_blocks(int nb_cap, int nb_loc_cap) {
-    return (size_t)nb_cap * 4 * 2 + (size_t)nb_loc_cap * 4 * 3 * G;
+    return (size_t)nb_cap * 4 * 2 + (size_t)nb_loc_cap * 4 * 2 * G;
   }
 };
 
@@ -353,10 +353,9 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   float* vn_s = reinterpret_cast<float*>(sp);                           // [nb_cap]
   float* score_s = vn_s + nb_cap;                                       // [nb_cap]
   float* z_s = score_s + nb_cap;                                        // [G][nbl]: z = s + log count (own blocks)
-  float* a_s = z_s + (size_t)G * nbl;                                   // [G][nbl]: cosh(delta) - 1
-  float* t_s = a_s + (size_t)G * nbl;                                   // [G][nbl]: tanh(delta / 2)
+  float* d_s = z_s + (size_t)G * nbl;                                   // [G][nbl]: delta (range bound)
   unsigned char* stage_base = reinterpret_cast<unsigned char*>(
-      (reinterpret_cast<uintptr_t>(t_s + (size_t)G * nbl) + 1023) & ~uintptr_t(1023));
+      (reinterpret_cast<uintptr_t>(d_s + (size_t)G * nbl) + 1023) & ~uintptr_t(1023));
 
   if (tid == 0) {
     for (int s = 0; s < n_stages; ++s) {
@@ -521,8 +520,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           delta_terms(delta, p.mass_exp, ch, a_term, th);
           norm_absorb(acc, z, ch);
           z_s[g * nbl + b - b_lo] = z;
-          a_s[g * nbl + b - b_lo] = a_term;
-          t_s[g * nbl + b - b_lo] = th;
+          d_s[g * nbl + b - b_lo] = delta;  // the score phase recomputes cosh - 1 and tanh from it
           const int64_t o = ((int64_t)pair * G + g) * p.max_blocks + b;
           if (p.aux.s != nullptr) p.aux.s[o] = s;
           if (p.aux.z != nullptr) p.aux.z[o] = z;
@@ -664,8 +662,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           delta_terms(delta, p.mass_exp, ch, a_term, th);
           norm_absorb(rn[g / kGroupWarps], z, ch);
           z_s[g * nbl + b - b_lo] = z;
-          a_s[g * nbl + b - b_lo] = a_term;
-          t_s[g * nbl + b - b_lo] = th;
+          d_s[g * nbl + b - b_lo] = delta;  // the score phase recomputes cosh - 1 and tanh from it
           const int64_t o = ((int64_t)pair * G + g) * p.max_blocks + b;
           if (p.aux.s != nullptr) p.aux.s[o] = s;
           if (p.aux.z != nullptr) p.aux.z[o] = z;
@@ -762,7 +759,9 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         const float pm = expf(z_s[g * nbl + b - b_lo] - norm_s[g]) * norm_s[16 + g];
-        sum += pm * fmaf(norm_s[32 + g], a_s[g * nbl + b - b_lo], two_bc * t_s[g * nbl + b - b_lo]);
+        float ch, a_term, th;
+        delta_terms(d_s[g * nbl + b - b_lo], p.mass_exp, ch, a_term, th);
+        sum += pm * fmaf(norm_s[32 + g], a_term, two_bc * th);
       }
       const float sc = sum / (float)G;
       st_cluster_f32(score_r0 + (uint32_t)b * 4u, sc);
