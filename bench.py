@@ -1,6 +1,6 @@
 """Benchmark of the condition-block sparse decode-attention layer-step.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 Workload (N = 1): the Llama-3-8B attention geometry - bf16, 32 query / 8 kv
@@ -13,6 +13,14 @@ prompts.  A "step" is one such layer-step over the batch.  With N GPUs every
 rank owns its own 16 sequences (batch x kv-head sharding: the units share
 nothing, so there is no collective on the data path) - weak scaling.
 
+Timing: W warm-up steps, then R regions of exactly K steps each; a region is
+bracketed by a device synchronise (and a barrier across ranks) on both sides,
+timed with CUDA events, maximum over ranks; the line reports the MEDIAN
+region (min and mean beside it) - one 20-step region lasts 1.5 ms, too short
+to stand alone.  Four KV pools are rotated between steps (> 126 MB of L2
+touched before a pool is seen again); `cold_l2` repeats the steps with a
+256 MiB buffer overwritten before each one.
+
 One JSON line on rank 0:
   value      decode tokens advanced through one attention layer per second,
              whole job, inputs resident in HBM (one C-ABI call per step)
@@ -20,9 +28,16 @@ One JSON line on rank 0:
              the step, output -> pinned host, every step
   roofline   the paged sparse-attention kernel: K/V bytes of the selected
              tokens / its CUDA-event duration, against the measured HBM peak
-  cpu_baseline  the CPU oracle (a port of the reference's PyTorch path) timed
-             on this box's host cores on a bounded sample
-`--impl reference` times that CPU path alone, with every host thread.
+  hybrid, kbar_bf16   the same step in the reference's own mode (unselected
+             blocks attended through their representatives) and with the
+             block key means stored in bf16, each with its own roofline
+  cpu_baseline  the CPU port of the reference's PyTorch path timed on this
+             box's host cores on a bounded sample: its sparse (gather the
+             selected tokens) and dense (score every token, then mask) legs
+  llama_decode  tokens/s of the whole Llama-3-8B-architecture decode (N = 1)
+  strong_cfg5, split_kv_cfg4   (N > 1) the two strong-scaling arms: kv-head
+             shards of the ragged 70B batch, and split-KV of the 128k batch
+`--impl reference` times the CPU path alone, with every host thread.
 """
 
 from __future__ import annotations
@@ -44,26 +59,30 @@ UNIT = "tok*layer/s"
 WORKLOAD = "cfg2_llama8b_32k"
 N_LAYER_POOLS = 4       # default number of KV pools rotated between steps (4 x 320 MiB touched > 126 MB of L2)
 FALLBACK_HBM_GBS = 6650.0
+FLUSH_BYTES = 256 << 20  # cold-L2 variant: at least twice the 126 MB L2
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
-    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20, help="steps per timed region")
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--repeats", type=int, default=25, help="timed regions of --steps steps; the median is reported")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--n-splits", type=int, default=0, help="split-KV parts per (sequence, kv head); 0 = auto")
     ap.add_argument("--rep-mode", default="sparse_only", choices=["sparse_only", "hybrid"])
     ap.add_argument("--workload", default=WORKLOAD)
     ap.add_argument("--cpu-sample-seqs", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-variants", action="store_true", help="skip the hybrid / bf16-k_bar / cold-L2 sub-records")
+    ap.add_argument("--no-strong", action="store_true", help="N > 1: skip the two strong-scaling sub-records")
     ap.add_argument("--no-graph", action="store_true", help="split-KV arm: launch the step eagerly")
     ap.add_argument("--kbar-bf16", action="store_true",
                     help="store the block key means in bf16 (the reference's approximate option) instead of fp32")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="split-KV arm: partials stored into the peers' buffers by the attention kernel (p2p) "
                          "or an NCCL all-gather after it (nccl)")
-    ap.add_argument("--llama-steps", type=int, default=48,
+    ap.add_argument("--llama-steps", type=int, default=256,
                     help="greedy decode steps of the full Llama-3-8B-architecture model (batch 32, 8192-token "
                          "prompts, random weights) timed after the layer-step, 1 GPU only; 0 skips it")
     ap.add_argument("--layer-pools", type=int, default=N_LAYER_POOLS,
@@ -96,15 +115,29 @@ def cpu_prepare(cfg, n_seqs, seed_offset=0):
     return small, prepared
 
 
-def cpu_layer_step(small, prepared):
-    """One layer-step on the host: score + top-k + sparse attention per sequence.  Returns seconds."""
+def cpu_layer_step(small, prepared, leg="sparse", rep_mode="sparse_only"):
+    """One layer-step on the host: score + top-k + attention per sequence.  ``leg`` picks the port of
+    the reference's sparse path (gather the selected tokens, IMPL/legacy.py:871-966) or of its dense
+    path (score every prefix token, then mask, IMPL/legacy.py:797-868).  Returns seconds."""
     from oracle import condition_block_oracle as orc
+    attend = orc.decode_attention if leg == "sparse" else orc.decode_attention_dense
     t0 = time.perf_counter()
     for plen, k, v, summ, qg in prepared:
         terms = orc.condition_terms(qg, summ)
         _, mask = orc.select_topk(terms["score"], summ.counts, small.top_k)
-        orc.decode_attention(qg, k, v, plen, small.block_size, mask, rep_mode="sparse_only")
+        attend(qg, k, v, plen, small.block_size, mask, rep_mode=rep_mode, z=terms["z"], v_bar=summ.v_bar)
     return time.perf_counter() - t0
+
+
+def cpu_legs(cfg, n, reps, rep_mode):
+    """Both CPU legs on the same ``n`` sampled sequences -> {"sparse": tok*layer/s, "dense": ...}, seconds per step."""
+    small, prepared = cpu_prepare(cfg, n)
+    out, secs = {}, {}
+    for leg in ("sparse", "dense"):
+        cpu_layer_step(small, prepared, leg, rep_mode)  # warm-up
+        dt = sum(cpu_layer_step(small, prepared, leg, rep_mode) for _ in range(reps)) / reps
+        out[leg], secs[leg] = n / dt, dt
+    return out, secs
 
 
 def run_reference_arm(args):
@@ -113,26 +146,29 @@ def run_reference_arm(args):
     if rank != 0:
         return
     import torch
-    from oracle.configs import CONFIGS
+    from interattn_b200.workloads import CONFIGS
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     cfg = CONFIGS[args.workload]
     n = 1 if args.steps > 20 else max(1, min(args.cpu_sample_seqs, 4))
     small, prepared = cpu_prepare(cfg, n)
     for _ in range(args.warmup):
-        cpu_layer_step(small, prepared)
+        cpu_layer_step(small, prepared, "sparse", args.rep_mode)
     total = 0.0
     for _ in range(args.steps):
-        total += cpu_layer_step(small, prepared)
+        total += cpu_layer_step(small, prepared, "sparse", args.rep_mode)
     value = n * args.steps / total
+    dense_dt = sum(cpu_layer_step(small, prepared, "dense", args.rep_mode) for _ in range(3)) / 3
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "sample": f"{n} of {cfg.batch} sequences per step"},
+        "config": {"workload": args.workload, "rep_mode": args.rep_mode,
+                   "sample": f"{n} of {cfg.batch} sequences per step"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{n} sequence(s) x {args.steps} steps: score + top-k + sparse attention, "
-                                   "summaries excluded"},
+                         "sample": f"{n} sequence(s) x {args.steps} steps: score + top-k + sparse attention "
+                                   "(the port of the reference's sparse CPU leg), summaries excluded",
+                         "legs": {"sparse": value, "dense": n / dense_dt}},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -215,11 +251,125 @@ def make_device_layer(cfg, device, seed):
     return ops.PagedKV(k_pool, v_pool, table, prefix, seq)
 
 
+def hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def committed_traffic(workload, kernel):
+    """DRAM bytes per launch from the committed ncu summary (profiles/dram_traffic.txt), or None."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.txt")) as f:
+            for ln in f:
+                parts = ln.split()
+                if len(parts) == 3 and parts[0] == workload and parts[1] == kernel:
+                    return int(parts[2])
+    except (OSError, ValueError):
+        pass
+    return None
+
+
+def algorithmic_bytes(cfg, rep_mode, kbar_bf16):
+    """(attention kernel, selection kernel) algorithmic bytes per launch."""
+    esz = 2 if cfg.dtype == "bfloat16" else 4
+    blocks = [(n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens]
+    tokens_sel = sum(min(cfg.top_k * cfg.block_size, n) for n in cfg.prefix_lens) * cfg.n_kv_heads
+    suffix_tok = sum(cfg.suffix_lens) * cfg.n_kv_heads
+    kv_bytes = (tokens_sel + suffix_tok) * cfg.head_dim * 2 * esz
+    if rep_mode == "hybrid":  # one v_bar row per unselected block
+        kv_bytes += sum(max(nb - cfg.top_k, 0) for nb in blocks) * cfg.n_kv_heads * cfg.head_dim * esz
+    sel_bytes = sum(blocks) * cfg.n_kv_heads * (cfg.head_dim * (2 if kbar_bf16 else 4) + 2 * cfg.head_dim * esz + 4)
+    return kv_bytes, sel_bytes
+
+
+class Regions:
+    """R timed regions of K steps each, bracketed by a synchronise (+ barrier) on both sides."""
+
+    def __init__(self, torch, dist, world, device):
+        self.torch, self.dist, self.world, self.device = torch, dist, world, device
+
+    def sync_all(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def run(self, step, K, R, first=0):
+        """step(i) enqueues step i.  Returns per-region milliseconds (max over ranks), a list of R."""
+        torch = self.torch
+        ms = []
+        i = first
+        for _ in range(R):
+            self.sync_all()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(K):
+                step(i)
+                i += 1
+            t1.record()
+            self.sync_all()
+            ms.append(t0.elapsed_time(t1))
+        t = torch.tensor(ms, device=self.device, dtype=torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(x) for x in t.cpu()]
+
+
+def summarise(ms_regions, K):
+    """Median / min / mean microseconds per step over the regions."""
+    per = sorted(1e3 * m / K for m in ms_regions)
+    return {"median": statistics.median(per), "min": per[0], "mean": sum(per) / len(per), "regions": len(per)}
+
+
+def kernel_times(torch, steppers, qs, K, repeats):
+    """Per-kernel device microseconds (median over K x repeats live steps, events between the launches)."""
+    n_pools = len(steppers)
+    n = K * repeats
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n)]
+    for row in ev:
+        for e in row:
+            e.record()
+    torch.cuda.synchronize()
+    for i in range(n):
+        steppers[i % n_pools].step_timed(qs[i % n_pools], ev[i])
+    torch.cuda.synchronize()
+    sel = statistics.median(r[0].elapsed_time(r[1]) for r in ev) * 1e3
+    att = statistics.median(r[1].elapsed_time(r[2]) for r in ev) * 1e3
+    return sel, att
+
+
+def variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summaries, n_splits, K, R, workload):
+    """One sub-record: the layer-step in another mode / summary layout, with its own roofline."""
+    from interattn_b200 import ops
+    steppers = [ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode, n_splits=n_splits)
+                for (kv, _), summ in zip(layers, summaries)]
+    n_pools = len(steppers)
+    for i in range(8):
+        steppers[i % n_pools].step(qs[i % n_pools])
+    ms = regions.run(lambda i: steppers[i % n_pools].step(qs[i % n_pools]), K, R)
+    sel_us, att_us = kernel_times(torch, steppers, qs, K, max(1, R // 5))
+    kv_bytes, sel_bytes = algorithmic_bytes(cfg, rep_mode, kbar_bf16)
+    peak, src = hbm_peak()
+    att_gbs, sel_gbs = kv_bytes / (att_us * 1e-6) / 1e9, sel_bytes / (sel_us * 1e-6) / 1e9
+    return {
+        "us_per_layer": summarise(ms, K), "kernel_us": {"select": sel_us, "sparse_decode": att_us},
+        "config": {"rep_mode": rep_mode, "k_bar": "bf16" if kbar_bf16 else "f32"},
+        "roofline": {"bound": "hbm", "kernel": "condition_block_finalize_attention_kernel", "achieved": att_gbs,
+                     "peak": peak, "peak_source": src, "unit": "GB/s", "frac": att_gbs / peak,
+                     "bytes_per_launch": kv_bytes, "traffic": committed_traffic(workload, f"sparse_decode_{rep_mode}")},
+        "roofline_select": {"bound": "hbm", "kernel": "condition_block_select_kernel", "achieved": sel_gbs,
+                            "peak": peak, "unit": "GB/s", "frac": sel_gbs / peak, "bytes_per_launch": sel_bytes},
+    }
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
     from interattn_b200 import ops
-    from oracle.configs import CONFIGS
+    from interattn_b200.workloads import CONFIGS
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -229,30 +379,65 @@ def run_gpu_arm(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        from datetime import timedelta
+        dist.init_process_group("nccl", device_id=device, timeout=timedelta(seconds=180))
+    regions = Regions(torch, dist, world, device)
+    line = layer_step_record(args, args.workload, torch, dist, regions, world, rank, local_rank, device, main=True)
+    if world > 1 and not args.no_strong and args.workload == WORKLOAD:
+        # the two strong-scaling arms, every rank takes part; rank 0 attaches them to its line
+        for key, fn in (("strong_cfg5", strong_cfg5_record), ("split_kv_cfg4", split_kv_record)):
+            try:
+                rec = fn(args, torch, dist, regions, world, rank, local_rank, device)
+            except Exception as e:  # the same code runs on every rank, so every rank lands here together
+                rec = {"error": f"{type(e).__name__}: {e}"[:300]}
+            if rank == 0:
+                line[key] = rec
+    if rank == 0:
+        if not args.no_cpu_baseline and world == 1:
+            cfg = CONFIGS[args.workload]
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            n = max(1, args.cpu_sample_seqs)
+            legs, secs = cpu_legs(cfg, n, 3, args.rep_mode)
+            hyb, _ = cpu_legs(cfg, n, 2, "hybrid") if args.rep_mode != "hybrid" else (legs, secs)
+            line["cpu_baseline"] = {
+                "value": legs["sparse"], "unit": UNIT, "cores": cores, "kind": "port",
+                "sample": f"{n} of {cfg.batch} sequences, one layer-step x 3 per leg: score + top-k + attention "
+                          f"(sparse leg {secs['sparse']:.2f} s, dense leg {secs['dense']:.2f} s per step), "
+                          "summaries excluded",
+                "legs": {"sparse": legs["sparse"], "dense": legs["dense"],
+                         "hybrid_sparse": hyb["sparse"], "hybrid_dense": hyb["dense"]}}
+        if args.llama_steps > 1 and world == 1 and args.workload == WORKLOAD:
+            line["llama_decode"] = llama_decode_line(args.llama_steps)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        from interattn_b200 import partition
+        partition.ordered_shutdown()
 
-    cfg = CONFIGS[args.workload]
-    # The variable-length Llama-3-70B configuration shards by kv head (one head per GPU on 8,
-    # two on 4, four on 2): every rank holds all sequences but only its heads - strong scaling,
-    # still no collective, the output rows of different heads are disjoint.
-    head_shard = args.workload == "cfg5_llama70b_ragged" and world > 1
+
+def layer_step_record(args, workload, torch, dist, regions, world, rank, local_rank, device, main, head_shard=False):
+    """The layer-step of one workload on this rank's shard; returns the JSON record (meaningful on rank 0)."""
+    from dataclasses import replace
+    from interattn_b200 import ops
+    from interattn_b200.workloads import CONFIGS
+    cfg = CONFIGS[workload]
     if head_shard:
-        from dataclasses import replace
+        # kv-head shards: every rank holds all sequences but only its heads - strong scaling, still no
+        # collective, the output rows of different heads are disjoint
         from interattn_b200.partition import plan_head_shards
         lo, hi = plan_head_shards(cfg.n_kv_heads, world)[rank]
         cfg = replace(cfg, n_kv_heads=hi - lo, n_q_heads=(hi - lo) * cfg.group_size)
     replicas = 1 if head_shard else world
-    props = torch.cuda.get_device_properties(device)
     n_splits = args.n_splits or None      # None: the library picks a wave-aware split count
     nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
     rows = cfg.n_q_heads
+    kbar_dt = torch.bfloat16 if args.kbar_bf16 else torch.float32
 
     layers, steppers, qs = [], [], []
     n_pools = max(1, args.layer_pools)
     for l in range(n_pools):
         kv = make_device_layer(cfg, device, seed=1000 * rank + l)
-        summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb,
-                                   k_bar_dtype=torch.bfloat16 if args.kbar_bf16 else torch.float32)
+        summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb, k_bar_dtype=kbar_dt)
         layers.append((kv, summ))
         steppers.append(ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=args.rep_mode,
                                             n_splits=n_splits))
@@ -261,130 +446,112 @@ def run_gpu_arm(args):
     n_splits = steppers[0].n_splits
     torch.cuda.synchronize()
 
-    def sync_all():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    # ---- device-resident arm: K steps, per-kernel events inside the same region -------------
-    K, W = args.steps, args.warmup
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
-    for row in ev:
-        for e in row:
-            e.record()
-    sampler = ClockSampler(local_rank)   # samples from the warm-up to the end of the second timed region
+    K, W, R = args.steps, args.warmup, max(1, args.repeats)
+    sampler = ClockSampler(local_rank)   # samples from the warm-up to the end of the last timed region
     sampler.start()
-    for i in range(W):
+    for i in range(max(W, 3)):
         steppers[i % n_pools].step(qs[i % n_pools])
-    sync_all()
-    # headline region: K steps through the plain one-call entry point
-    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_begin.record()
-    for i in range(K):
-        steppers[i % n_pools].step(qs[i % n_pools])
-    t_end.record()
-    sync_all()
-    elapsed_ms = t_begin.elapsed_time(t_end)
-    # the same K steps again with events between the kernels: per-kernel device times for the roofline
-    for i in range(K):
-        steppers[i % n_pools].step_timed(qs[i % n_pools], ev[i])
-    sync_all()
-    sel_ms = sum(r[0].elapsed_time(r[1]) for r in ev) / K
-    att_ms = sum(r[1].elapsed_time(r[2]) for r in ev) / K
-    fin_ms = sum(r[2].elapsed_time(r[3]) for r in ev) / K
+    # headline: R regions of K steps through the plain one-call entry point
+    ms = regions.run(lambda i: steppers[i % n_pools].step(qs[i % n_pools]), K, R)
+    # the same steps again with events between the kernels: per-kernel device times for the roofline
+    sel_us, att_us = kernel_times(torch, steppers, qs, K, max(1, R // 5))
     status = ops.device_status()
 
-    # ---- end-to-end arm: host q in, host output back, every step ---------------------------------
+    # end-to-end: host q in, host output back, every step
     q_host = [q.cpu().pin_memory() for q in qs]
     out_host = [torch.empty_like(q).pin_memory() for q in q_host]
-    for i in range(min(W, 5)):
+    for i in range(5):
         steppers[i % n_pools].step_host(q_host[i % n_pools], out_host[i % n_pools])
-    sync_all()
-    e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_begin.record()
-    for i in range(K):
-        steppers[i % n_pools].step_host(q_host[i % n_pools], out_host[i % n_pools])
-    e_end.record()
-    sync_all()
+    e2e_ms = regions.run(lambda i: steppers[i % n_pools].step_host(q_host[i % n_pools], out_host[i % n_pools]), K, R)
     clocks = sampler.stop()
-    e2e_ms = e_begin.elapsed_time(e_end)
 
-    times = torch.tensor([elapsed_ms, e2e_ms, att_ms, sel_ms, fin_ms], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, att_ms, sel_ms, fin_ms = [float(x) for x in times.cpu()]
+    # cold L2: a 256 MiB buffer overwritten before every step, the step timed by its own events
+    cold = None
+    if main and not args.no_variants:
+        flush = torch.empty((FLUSH_BYTES,), device=device, dtype=torch.uint8)
+        n = K * max(1, R // 5)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for i in range(n):
+            flush.fill_(i & 0xff)
+            ev[i][0].record()
+            steppers[i % n_pools].step(qs[i % n_pools])
+            ev[i][1].record()
+        torch.cuda.synchronize()
+        per = sorted(a.elapsed_time(b) * 1e3 for a, b in ev)
+        cold = {"us_per_layer": {"median": statistics.median(per), "min": per[0], "mean": sum(per) / len(per)},
+                "flush_bytes": FLUSH_BYTES, "steps": n,
+                "note": "one step at a time between events, so launch latency is not hidden by the next step"}
+        del flush
 
-    if rank == 0:
-        esz = 2 if cfg.dtype == "bfloat16" else 4
-        tokens_sel = sum(min(cfg.top_k * cfg.block_size, n) for n in cfg.prefix_lens) * cfg.n_kv_heads
-        suffix_tok = sum(cfg.suffix_lens) * cfg.n_kv_heads
-        kv_bytes = (tokens_sel + suffix_tok) * cfg.head_dim * 2 * esz
-        sel_bytes = sum((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens) * cfg.n_kv_heads * (
-            cfg.head_dim * (2 if args.kbar_bf16 else 4) + 2 * cfg.head_dim * esz + 4)
-        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured"
-        except (OSError, KeyError, ValueError):
-            pass
-        traffic = None   # DRAM bytes per launch of the attention kernel, from the committed ncu summary
-        try:
-            with open(os.path.join(ROOT, "profiles", "dram_traffic.txt")) as f:
-                for ln in f:
-                    parts = ln.split()
-                    if len(parts) == 3 and parts[0] == args.workload and parts[1] == "sparse_decode":
-                        traffic = int(parts[2])
-        except (OSError, ValueError):
-            pass
-        att_gbs = kv_bytes / (att_ms * 1e-3) / 1e9
-        sel_gbs = sel_bytes / (sel_ms * 1e-3) / 1e9
-        q_bytes = cfg.batch * rows * cfg.head_dim * esz
-        line = {
-            "metric": METRIC, "value": replicas * cfg.batch * K / (elapsed_ms * 1e-3), "unit": UNIT,
-            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": elapsed_ms / K,
-            "higher_is_better": True, "scaling": "strong" if head_shard else "weak", "vs_baseline": None,
-            "dtype": "bf16" if cfg.dtype == "bfloat16" else "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": cfg.batch, "n_q_heads": cfg.n_q_heads,
-                       "n_kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim, "context": max(cfg.prefix_lens),
-                       "page": cfg.page_size, "block": cfg.block_size, "top_k": cfg.top_k,
-                       "rep_mode": args.rep_mode, "n_splits": n_splits, "k_bar": "bf16" if args.kbar_bf16 else "f32", "parallelism": (f"kv-head shard x{world}" if head_shard else f"batch-shard x{world}"),
-                       "l2": f"{n_pools} layer pools rotated, {(kv_bytes + sel_bytes) >> 20} MiB read per step "
-                             "(> 126 MB L2), no flush"},
-            "us_per_layer": 1e3 * elapsed_ms / K,
-            "kernel_us": {"select": 1e3 * sel_ms, "sparse_decode": 1e3 * att_ms, "finalize": 1e3 * fin_ms},
-            "roofline": {"bound": "hbm", "kernel": "condition_block_finalize_attention_kernel",
-                         "achieved": att_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                         "frac": att_gbs / peak, "traffic": traffic, "bytes_per_launch": kv_bytes},
-            "roofline_select": {"bound": "hbm", "kernel": "condition_block_select_kernel", "achieved": sel_gbs,
-                                "peak": peak, "unit": "GB/s", "frac": sel_gbs / peak,
-                                "bytes_per_launch": sel_bytes},
-            "e2e": {"value": replicas * cfg.batch * K / (e2e_ms * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": q_bytes, "d2h_bytes_per_step": q_bytes,
-                    "us_per_layer": 1e3 * e2e_ms / K,
-                    "note": "KV pool and block summaries are cache state resident on the device; the step's "
-                            "inputs (q) and outputs cross PCIe every step"},
-            "gpu_launches": 2 * K,   # selection + attention (finalize fused) per step, headline region
-            "clocks": clocks,
-            "device_status": status,
-        }
-        if not args.no_cpu_baseline and world == 1:
-            cores = os.cpu_count() or 1
-            torch.set_num_threads(cores)
-            n = max(1, args.cpu_sample_seqs)
-            small, prepared = cpu_prepare(cfg, n)
-            cpu_layer_step(small, prepared)  # warm-up
-            reps = 5
-            dt = sum(cpu_layer_step(small, prepared) for _ in range(reps)) / reps
-            line["cpu_baseline"] = {
-                "value": n / dt, "unit": UNIT, "cores": cores, "kind": "port",
-                "sample": f"{n} of {cfg.batch} sequences, one layer-step x {reps}: score + top-k + sparse "
-                          f"attention ({dt:.2f} s per step), summaries excluded"}
-        if args.llama_steps > 1 and world == 1 and args.workload == WORKLOAD:
-            line["llama_decode"] = llama_decode_line(args.llama_steps)
-        print(json.dumps(line), flush=True)
+    t = torch.tensor([sel_us, att_us], device=device, dtype=torch.float64)
     if world > 1:
-        dist.destroy_process_group()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sel_us, att_us = [float(x) for x in t.cpu()]
+    step_us, e2e_us = summarise(ms, K), summarise(e2e_ms, K)
+
+    esz = 2 if cfg.dtype == "bfloat16" else 4
+    kv_bytes, sel_bytes = algorithmic_bytes(cfg, args.rep_mode, args.kbar_bf16)
+    peak, peak_src = hbm_peak()
+    att_gbs = kv_bytes / (att_us * 1e-6) / 1e9
+    sel_gbs = sel_bytes / (sel_us * 1e-6) / 1e9
+    q_bytes = cfg.batch * rows * cfg.head_dim * esz
+    line = {
+        "metric": METRIC, "value": replicas * cfg.batch / (step_us["median"] * 1e-6), "unit": UNIT,
+        "n_gpus": world, "steps": K, "warmup": W, "repeats": R, "ms_per_step": step_us["median"] * 1e-3,
+        "higher_is_better": True, "scaling": "strong" if head_shard else "weak", "vs_baseline": None,
+        "dtype": "bf16" if cfg.dtype == "bfloat16" else "f32", "data": "synthetic",
+        "config": {"workload": workload, "batch_per_gpu": cfg.batch, "n_q_heads": cfg.n_q_heads,
+                   "n_kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim, "context": max(cfg.prefix_lens),
+                   "page": cfg.page_size, "block": cfg.block_size, "top_k": cfg.top_k,
+                   "rep_mode": args.rep_mode, "n_splits": n_splits, "k_bar": "bf16" if args.kbar_bf16 else "f32",
+                   "parallelism": (f"kv-head shard x{world}" if head_shard else f"batch-shard x{world}"),
+                   "timing": f"median of {R} regions of {K} steps, each between synchronise + barrier, max over ranks",
+                   "l2": f"{n_pools} layer pools rotated, {(kv_bytes + sel_bytes) >> 20} MiB read per step "
+                         "(> 126 MB L2), no flush; cold_l2 = flushed before every step"},
+        "us_per_layer": step_us["median"], "us_per_layer_stats": step_us,
+        "kernel_us": {"select": sel_us, "sparse_decode": att_us, "finalize": 0.0},
+        "roofline": {"bound": "hbm", "kernel": "condition_block_finalize_attention_kernel",
+                     "achieved": att_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                     "frac": att_gbs / peak, "traffic": committed_traffic(workload, "sparse_decode"),
+                     "bytes_per_launch": kv_bytes},
+        "roofline_select": {"bound": "hbm", "kernel": "condition_block_select_kernel", "achieved": sel_gbs,
+                            "peak": peak, "unit": "GB/s", "frac": sel_gbs / peak, "bytes_per_launch": sel_bytes,
+                            "traffic": committed_traffic(workload, "select")},
+        "e2e": {"value": replicas * cfg.batch / (e2e_us["median"] * 1e-6), "unit": UNIT,
+                "h2d_bytes_per_step": q_bytes, "d2h_bytes_per_step": q_bytes,
+                "us_per_layer": e2e_us["median"], "us_per_layer_stats": e2e_us,
+                "note": "KV pool and block summaries are cache state resident on the device; the step's "
+                        "inputs (q) and outputs cross PCIe every step"},
+        "gpu_launches": 2 * K,   # selection + attention (finalize fused) per step, in each timed region
+        "clocks": clocks,
+        "device_status": status,
+    }
+    if cold is not None:
+        line["cold_l2"] = cold
+    if main and not args.no_variants and world == 1:
+        # the reference's own mode (representatives of the unselected blocks) and the bf16 k_bar layout
+        Rv = max(5, R // 2)
+        summ_f32 = [s for _, s in layers]
+        if args.rep_mode != "hybrid":
+            line["hybrid"] = variant_record(torch, regions, cfg, layers, qs, "hybrid", args.kbar_bf16, summ_f32,
+                                            n_splits, K, Rv, workload)
+        if not args.kbar_bf16:
+            summ_bf16 = [ops.build_summaries(kv, cfg.block_size, max_blocks=nb, k_bar_dtype=torch.bfloat16)
+                         for kv, _ in layers]
+            line["kbar_bf16"] = variant_record(torch, regions, cfg, layers, qs, args.rep_mode, True, summ_bf16,
+                                               n_splits, K, Rv, workload)
+    return line
+
+
+def strong_cfg5_record(args, torch, dist, regions, world, rank, local_rank, device):
+    """kv-head shards of the ragged Llama-3-70B batch (one kv head per GPU on 8, two on 4, four on 2)."""
+    import copy
+    a = copy.copy(args)
+    a.no_variants, a.rep_mode, a.kbar_bf16 = True, "sparse_only", False
+    rec = layer_step_record(a, "cfg5_llama70b_ragged", torch, dist, regions, world, rank, local_rank, device,
+                            main=False, head_shard=True)
+    return {k: rec[k] for k in ("value", "unit", "us_per_layer", "us_per_layer_stats", "kernel_us", "scaling",
+                                "config", "roofline", "roofline_select", "device_status")}
 
 
 def llama_decode_line(steps):
@@ -402,33 +569,21 @@ def llama_decode_line(steps):
         return {"metric": "llama3_8b_decode_tokens_per_s", "value": st["tokens_per_s"], "unit": "tok/s",
                 "ms_per_decode_step": 1e3 * st["decode_s"] / max(st["decode_steps_timed"], 1),
                 "decode_steps_timed": st["decode_steps_timed"], "prefill_s": st["prefill_s"],
-                "config": {"layers": 32, "batch": 32, "prompt": 8192, "block": 64, "top_k": 64, "dtype": "bf16",
-                           "cuda_graph": True, "fused_step": True, "weights": "random init",
-                           "data": "uniform random token ids"}}
+                "config": {"layers": 32, "batch": 32, "prompt": 8192, "new_tokens": int(steps), "block": 64,
+                           "top_k": 64, "dtype": "bf16", "cuda_graph": True, "fused_step": True,
+                           "weights": "random init", "data": "uniform random token ids"}}
     except Exception as e:   # the layer-step line above must still be printed
         return {"metric": "llama3_8b_decode_tokens_per_s", "error": f"{type(e).__name__}: {e}"[:300]}
 
 
-def run_split_kv_arm(args):
-    """Long-context split-KV (strong scaling): the blocks of every sequence are cut
-    into contiguous ranges, one per rank; every rank selects globally from the
-    replicated summaries, attends over its range and the ranks all-gather (o, lse)
-    over NCCL before the merge.  A step is the whole exchange: four launches with
-    preallocated buffers, captured per layer pool into a CUDA graph (the all-gather
-    included) unless --no-graph is given or the capture fails."""
-    import torch
-    import torch.distributed as dist
+def split_kv_record(args, torch, dist, regions, world, rank, local_rank, device):
+    """Long-context split-KV (strong scaling): the blocks of every sequence are cut into contiguous
+    ranges, one per rank; a step is the whole exchange, captured per layer pool into a CUDA graph
+    unless --no-graph is given or the capture fails."""
     from interattn_b200 import ops, partition
-    from oracle.configs import CONFIGS
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    from datetime import timedelta
-    dist.init_process_group("nccl", device_id=device, timeout=timedelta(seconds=120))
-    cfg = CONFIGS[args.workload]
+    from interattn_b200.workloads import CONFIGS
+    workload = "cfg4_longctx_128k"
+    cfg = CONFIGS[workload]
     nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
     n_pools = max(1, args.layer_pools)
     steps_obj = []
@@ -439,9 +594,9 @@ def run_split_kv_arm(args):
         g = torch.Generator(device=device).manual_seed(77 + l)
         q = torch.randn((cfg.batch, cfg.n_q_heads, cfg.head_dim), generator=g, device=device).to(cfg.torch_dtype)
         cls = partition.SplitKVDecodeAttentionP2P if args.exchange == "p2p" else partition.SplitKVDecodeAttention
-        step = cls(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=args.rep_mode, n_splits=args.n_splits or 4)
+        step = cls(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode="sparse_only", n_splits=args.n_splits or 4)
         steps_obj.append((step, q))
-    K, W = args.steps, args.warmup
+    K, R = args.steps, max(1, args.repeats)
     for step, q in steps_obj:          # communicator set-up and first launches outside any capture
         step.step(q)
     torch.cuda.synchronize()
@@ -467,49 +622,58 @@ def run_split_kv_arm(args):
             graphs = None
     run_step = (lambda i: graphs[i % n_pools].replay()) if graphs is not None else (
         lambda i: steps_obj[i % n_pools][0].step(steps_obj[i % n_pools][1]))
+    for i in range(max(args.warmup, 3)):
+        run_step(i)
+    ms = regions.run(run_step, K, R)
+    status = ops.device_status()
+    step_us = summarise(ms, K)
+    rec = {
+        "value": cfg.batch / (step_us["median"] * 1e-6), "unit": UNIT, "us_per_layer": step_us["median"],
+        "us_per_layer_stats": step_us, "scaling": "strong",
+        "config": {"workload": workload, "batch": cfg.batch, "context": max(cfg.prefix_lens), "top_k": cfg.top_k,
+                   "parallelism": f"split-kv x{world}",
+                   "exchange": ("peer stores of the (o, lse) partials from the attention kernel + flags"
+                                if args.exchange == "p2p" else "NCCL all_gather of the (o, lse) partials"),
+                   "selection": getattr(steps_obj[0][0], "selection", "replicated"),
+                   "cuda_graph": graphs is not None},
+        "gpu_launches_per_step": getattr(steps_obj[0][0], "launches_per_step", 3), "device_status": status,
+    }
+    # graphs that captured NCCL kernels keep the communicator referenced: destroy them before anything else
+    for g_ in graphs or []:
+        g_.reset()
+    for step, _ in steps_obj:
+        close = getattr(step, "close", None)
+        if close is not None:
+            close()
+    return rec
 
-    def sync_all():
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
 
+def run_split_kv_arm(args):
+    """`--workload cfg4_longctx_128k` under torchrun: the split-KV arm alone, as the job's headline line."""
+    import torch
+    import torch.distributed as dist
+    from datetime import timedelta
+    from interattn_b200 import partition
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=device, timeout=timedelta(seconds=180))
+    regions = Regions(torch, dist, world, device)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    for i in range(W):
-        run_step(i)
-    sync_all()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for i in range(K):
-        run_step(i)
-    t1.record()
-    sync_all()
+    rec = split_kv_record(args, torch, dist, regions, world, rank, local_rank, device)
     clocks = sampler.stop()
-    times = torch.tensor([t0.elapsed_time(t1)], device=device, dtype=torch.float64)
-    dist.all_reduce(times, op=dist.ReduceOp.MAX)
     if rank == 0:
-        ms = float(times[0])
-        line = {
-            "metric": METRIC, "value": cfg.batch * K / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
-            "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "batch": cfg.batch, "context": max(cfg.prefix_lens),
-                       "top_k": cfg.top_k, "rep_mode": args.rep_mode, "parallelism": f"split-kv x{world}",
-                       "exchange": ("peer stores of the (o, lse) partials from the attention kernel + flags"
-                                    if args.exchange == "p2p" else "NCCL all_gather of the (o, lse) partials")
-                                   + ", selection replicated",
-                       "cuda_graph": graphs is not None},
-            "us_per_layer": 1e3 * ms / K, "gpu_launches": 3 * K, "clocks": clocks, "device_status": ops.device_status(),
-        }
+        line = {"metric": METRIC, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "repeats": args.repeats, "ms_per_step": rec["us_per_layer"] * 1e-3, "higher_is_better": True,
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "clocks": clocks,
+                "gpu_launches": rec["gpu_launches_per_step"] * args.steps}
+        line.update(rec)
         print(json.dumps(line), flush=True)
-    if graphs is not None:
-        # the captured graphs hold the communicator's kernels; destroying the communicator under them
-        # did not return on two GPUs - drop the graphs, drain the device and leave without the teardown
-        del graphs, run_step
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        os._exit(0)
-    dist.destroy_process_group()
+    sys.stdout.flush()
+    partition.ordered_shutdown()
 
 
 def main():

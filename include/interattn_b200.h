@@ -84,6 +84,9 @@ typedef struct ia_geom {
   int32_t max_blocks;   /* blocks per (sequence, kv head) in the summary arrays */
   int32_t dtype;        /* ia_dtype of q, pools, k_max/k_min/v_bar */
   int32_t reserved;     /* flags: IA_GEOM_KBAR_BF16, else 0 */
+  int32_t n_pool_pages; /* physical pages in k_pool / v_pool; block-table entries are checked against
+                           it before they are used.  0: unknown, entries are trusted. */
+  int32_t reserved2;    /* 0 */
   int64_t pool_page_stride; /* in elements */
   int64_t pool_head_stride; /* in elements */
 } ia_geom;
@@ -115,15 +118,30 @@ typedef struct ia_select_aux {
   float* globals; /* [batch, 4, rows]  z_m, z_l, c_m, c_l (online-softmax normalisers) */
 } ia_select_aux;
 
-/* Version of this ABI; bumped on any incompatible change. */
+/* Version of this ABI; bumped on any incompatible change (2: ia_geom carries n_pool_pages). */
 int ia_abi_version(void);
 
 /* Message for the last non-OK status returned on the calling thread. */
 const char* ia_last_error_string(void);
 
-/* Reads and clears the device status word: bit 0 is set when a bounded
- * shared-memory barrier wait inside the selection kernel ran out (its results
- * are then invalid).  Synchronises the device; a debugging aid. */
+/* The device status word: kernels never trap and never wait without a limit; what goes wrong on
+ * the device is recorded here instead, as an OR of these masks.
+ *   IA_DEV_STATUS_SELECT_WAIT  a bounded shared-memory barrier wait inside the selection kernel ran
+ *                              out: that launch's selection is invalid
+ *   IA_DEV_STATUS_GEMM_WAIT    the same inside ia_llama_gemm: that product is invalid
+ *   IA_DEV_STATUS_PEER_WAIT    a bounded wait for another GPU's flag ran out (ia_finalize_exchange,
+ *                              ia_select_exchange): that step's output is invalid
+ *   IA_DEV_STATUS_BAD_INDEX    a selected block index outside [0, max_blocks), a block-table entry
+ *                              outside [0, n_pool_pages), a logical page outside the table row, or an
+ *                              index list that is not ascending was met.  The access was skipped
+ *                              (the page contributes nothing), so no memory outside the arrays the
+ *                              geometry declares is touched; the output lacks those tokens.
+ * ia_read_device_status reads and clears the word.  It synchronises the device, so call it where
+ * the host waits anyway. */
+#define IA_DEV_STATUS_SELECT_WAIT 1
+#define IA_DEV_STATUS_GEMM_WAIT 2
+#define IA_DEV_STATUS_PEER_WAIT 4
+#define IA_DEV_STATUS_BAD_INDEX 8
 int ia_read_device_status(int* out);
 
 /* Replaces _build_prompt_blocks (IMPL/core.py:449-500): one pass over the K/V
@@ -165,7 +183,10 @@ int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefi
  *   o_partial   f32 [batch, rows, n_splits, head_dim]
  *   lse_partial f32 [batch, rows, n_splits]       (-inf for an empty part)
  * block_lo/block_hi (blocks, hi exclusive; pass 0 / max_blocks for all) and
- * with_suffix restrict the call to one rank's share in multi-GPU split-KV. */
+ * with_suffix restrict the call to one rank's share in multi-GPU split-KV.
+ * sel_idx must be ascending per (sequence, kv head), as ia_select writes it.  Indices and table
+ * entries are checked against max_blocks, max_pages and n_pool_pages before use: a bad one is
+ * skipped and reported as IA_DEV_STATUS_BAD_INDEX, never dereferenced. */
 int ia_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
                      const int32_t* block_table, const int32_t* prefix_lens,
                      const int32_t* seq_lens, const int32_t* sel_idx, const int32_t* sel_count,
@@ -181,7 +202,6 @@ int ia_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
 int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, int n_parts,
                 int head_dim, void* out, int out_dtype, float* out_lse, ia_stream_t stream);
 
-/* Scratch needed by ia_decode_attention, in bytes. */
 /* ---- split-KV across GPUs with the exchange inside the kernels -------------------------
  * No counterpart in the reference (one GPU).  Instead of an all-gather after the attention
  * kernel, the kernel stores every partial into the gather buffer of every rank through
@@ -194,8 +214,8 @@ int ia_finalize(const float* o_partial, const float* lse_partial, int n_rows, in
  *              Entry my_rank is this rank's own memory, the others are peer mappings of
  *              the same allocations (CUDA IPC or symmetric memory).
  *   step_counter, grid_counter  this rank's own int32 words, zero at start.
- * A wait that runs out sets bit 4 of the device status word (ia_read_device_status) and
- * the kernel carries on; nothing spins without a limit. */
+ * A wait that runs out sets IA_DEV_STATUS_PEER_WAIT in the device status word and the kernel
+ * carries on (the output of that step is then invalid); nothing spins without a limit. */
 typedef struct ia_peer_exchange {
   int32_t n_ranks, my_rank;
   float* gather[8];
@@ -220,6 +240,9 @@ int ia_finalize_exchange(const ia_peer_exchange* exchange, int n_rows, int n_par
 int ia_finalize_gathered(const float* gathered, int n_ranks, int64_t rank_stride, int n_rows, int n_parts,
                          int head_dim, void* out, int out_dtype, ia_stream_t stream);
 
+/* Scratch needed by ia_decode_attention (and its _timed / _host forms), in bytes, on the current
+ * device: the selection list, the split-KV partials of both attention grids and, in hybrid mode,
+ * the representatives' logits. */
 int64_t ia_workspace_bytes(const ia_geom* geom, int max_sel, int n_splits, int rep_mode);
 
 /* A good n_splits for ia_sparse_decode / ia_decode_attention on the current
@@ -233,8 +256,12 @@ int ia_suggest_splits(const ia_geom* geom, int expected_blocks);
  * selection kernel, then the attention kernel with the split-KV finalize fused
  * in (the CTA that completes a (sequence, kv head) last merges its parts and
  * writes out) - two launches on one stream instead of the reference's three.
- * workspace: ia_workspace_bytes() bytes, 256-byte aligned.  out [batch, rows, head_dim] in geom->dtype.  sel_idx/sel_count
- * may be null (the selection then lives in the workspace). */
+ * Every pair is cut into n_splits parts (ia_suggest_splits).  INTERATTN_B200_DECODE_GRID=flat in the
+ * environment switches bf16 pools to a fixed grid of two CTAs per SM, each taking an equal share of
+ * all pairs' pages whatever n_splits says (slower on B200 as measured; kept for comparison).
+ * workspace: ia_workspace_bytes() bytes, 256-byte aligned.  out [batch, rows, head_dim] in
+ * geom->dtype, 16-byte aligned.  sel_idx/sel_count may be null (the selection then lives in the
+ * workspace). */
 int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool,
                         const int32_t* block_table, const int32_t* prefix_lens,
                         const int32_t* seq_lens, const ia_summaries* summaries,
@@ -282,8 +309,8 @@ int ia_decode_attention_host(const void* q_host, void* q_dev, const void* k_pool
  *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
  *  - A step whose ia_workspace_bytes() exceeds IA_NOALLOC_SCRATCH_BYTES is
  *    refused with IA_ERR_UNSUPPORTED (at the Llama-3-8B geometry, batch 16,
- *    top-64, 3 splits the step needs about 0.8 MB; hybrid mode at 32k context
- *    about 1.9 MB).
+ *    top-64, 2 splits the step needs about 4 MB on a 148-SM GPU; hybrid mode
+ *    at 32k context about 5 MB).
  *  - The first call on each device looks up the array's device address (with
  *    that device current); make that first call before any stream capture.
  *  - All calls share the one array and it keeps the previous call's contents.

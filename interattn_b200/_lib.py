@@ -24,14 +24,16 @@ IA_SELECT_TOPK, IA_SELECT_EPS = 0, 1
 IA_SELECT_TERM1_MASS_EXP = 0x100   # OR-ed into the mode
 IA_GEOM_KBAR_BF16 = 1              # ia_geom.reserved flag: k_bar stored in bf16
 IA_REP_SPARSE_ONLY, IA_REP_HYBRID = 0, 1
-ABI_VERSION = 1
+ABI_VERSION = 2
+# masks of the device status word (ia_read_device_status)
+IA_DEV_STATUS_SELECT_WAIT, IA_DEV_STATUS_GEMM_WAIT, IA_DEV_STATUS_PEER_WAIT, IA_DEV_STATUS_BAD_INDEX = 1, 2, 4, 8
 
 
 class Geom(Structure):
     _fields_ = [
         ("batch", c_int32), ("n_kv_heads", c_int32), ("group_size", c_int32), ("head_dim", c_int32),
         ("page_size", c_int32), ("block_size", c_int32), ("max_pages", c_int32), ("max_blocks", c_int32),
-        ("dtype", c_int32), ("reserved", c_int32),
+        ("dtype", c_int32), ("reserved", c_int32), ("n_pool_pages", c_int32), ("reserved2", c_int32),
         ("pool_page_stride", c_int64), ("pool_head_stride", c_int64),
     ]
 

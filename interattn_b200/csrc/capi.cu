@@ -64,6 +64,9 @@ int check_geom(const ia_geom* g) {
   const int64_t esz = g->dtype == IA_BF16 ? 2 : 4;
   if ((g->pool_head_stride * esz) % 16 != 0 || (g->pool_page_stride * esz) % 16 != 0)
     return fail(IA_ERR_BAD_ARG, "geom: pool strides must be multiples of 16 bytes");
+  if (g->n_pool_pages < 0 || g->reserved2 != 0)
+    return fail(IA_ERR_BAD_ARG, "geom: n_pool_pages %d (0 = unknown), reserved2 %d (must be 0)", g->n_pool_pages,
+                g->reserved2);
   return IA_OK;
 }
 
@@ -83,6 +86,8 @@ struct Workspace {
   float* o_partial;
   float* lse_partial;
   int* split_counters;
+  float* flat_o;    // partials of the equal-share attention grid (bf16 pools), else null
+  float* flat_lse;
   int64_t bytes;
 };
 
@@ -105,6 +110,11 @@ static Workspace carve(const ia_geom& g, int max_sel, int n_splits, int rep_mode
   w.o_partial = reinterpret_cast<float*>(take(rows * n_splits * g.head_dim * 4));
   w.lse_partial = reinterpret_cast<float*>(take(rows * n_splits * 4));
   w.split_counters = reinterpret_cast<int*>(take(pairs * 4));
+  if (decode_flat_grid_possible(g)) {
+    const int64_t slots = decode_flat_slots(g);
+    w.flat_o = reinterpret_cast<float*>(take(slots * g.group_size * g.head_dim * 4));
+    w.flat_lse = reinterpret_cast<float*>(take(slots * g.group_size * 4));
+  }
   w.bytes = off;
   return w;
 }
@@ -115,13 +125,12 @@ using namespace ia;
 
 extern "C" {
 
-int ia_abi_version(void) { return 1; }
+int ia_abi_version(void) { return 2; }
 
 const char* ia_last_error_string(void) { return tls_error; }
 
-// Reads and clears the device status word (bit 0: a bounded mbarrier wait in
-// the selection kernel ran out).  Synchronises the device; a debugging aid,
-// not part of the step.
+// Reads and clears the device status word (IA_DEV_STATUS_* masks).  Synchronises
+// the device, so it is not part of the step.
 int ia_read_device_status(int* out) {
   if (out == nullptr) return fail(IA_ERR_BAD_ARG, "out is null");
   return read_and_clear_device_status(out);
@@ -340,8 +349,8 @@ static int decode_attention_impl(const void* q, const void* k_pool, const void* 
   if (int s = check_summaries(summaries)) return s;
   if (!q || !k_pool || !v_pool || !block_table || !prefix_lens || !seq_lens)
     return fail(IA_ERR_BAD_ARG, "decode_attention: null argument");
-  if (!aligned16(k_pool) || !aligned16(v_pool) || !aligned16(q))
-    return fail(IA_ERR_BAD_ARG, "decode_attention: q and pools must be 16-byte aligned");
+  if (!aligned16(k_pool) || !aligned16(v_pool) || !aligned16(q) || !aligned16(out))
+    return fail(IA_ERR_BAD_ARG, "decode_attention: q, out and pools must be 16-byte aligned");
   const int full_mode = mode;
   mode &= 0xff;  // the high bits carry the score variant (IA_SELECT_TERM1_MASS_EXP)
   if ((mode != IA_SELECT_TOPK && mode != IA_SELECT_EPS) || (full_mode & ~(0xff | IA_SELECT_TERM1_MASS_EXP)))
@@ -359,7 +368,7 @@ static int decode_attention_impl(const void* q, const void* k_pool, const void* 
                             w.split_counters, st))
     return s;
   mark(1);
-  FusedFinalize fused{out, geom->dtype, w.split_counters};
+  FusedFinalize fused{out, geom->dtype, w.split_counters, w.flat_o, w.flat_lse};
   const int s = launch_sparse_decode(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, idx, cnt, max_sel,
                                      summaries, w.z, *geom, rep_mode, n_splits, 0, geom->max_blocks, 1, w.o_partial,
                                      w.lse_partial, &fused, st);
@@ -471,8 +480,9 @@ int ia_decode_attention_noalloc(const void* q, const void* k_pool, const void* v
   void* scratch = nullptr;
   if (int s = noalloc_scratch(&scratch)) return s;
   // Nothing in the scratch has to start at zero: the selection kernel writes the
-  // whole index list and every count, the attention kernel every (row, split)
-  // partial, and hybrid-mode logits are read only where the selection wrote them.
+  // whole index list and every count and clears the per-pair arrival counters, the
+  // attention kernel writes every partial it later merges, and hybrid-mode logits
+  // are read only where the selection wrote them.
   return decode_attention_impl(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, summaries, geom, mode, top_k,
                                eps, max_sel, rep_mode, n_splits, scratch, need, nullptr, nullptr, out, nullptr,
                                stream);

@@ -39,6 +39,16 @@ struct DecodeParams {
   int64_t page_stride, head_stride;
   int n_kv_heads, group_size, page_size, block_size, max_pages, max_blocks, max_sel;
   int rep_mode, n_splits, block_lo, block_hi, with_suffix;
+  // Guards for caller-supplied indices: a selected block outside [0, max_blocks), or a block-table
+  // entry outside [0, n_pool_pages) (n_pool_pages 0: the pool size is unknown, entries are trusted),
+  // makes its item empty - nothing is read through it - and sets DEV_STATUS_BAD_INDEX in *status.
+  int n_pool_pages;
+  int* status;  // device status word
+  // Equal-share grid (sparse_decode_mma.cu, flat kernel): partials of the (CTA, pair) segments,
+  // [slot][G][D] and [slot][G] with slot = cta + pair.
+  float* flat_o;
+  float* flat_lse;
+  int n_pairs;
 };
 
 enum : int { ITEM_PAGE = 0, ITEM_REP_TILE = 1 };
@@ -71,14 +81,20 @@ __device__ __forceinline__ ItemRange item_range(const DecodeParams& p, int seq, 
   const int32_t* idx = p.sel_idx + (int64_t)pair * p.max_sel;
   if (threadIdx.x < 2) scratch[threadIdx.x] = 0;
   __syncthreads();
-  int below_lo = 0, below_hi = 0;
+  // The list is ascending (ia_select writes it so; the header asks it of callers): the entries of the
+  // block range are then the run [#(b < lo), #(b < hi)).  A list out of order - an entry that follows
+  // a larger one - or an entry outside [0, max_blocks) is reported in the status word; the result is
+  // then unspecified but every access stays guarded.
+  int below_lo = 0, below_hi = 0, disorder = 0;
   for (int i = threadIdx.x; i < count; i += blockDim.x) {
     const int b = idx[i];
     below_lo += (b < r.lo_b);
     below_hi += (b < r.hi_b);
+    disorder |= (i > 0 && idx[i - 1] >= b) || b < 0 || b >= p.max_blocks;  // out of range: dropped by the range below
   }
   if (below_lo) atomicAdd(&scratch[0], below_lo);
   if (below_hi) atomicAdd(&scratch[1], below_hi);
+  if (disorder && p.status != nullptr) atomicOr(p.status, DEV_STATUS_BAD_INDEX);
   __syncthreads();
   r.sel_first = scratch[0];
   const int n_sel = max(scratch[1] - scratch[0], 0);
@@ -96,41 +112,114 @@ __device__ __forceinline__ ItemRange item_range(const DecodeParams& p, int seq, 
   return r;
 }
 
+// Physical page of logical page `lpage` of a sequence, or -1 (and DEV_STATUS_BAD_INDEX) when the
+// logical page lies outside the table row or the entry outside the pool: the caller then makes the
+// item empty, so a bad index or table entry is never dereferenced.
+__device__ __forceinline__ int guarded_page(const DecodeParams& p, const int32_t* table, int lpage) {
+  bool ok = lpage >= 0 && lpage < p.max_pages;
+  int page = 0;
+  if (ok) {
+    page = table[lpage];
+    ok = page >= 0 && (p.n_pool_pages <= 0 || page < p.n_pool_pages);
+  }
+  if (!ok) {
+    if (p.status != nullptr) atomicOr(p.status, DEV_STATUS_BAD_INDEX);
+    return -1;
+  }
+  return page;
+}
+
+// Item i of a (sequence, kv head) whose list starts with n_sel_items selected pages (from entry
+// sel_first of its index list), then n_rep representative tiles from block lo_b, then the suffix.
+struct ResolvedItem { int kind, first, lo, hi; };
+__device__ __forceinline__ ResolvedItem resolve_one(const DecodeParams& p, const int32_t* idx, const int32_t* table,
+                                                    int i, int sel_first, int n_sel_items, int n_rep, int lo_b,
+                                                    int hi_b, int suf_first_page, int prefix, int seq_len) {
+  const int ppb = p.block_size / p.page_size;
+  ResolvedItem it;
+  if (i < n_sel_items) {
+    const int blk = idx[sel_first + i / ppb];
+    it.kind = ITEM_PAGE;
+    it.lo = 0;
+    it.hi = 0;
+    it.first = 0;
+    if (blk < 0 || blk >= p.max_blocks) {
+      if (p.status != nullptr) atomicOr(p.status, DEV_STATUS_BAD_INDEX);
+    } else {
+      const int lpage = blk * ppb + i % ppb;
+      const int tok0 = lpage * p.page_size;
+      it.hi = max(min(p.page_size, prefix - tok0), 0);
+      if (it.hi > 0) {
+        it.first = guarded_page(p, table, lpage);
+        if (it.first < 0) { it.first = 0; it.hi = 0; }
+      }
+    }
+  } else if (i < n_sel_items + n_rep) {
+    const int b0 = lo_b + (i - n_sel_items) * kRepTile;
+    it.kind = ITEM_REP_TILE;
+    it.first = b0;
+    it.lo = 0;
+    it.hi = min(kRepTile, hi_b - b0);
+  } else {
+    const int lpage = suf_first_page + (i - n_sel_items - n_rep);
+    const int tok0 = lpage * p.page_size;
+    it.kind = ITEM_PAGE;
+    it.lo = max(prefix - tok0, 0);
+    it.hi = min(p.page_size, seq_len - tok0);
+    it.first = guarded_page(p, table, lpage);
+    if (it.first < 0) { it.first = 0; it.hi = it.lo; }
+  }
+  return it;
+}
+
 // Resolve items [chunk_begin, chunk_end) into items_s[0 ..).  All threads; ends with a barrier.
 __device__ __forceinline__ void resolve_items(const DecodeParams& p, const ItemRange& r, int seq, int head,
                                               int chunk_begin, int chunk_end, Item* items_s) {
   const int pair = seq * p.n_kv_heads + head;
   const int32_t* idx = p.sel_idx + (int64_t)pair * p.max_sel;
   const int32_t* table = p.block_table + (int64_t)seq * p.max_pages;
-  const int ppb = p.block_size / p.page_size;
   for (int i = chunk_begin + threadIdx.x; i < chunk_end; i += blockDim.x) {
-    Item it;
-    if (i < r.n_sel_items) {
-      const int blk = idx[r.sel_first + i / ppb];
-      const int lpage = blk * ppb + i % ppb;
-      const int tok0 = lpage * p.page_size;
-      it.kind = ITEM_PAGE;
-      it.lo = 0;
-      it.hi = max(min(p.page_size, r.prefix - tok0), 0);
-      it.first = it.hi > 0 ? table[lpage] : 0;
-    } else if (i < r.n_sel_items + r.n_rep) {
-      const int b0 = r.lo_b + (i - r.n_sel_items) * kRepTile;
-      it.kind = ITEM_REP_TILE;
-      it.first = b0;
-      it.lo = 0;
-      it.hi = min(kRepTile, r.hi_b - b0);
-    } else {
-      const int lpage = r.suf_first_page + (i - r.n_sel_items - r.n_rep);
-      const int tok0 = lpage * p.page_size;
-      it.kind = ITEM_PAGE;
-      it.lo = max(r.prefix - tok0, 0);
-      it.hi = min(p.page_size, r.seq_len - tok0);
-      it.first = table[lpage];
-    }
-    items_s[i - chunk_begin] = it;
+    const ResolvedItem ri = resolve_one(p, idx, table, i, r.sel_first, r.n_sel_items, r.n_rep, r.lo_b, r.hi_b,
+                                        r.suf_first_page, r.prefix, r.seq_len);
+    items_s[i - chunk_begin] = Item{ri.kind, ri.first, ri.lo, ri.hi};
   }
   __syncthreads();
 }
+
+// ---- equal shares of the flattened item list -----------------------------------------
+// The items of all (sequence, kv head) pairs, pair after pair, form one list of N items; CTA c of
+// n_ctas owns the contiguous slice [N c / n_ctas, N (c + 1) / n_ctas), which may end inside a pair
+// and start the next.  A (CTA, pair) intersection is a segment and yields one partial.  As c and
+// pair only ever step by one from a segment to the next, c + pair numbers the segments without
+// collisions: slot = c + pair.
+struct PairItems {
+  int prefix, seq_len, nb_eff, n_sel_items, n_rep, n_suf, suf_first_page;
+  __device__ __forceinline__ int total() const { return n_sel_items + n_rep + n_suf; }
+};
+__device__ __forceinline__ PairItems pair_items(const DecodeParams& p, int pair) {
+  PairItems r;
+  const int seq = pair / p.n_kv_heads;
+  const int capacity = p.max_pages * p.page_size;
+  r.prefix = min(max(p.prefix_lens[seq], 0), capacity);
+  r.seq_len = min(p.seq_lens[seq], capacity);
+  r.nb_eff = min((r.prefix + p.block_size - 1) / p.block_size, p.max_blocks);
+  const int count = max(min(p.sel_count[pair], p.max_sel), 0);
+  r.n_sel_items = count * (p.block_size / p.page_size);
+  r.n_rep = (p.rep_mode == IA_REP_HYBRID) ? (r.nb_eff + kRepTile - 1) / kRepTile : 0;
+  r.suf_first_page = r.prefix / p.page_size;
+  r.n_suf = (p.with_suffix && r.seq_len > r.prefix) ? (r.seq_len - 1) / p.page_size - r.suf_first_page + 1 : 0;
+  return r;
+}
+// first item of CTA c's slice, and the CTA that owns item i (the inverse)
+__device__ __host__ __forceinline__ int64_t flat_slice_begin(int64_t n_items, int c, int n_ctas) {
+  return n_items * c / n_ctas;
+}
+__device__ __host__ __forceinline__ int flat_cta_of(int64_t n_items, int64_t i, int n_ctas) {
+  return (int)(((i + 1) * n_ctas + n_items - 1) / n_items) - 1;
+}
+// kind and pair in one word, valid rows and kv head in another; `mask` (representative tiles): bit t
+// set = block first + t is selected and contributes its tokens, not its representative
+struct __align__(16) FlatItem { int kind_pair, first, lohi_head, mask; };
 
 // ---- exchange of the partials with peer GPUs ---------------------------------------
 // Gather buffer of a rank: [2 (step parity)][n_ranks][chunk_floats]; a chunk is o [rows, n_splits, D]

@@ -21,7 +21,12 @@ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // Bit set by a kernel whose bounded wait (mbarrier) ran out; read with
 // ia_read_device_status().  Waiting is always bounded so that a programming
 // error shows up as a status bit instead of a hung GPU.
-enum : int { DEV_STATUS_SELECT_WAIT_TIMEOUT = 1, DEV_STATUS_GEMM_WAIT_TIMEOUT = 2, DEV_STATUS_PEER_WAIT_TIMEOUT = 4 };
+enum : int {
+  DEV_STATUS_SELECT_WAIT_TIMEOUT = IA_DEV_STATUS_SELECT_WAIT,
+  DEV_STATUS_GEMM_WAIT_TIMEOUT = IA_DEV_STATUS_GEMM_WAIT,
+  DEV_STATUS_PEER_WAIT_TIMEOUT = IA_DEV_STATUS_PEER_WAIT,
+  DEV_STATUS_BAD_INDEX = IA_DEV_STATUS_BAD_INDEX
+};
 int* device_status_address();  // device address of the status word on the current device
 int read_and_clear_device_status(int* out);  // defined next to the kernel that owns the word
 
@@ -160,7 +165,17 @@ struct FusedFinalize {
   void* out;            // [batch, rows, D]
   int out_dtype;        // ia_dtype
   int* split_counters;  // [batch * kv heads], zero at launch
+  float* flat_o;        // partials of the equal-share grid, decode_flat_partial_floats() floats (o, then lse)
+  float* flat_lse;
 };
+// The one-call layer-step cuts the items of all (sequence, kv head) pairs into equal shares for
+// decode_flat_ctas() CTAs where decode_flat_grid_applies(); its partials need this many floats.
+int decode_flat_ctas();
+bool decode_flat_grid_applies(const ia_geom& g, bool fused_finalize, bool full_range, bool exchange);
+bool decode_flat_grid_possible(const ia_geom& g);  // the same without the environment switch: sizes the workspace
+inline int64_t decode_flat_slots(const ia_geom& g) {
+  return (int64_t)decode_flat_ctas() + (int64_t)g.batch * g.n_kv_heads;  // one per (CTA, pair) segment
+}
 int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* block_table, const int32_t* prefix_lens,
                          const int32_t* seq_lens, const int32_t* sel_idx, const int32_t* sel_count,

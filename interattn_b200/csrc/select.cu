@@ -71,6 +71,29 @@ int read_and_clear_device_status(int* out) {
 
 namespace {
 
+// Profiling build (-DIA_SELECT_TRACE): thread 0 of every CTA leaves time stamps (microseconds since the
+// CTA started, from the nanosecond global timer) in the first floats of its pair's aux.score row instead
+// of the scores - a timeline of the kernel's phases without a profiler.  Expands to nothing otherwise.
+#ifdef IA_SELECT_TRACE
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define IA_TRACE_BEGIN()                                                                              \
+  const unsigned long long trace_t0 = trace_now();                                                     \
+  if (threadIdx.x == 0 && p.aux.delta != nullptr) /* start time modulo 2^24 ns: exact in a float */      \
+    p.aux.delta[(int64_t)blockIdx.x * 16 + 15] = (float)(trace_t0 & 0xffffffull)
+#define IA_TRACE(i)                                                                                   \
+  do {                                                                                                \
+    if (threadIdx.x == 0 && p.aux.delta != nullptr)                                                    \
+      p.aux.delta[(int64_t)blockIdx.x * 16 + (i)] = (float)(trace_now() - trace_t0) * 1e-3f;           \
+  } while (0)
+#else
+#define IA_TRACE_BEGIN() do { } while (0)
+#define IA_TRACE(i) do { } while (0)
+#endif
+
 // CTA shape: NG warp groups of four warps (one ring stage each at a time) plus one
 // TMA producer warp.  The wide shape (3 groups, 416 threads, one CTA per SM) gives a
 // single (sequence, kv head) pair the whole SM; the narrow shape (1 group, 160
@@ -189,6 +212,22 @@ __device__ __forceinline__ void norm_absorb(RowNorm& a, float z, float ch) {
   a.l = fmaf(a.l, sa, w);
   a.d = fmaf(a.d, sa, w * ch);
   a.m = m;
+}
+// Merge of the states held by the lanes whose indices differ in the bits of `xor_mask` (a set of
+// power-of-two strides below 32): one max-reduction, one rescale of every lane's sums to the
+// common maximum, one sum-reduction - two exponentials on the dependent path instead of two per level.
+template <int kFirst, int kEnd> __device__ __forceinline__ void norm_reduce_lanes(RowNorm& a) {
+  float top = a.m;
+#pragma unroll
+  for (int o = kFirst; o < kEnd; o <<= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+  const float f = (a.m == -INFINITY) ? 0.f : expf(a.m - top);  // top is finite whenever a.m is
+  float l = a.l * f, d = a.d * f;
+#pragma unroll
+  for (int o = kFirst; o < kEnd; o <<= 1) {
+    l += __shfl_xor_sync(0xffffffffu, l, o);
+    d += __shfl_xor_sync(0xffffffffu, d, o);
+  }
+  a.m = top; a.l = l; a.d = d;
 }
 __device__ __forceinline__ void norm_merge(RowNorm& a, float bm, float bl, float bd) {
   const float m = fmaxf(a.m, bm);
@@ -314,8 +353,15 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   // lengths or the query, and the attention kernel of the previous step may still be
   // reading the selection this kernel overwrites).  Then let this step's attention
   // kernel start occupying free SMs.
+  IA_TRACE_BEGIN();
+  if (tid == Shape<NG>::consumer_warps * 32) {  // the producer lane: descriptors are kernel parameters, fetch them early
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_kbar) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_kmax) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_kmin) : "memory");
+  }
   grid_dependency_wait();
   grid_launch_dependents();
+  IA_TRACE(0);
   const int prefix = p.prefix_lens[seq];
   const int nb = min((prefix + p.block_size - 1) / p.block_size, p.max_blocks);
   const int n_tiles = (nb + kTileBlocks - 1) / kTileBlocks;
@@ -357,65 +403,89 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   unsigned char* stage_base = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(d_s + (size_t)G * nbl) + 1023) & ~uintptr_t(1023));
 
-  if (tid == 0) {
-    for (int s = 0; s < n_stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kUseMma<T, G> ? 2 : kGroupWarps);
+  const int64_t sum_row0 = (int64_t)pair * p.max_blocks;  // first summary row of this pair
+  // one ring stage: the TMA box copies of 32 blocks' summaries, completing on the stage's barrier
+  auto issue_tile = [&](int lt) {
+    const int stage = lt % n_stages;
+    unsigned char* st = stage_base + (size_t)stage * L::bytes;
+    const int y = (int)sum_row0 + (t_lo + lt) * kTileBlocks;  // rows past the array are zero-filled by the TMA unit
+    mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)L::bytes);
+#pragma unroll
+    for (int j = 0; j < L::kbar_boxes; ++j)
+      tma_load_2d(st + j * L::box_bytes, &p.tm_kbar, j * L::kbar_box_cols, y, &full_bar[stage]);
+#pragma unroll
+    for (int j = 0; j < L::bnd_boxes; ++j) {
+      tma_load_2d(st + L::kbar_bytes + j * L::box_bytes, &p.tm_kmax, j * L::bnd_box_cols, y, &full_bar[stage]);
+      tma_load_2d(st + L::kbar_bytes + L::bnd_bytes + j * L::box_bytes, &p.tm_kmin, j * L::bnd_box_cols, y,
+                  &full_bar[stage]);
     }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  const T* qrow = static_cast<const T*>(p.q) + (int64_t)pair * G * D;
-  for (int i = tid; i < G * D; i += kThreads) {
-    const float v = to_f32(qrow[i]);
-    q_s[i] = v;
-    aq_s[i] = fabsf(v);
+  };
+  // The producer lane owns the barriers: it initialises them and fills the ring's first uses while
+  // the other warps still fetch the query and the value norms - the summaries are on their way
+  // before the CTA's set-up barrier.  The consumers touch the barriers only after that barrier.
+  // With the pair to itself (C == 1) the CTA does not even wait for the sequence length: it primes
+  // the ring with the first tiles of the pair's rows of the summary arrays (they exist up to
+  // max_blocks whatever the length; a tile past the sequence's last block is awaited and skipped),
+  // so the length's load latency is off the path to the first data.
+  const int n_primed = C == 1 ? min(n_stages, nb_cap / kTileBlocks) : min(n_stages, n_my_tiles);
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      for (int s = 0; s < n_stages; ++s) {
+        mbar_init(&full_bar[s], 1);
+        mbar_init(&empty_bar[s], kUseMma<T, G> ? 2 : kGroupWarps);
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      for (int lt = 0; lt < n_primed; ++lt) issue_tile(lt);
+    }
+    __syncwarp();
+  } else {
+    const T* qrow = static_cast<const T*>(p.q) + (int64_t)pair * G * D;
+    for (int i = tid; i < G * D; i += kConsumerWarps * 32) {
+      const float v = to_f32(qrow[i]);
+      q_s[i] = v;
+      aq_s[i] = fabsf(v);
+    }
   }
   const float* vn_g = p.v_norm_max + (int64_t)pair * p.max_blocks;
   {
+    // value norms of every block the arrays hold, four loads in flight per thread before the first
+    // use of the sequence length (entries past the last block are parked but never read)
     float bmax = 0.f;  // b_all = max_b v_norm_max[b]
-    for (int b = tid; b < nb; b += kThreads) {
-      const float v = vn_g[b];
-      vn_s[b] = v;
-      bmax = fmaxf(bmax, v);
+    if (warp != kConsumerWarps) {
+      constexpr int kStride = kConsumerWarps * 32;
+      for (int base = tid; base < p.max_blocks; base += 4 * kStride) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = base + j * kStride < p.max_blocks ? vn_g[base + j * kStride] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int b = base + j * kStride;
+          if (b < p.max_blocks) vn_s[b] = v[j];
+          if (b < nb) bmax = fmaxf(bmax, v[j]);
+        }
+      }
+      bmax = warp_max(bmax);
     }
-    bmax = warp_max(bmax);
     if (lane == 0) redb_s[warp] = bmax;
   }
   __syncthreads();
+  IA_TRACE(1);
 
   const float root = sqrtf((float)D);
   const float log_full = logf((float)p.block_size);
-  const int64_t sum_row0 = (int64_t)pair * p.max_blocks;  // first summary row of this pair
 
   // ---- phase 1: stream the summaries, s / delta per (row, block) -----------------
   if (warp == kConsumerWarps) {
     // producer: one elected lane issues the TMA box copies of each stage
     bool alive = true;
-    const int row0 = (int)sum_row0;
-    for (int lt = 0; lt < n_my_tiles; ++lt) {
-      const int t = t_lo + lt;
+    for (int lt = n_primed; lt < n_my_tiles; ++lt) {  // the first use of every stage was issued above
       const int stage = lt % n_stages;
       const int use = lt / n_stages;
-      if (use > 0 && alive) {
-        if (!mbar_wait(&empty_bar[stage], (uint32_t)((use - 1) & 1))) {
-          alive = false;
-          if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
-        }
+      if (alive && !mbar_wait(&empty_bar[stage], (uint32_t)((use - 1) & 1))) {
+        alive = false;
+        if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
       }
-      if (lane == 0) {
-        unsigned char* st = stage_base + (size_t)stage * L::bytes;
-        const int y = row0 + t * kTileBlocks;  // rows past the array are zero-filled by the TMA unit
-        mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)L::bytes);
-#pragma unroll
-        for (int j = 0; j < L::kbar_boxes; ++j)
-          tma_load_2d(st + j * L::box_bytes, &p.tm_kbar, j * L::kbar_box_cols, y, &full_bar[stage]);
-#pragma unroll
-        for (int j = 0; j < L::bnd_boxes; ++j) {
-          tma_load_2d(st + L::kbar_bytes + j * L::box_bytes, &p.tm_kmax, j * L::bnd_box_cols, y, &full_bar[stage]);
-          tma_load_2d(st + L::kbar_bytes + L::bnd_bytes + j * L::box_bytes, &p.tm_kmin, j * L::bnd_box_cols, y,
-                      &full_bar[stage]);
-        }
-      }
+      if (lane == 0) issue_tile(lt);
       __syncwarp();
     }
   } else if constexpr (kUseMma<T, G>) {
@@ -451,7 +521,8 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     const uint32_t row_xor = (uint32_t)(arow & 7);
     RowNorm rn[2] = {{-INFINITY, 0.f, 0.f}, {-INFINITY, 0.f, 0.f}};
     bool alive = true;
-    for (int lt = slot; slot < n_slots && lt < n_my_tiles; lt += n_slots) {
+    int lt = slot;
+    for (; slot < n_slots && lt < n_my_tiles; lt += n_slots) {
       const int t = t_lo + lt;
       const int stage = lt % n_stages;
       const int use = lt / n_stages;
@@ -459,6 +530,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         alive = false;
         if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
       }
+      if (lt == slot) IA_TRACE(2);
       const uint32_t st = smem_u32(stage_base + (size_t)stage * L::bytes);
       float cd[4] = {0.f, 0.f, 0.f, 0.f};
       float xp[4] = {0.f, 0.f, 0.f, 0.f}, xm[4] = {0.f, 0.f, 0.f, 0.f};  // k_max . q+, k_max . q-
@@ -524,7 +596,9 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           const int64_t o = ((int64_t)pair * G + g) * p.max_blocks + b;
           if (p.aux.s != nullptr) p.aux.s[o] = s;
           if (p.aux.z != nullptr) p.aux.z[o] = z;
+#ifndef IA_SELECT_TRACE
           if (p.aux.delta != nullptr) p.aux.delta[o] = delta;
+#endif
         }
       };
       const int b0 = t * kTileBlocks + mh * 16 + n;
@@ -548,18 +622,20 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           finish(kq * 2 + (e & 1), b0 + (e >> 1) * 8, cd[e], xp[e] + nm[e], np_[e] + xm[e], rn[e & 1]);
       }
     }
+    // primed tiles past the sequence's last one: nothing to score, but their copies must have landed
+    // before this CTA's shared memory can go away
+    for (; slot < n_slots && lt < n_primed; lt += n_slots)
+      if (alive && !mbar_wait(&full_bar[lt % n_stages], 0u)) {
+        alive = false;
+        if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
+      }
     // rows held by this lane: G <= 4: 2 (kq & 1) + {0, 1}, shared by the 16 lanes with the same
     // kq & 1; else 2 kq + {0, 1}, shared by 8 lanes.  Merge them; one lane per row reports.
+    IA_TRACE(3);
     constexpr int kFirstXor = G <= 4 ? 2 : 4;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-#pragma unroll
-      for (int o = kFirstXor; o < 32; o <<= 1) {
-        const float om = __shfl_xor_sync(0xffffffffu, rn[r].m, o);
-        const float ol = __shfl_xor_sync(0xffffffffu, rn[r].l, o);
-        const float od = __shfl_xor_sync(0xffffffffu, rn[r].d, o);
-        norm_merge(rn[r], om, ol, od);
-      }
+      norm_reduce_lanes<kFirstXor, 32>(rn[r]);
       const int g = (G <= 4 ? (kq & 1) : kq) * 2 + r;
       const bool reporter = (G <= 4) ? (lane < 2) : (n == 0);
       if (reporter && g < G) {
@@ -578,7 +654,8 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     for (int r = 0; r < kRowsPerWarp; ++r) rn[r] = RowNorm{-INFINITY, 0.f, 0.f};
     const int n_groups = n_slots;  // see the note on the ring geometry above
     bool alive = true;
-    for (int lt = group; group < n_groups && lt < n_my_tiles; lt += n_groups) {
+    int lt = group;
+    for (; group < n_groups && lt < n_my_tiles; lt += n_groups) {
       const int t = t_lo + lt;
       const int stage = lt % n_stages;
       const int use = lt / n_stages;
@@ -666,21 +743,22 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           const int64_t o = ((int64_t)pair * G + g) * p.max_blocks + b;
           if (p.aux.s != nullptr) p.aux.s[o] = s;
           if (p.aux.z != nullptr) p.aux.z[o] = z;
+#ifndef IA_SELECT_TRACE
           if (p.aux.delta != nullptr) p.aux.delta[o] = delta;
+#endif
         }
       }
       group_sync(group);  // partial sums may be overwritten from here on
     }
+    for (; group < n_groups && lt < n_primed; lt += n_groups)  // primed tiles past the last one: see above
+      if (alive && !mbar_wait(&full_bar[lt % n_stages], 0u)) {
+        alive = false;
+        if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
+      }
     // this warp scored rows wq, wq + 4, ...: merge its 32 lanes, lane 0 reports
 #pragma unroll
     for (int r = 0; r < kRowsPerWarp; ++r) {
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float om = __shfl_xor_sync(0xffffffffu, rn[r].m, o);
-        const float ol = __shfl_xor_sync(0xffffffffu, rn[r].l, o);
-        const float od = __shfl_xor_sync(0xffffffffu, rn[r].d, o);
-        norm_merge(rn[r], om, ol, od);
-      }
+      norm_reduce_lanes<1, 32>(rn[r]);
       const int g = wq + r * kGroupWarps;
       if (lane == 0 && g < G) {
         red_s[(warp * 16 + g) * 3 + 0] = rn[r].m;
@@ -690,6 +768,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     }
   }
   __syncthreads();
+  IA_TRACE(4);
 
   // ---- phase 2: merge the warps' row normalisers (warp g merges row g as a tree) ---------
   for (int g = warp; g < G; g += kWarps) {
@@ -698,32 +777,26 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     const bool has = lane < kConsumerWarps && (kUseMma<T, G> ? true : (lane % kGroupWarps == g % kGroupWarps));
     RowNorm tot{-INFINITY, 0.f, 0.f};
     if (has) tot = RowNorm{red_s[(lane * 16 + g) * 3], red_s[(lane * 16 + g) * 3 + 1], red_s[(lane * 16 + g) * 3 + 2]};
-#pragma unroll
-    for (int o = 1; o < 16; o <<= 1) {
-      const float om = __shfl_xor_sync(0xffffffffu, tot.m, o);
-      const float ol = __shfl_xor_sync(0xffffffffu, tot.l, o);
-      const float od = __shfl_xor_sync(0xffffffffu, tot.d, o);
-      norm_merge(tot, om, ol, od);
-    }
-    // this CTA's share of row g goes to every CTA of the cluster (slot = own rank)
-    if (lane < C) {
+    norm_reduce_lanes<1, 16>(tot);
+    // this CTA's share of row g goes to every CTA of the cluster (slot = own rank); a CTA that has
+    // the pair to itself keeps it where the next loop looks for it, without the cluster round trip
+    if (C == 1) {
+      if (lane == 0) {
+        xch_s[g * 3] = tot.m; xch_s[g * 3 + 1] = tot.l; xch_s[g * 3 + 2] = tot.d;
+      }
+    } else if (lane < C) {
       const uint32_t dst = map_to_rank(xch_s + (crank * 16 + g) * 3, (uint32_t)lane);
       st_cluster_f32(dst, tot.m);
       st_cluster_f32(dst + 4, tot.l);
       st_cluster_f32(dst + 8, tot.d);
     }
   }
-  cluster_sync_all();
+  if (C > 1) cluster_sync_all();
+  else __syncwarp();  // row g was parked by this very warp
   for (int g = warp; g < G; g += kWarps) {
     RowNorm tot{-INFINITY, 0.f, 0.f};
     if (lane < C) tot = RowNorm{xch_s[(lane * 16 + g) * 3], xch_s[(lane * 16 + g) * 3 + 1], xch_s[(lane * 16 + g) * 3 + 2]};
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
-      const float om = __shfl_xor_sync(0xffffffffu, tot.m, o);
-      const float ol = __shfl_xor_sync(0xffffffffu, tot.l, o);
-      const float od = __shfl_xor_sync(0xffffffffu, tot.d, o);
-      norm_merge(tot, om, ol, od);
-    }
+    if (C > 1) norm_reduce_lanes<1, 8>(tot);
     float b_all = lane < kWarps ? redb_s[lane] : 0.f;
     b_all = warp_max(b_all);
 
@@ -746,6 +819,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     }
   }
   __syncthreads();
+  IA_TRACE(5);
 
   // ---- phase 3: GQA-mean condition score -------------------------------------------
   // cond = softmax(z) (2 b_all (cosh d - 1) / denom + 2 b_c tanh(d / 2))   (IMPL/core.py:535-544)
@@ -764,11 +838,14 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         sum += pm * fmaf(norm_s[32 + g], a_term, two_bc * th);
       }
       const float sc = sum / (float)G;
-      st_cluster_f32(score_r0 + (uint32_t)b * 4u, sc);
+      if (C == 1) score_s[b] = sc;
+      else st_cluster_f32(score_r0 + (uint32_t)b * 4u, sc);
       if (p.aux.score != nullptr) p.aux.score[(int64_t)pair * p.max_blocks + b] = sc;
     }
   }
-  cluster_sync_all();
+  if (C > 1) cluster_sync_all();
+  else __syncthreads();
+  IA_TRACE(6);
   if (crank != 0) return;  // nobody reads this CTA's shared memory any more
 
   // ---- phase 4: routing ----------------------------------------------------------------
@@ -796,15 +873,9 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         const uint32_t key = b < nb ? order_key(score_s[b]) : 0u;
         const bool live = b < nb && (key & fixed_mask) == fixed;
         const uint32_t digit = (key >> shift) & 255u;
-        // scores cluster in a few bins: lanes that share the first live lane's digit
-        // send one atomic together, the rest go one by one
-        const uint32_t alive_mask = __ballot_sync(0xffffffffu, live);
-        if (alive_mask != 0u) {
-          const uint32_t lead_digit = __shfl_sync(0xffffffffu, digit, __ffs(alive_mask) - 1);
-          const uint32_t same = __ballot_sync(0xffffffffu, live && digit == lead_digit);
-          if (lane == __ffs(alive_mask) - 1) atomicAdd(&h[lead_digit], __popc(same));
-          if (live && digit != lead_digit) atomicAdd(&h[digit], 1);
-        }
+        // scores cluster in a few bins: the lanes that share a digit send one atomic together
+        const uint32_t peers = __match_any_sync(0xffffffffu, live ? digit : 0xffffffffu);
+        if (live && lane == __ffs(peers) - 1) atomicAdd(&h[digit], __popc(peers));
       }
       __syncthreads();
       // lane owns bins [8 lane, 8 lane + 8); `above` = keys in the bins of higher lanes
@@ -838,6 +909,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
       // every key of the threshold bin is wanted: the remaining digits cannot change the outcome
       if (in_bin == remaining) break;
     }
+    IA_TRACE(7);
     thr_key = fixed;
     thr_mask = fixed_mask;
     take_equal = remaining;
@@ -888,6 +960,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     }
     n_written = gt_seen + min(eq_seen, take_equal);
   }
+  IA_TRACE(8);
   const int count = max(min(n_written, p.max_sel), 0);
   for (int i = count + tid; i < p.max_sel; i += kThreads) out_idx[i] = -1;
   if (tid == 0) {
@@ -914,8 +987,20 @@ static EncodeTiledFn tensor_map_encoder() {
   return fn;
 }
 
-// a [rows, D] row-major matrix cut into boxes of 128 bytes x 32 rows with the 128-byte swizzle
+// a [rows, D] row-major matrix cut into boxes of 128 bytes x 32 rows with the 128-byte swizzle.
+// The descriptor depends only on (base, rows, D, element type); a decode loop asks for the same few
+// every step, so the last ones encoded on this thread are kept.
+struct CachedMap { const void* base; int64_t rows; int D; bool is_bf16; CUtensorMap map; };
 static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t rows, int D) {
+  constexpr int kSlots = 16;
+  static thread_local CachedMap cache[kSlots];
+  static thread_local int next_slot = 0;
+  for (int i = 0; i < kSlots; ++i)
+    if (cache[i].base == base && cache[i].rows == rows && cache[i].D == D && cache[i].is_bf16 == is_bf16 &&
+        base != nullptr) {
+      *tm = cache[i].map;
+      return IA_OK;
+    }
   EncodeTiledFn enc = tensor_map_encoder();
   if (enc == nullptr) return fail(IA_ERR_LAUNCH, "select: cuTensorMapEncodeTiled is not available from this driver");
   const int esz = is_bf16 ? 2 : 4;
@@ -928,6 +1013,8 @@ static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t 
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(IA_ERR_LAUNCH, "select: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  cache[next_slot] = CachedMap{base, rows, D, is_bf16, *tm};
+  next_slot = (next_slot + 1) % kSlots;
   return IA_OK;
 }
 
@@ -976,24 +1063,36 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   if (int s = encode_rows(&p.tm_kmax, p.k_max, sizeof(T) == 2, rows, D)) return s;
   if (int s = encode_rows(&p.tm_kmin, p.k_min, sizeof(T) == 2, rows, D)) return s;
 
-  // Narrow shape: more pairs than SMs and room for two or three CTAs per SM (each CTA
-  // pays 1 KB of reserved shared memory) with a ring of at least two stages.
-  // INTERATTN_B200_SELECT_SHAPE=wide|narrow pins the choice where it fits.
+  // Narrow shape: more pairs than SMs and room for two or three CTAs per SM (each CTA pays 1 KB of
+  // reserved shared memory) with a ring of at least two stages.  A cluster of narrow CTAs per pair
+  // (every CTA keeps only its slice of the (row, block) arrays) is built too but never chosen:
+  // on B200 it measured slower than one wide CTA per pair wherever the narrow shape does not fit a
+  // whole pair (ragged 70B batch: 162 / 181 us with clusters of 2 / 4 against 119 us) - the
+  // cluster barriers and the score hand-over cost more than the overlap of the tails returns.
+  // INTERATTN_B200_SELECT_SHAPE=wide|narrow (+ INTERATTN_B200_SELECT_CLUSTER) pin the choice where it fits.
   const char* shape = getenv("INTERATTN_B200_SELECT_SHAPE");
   const bool want_narrow = shape != nullptr ? strcmp(shape, "narrow") == 0 : n_pairs > sms;
-  if (cluster == 1 && want_narrow) {
-    const size_t fixed = PN::fixed + PN::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
-    int ctas = (n_pairs + sms - 1) / sms;
-    ctas = ctas < 2 ? 2 : (ctas > 3 ? 3 : ctas);
-    for (; ctas >= 2; --ctas) {
-      const size_t budget = (size_t)sm_smem / ctas - 1024;
-      if (budget < fixed + 2 * (size_t)L::bytes) continue;
-      int stages = (int)((budget - fixed) / L::bytes);
-      if (stages > max_tiles) stages = max_tiles < 2 ? 2 : max_tiles;
-      if (stages > kMaxStages) stages = kMaxStages;
-      p.n_stages = stages;
-      return launch_shaped<T, D, G, kNarrowGroups, KB>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
+  if (want_narrow) {
+    for (int c = cluster; c <= 8; c *= 2) {
+      p.cluster = c;
+      p.nb_loc_cap = (max_tiles / c + 1) * kTileBlocks;
+      const size_t fixed = PN::fixed + PN::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
+      int ctas = (n_pairs * c + sms - 1) / sms;
+      ctas = ctas < 2 ? 2 : (ctas > 3 ? 3 : ctas);
+      for (; ctas >= 2; --ctas) {
+        const size_t budget = (size_t)sm_smem / ctas - 1024;
+        if (budget < fixed + 2 * (size_t)L::bytes) continue;
+        int stages = (int)((budget - fixed) / L::bytes);
+        const int my_tiles = (max_tiles + c - 1) / c;
+        if (stages > my_tiles) stages = my_tiles < 2 ? 2 : my_tiles;
+        if (stages > kMaxStages) stages = kMaxStages;
+        p.n_stages = stages;
+        return launch_shaped<T, D, G, kNarrowGroups, KB>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
+      }
+      break;  // the narrow shape is only ever tried with the cluster chosen above (1 unless pinned)
     }
+    p.cluster = cluster;  // no narrow form fits: the wide shape with the cluster chosen above
+    p.nb_loc_cap = (max_tiles / cluster + 1) * kTileBlocks;
   }
   const size_t fixed = PW::fixed + PW::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
   if ((size_t)max_smem < fixed + 2 * (size_t)L::bytes)

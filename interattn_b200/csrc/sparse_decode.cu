@@ -13,7 +13,7 @@
 
 namespace ia {
 
-int launch_sparse_decode_mma(const DecodeParams& p, const ia_geom& g, cudaStream_t stream);  // bf16 tensor-core path
+int launch_sparse_decode_mma(const DecodeParams& p, const ia_geom& g, bool flat, cudaStream_t stream);  // bf16 tensor-core path
 
 namespace {
 
@@ -190,7 +190,12 @@ int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
     p.final_out = fused->out;
     p.split_counters = fused->split_counters;
     p.final_dtype = fused->out_dtype;
+    p.flat_o = fused->flat_o;
+    p.flat_lse = fused->flat_lse;
   }
+  p.n_pool_pages = g.n_pool_pages;
+  p.status = device_status_address();
+  p.n_pairs = g.batch * g.n_kv_heads;
   p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.block_table = block_table;
   p.prefix_lens = prefix_lens; p.seq_lens = seq_lens; p.sel_idx = sel_idx; p.sel_count = sel_count;
   p.v_bar = summaries ? summaries->v_bar : nullptr;
@@ -205,8 +210,12 @@ int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
   const char* force = getenv("INTERATTN_B200_DECODE_KERNEL");  // "fma" pins the portable kernel (profiling aid)
   const bool want_fma = force != nullptr && force[0] == 'f';
   if (g.dtype == IA_BF16 && g.page_size == 16 && g.group_size <= 16 && !want_fma &&
-      (g.head_dim == 128 || g.head_dim == 64))
-    return launch_sparse_decode_mma(p, g, stream);
+      (g.head_dim == 128 || g.head_dim == 64)) {
+    const bool flat = p.flat_o != nullptr &&
+                      decode_flat_grid_applies(g, fused != nullptr, block_lo <= 0 && block_hi >= g.max_blocks,
+                                               exchange != nullptr);
+    return launch_sparse_decode_mma(p, g, flat, stream);
+  }
   if (g.dtype == IA_BF16) {
     if (g.head_dim == 128) return launch_fma_group<__nv_bfloat16, 128>(p, g, stream);
     if (g.head_dim == 64) return launch_fma_group<__nv_bfloat16, 64>(p, g, stream);

@@ -59,6 +59,9 @@ class PagedKV:
     block_table: torch.Tensor
     prefix_lens: torch.Tensor
     seq_lens: torch.Tensor
+    # Pages the kernels may address (block-table entries are checked against it before use; an
+    # entry outside is skipped and reported in the device status word).  Default: the whole pool.
+    n_pool_pages: Optional[int] = None
 
     def __post_init__(self):
         _need_cuda(self.k_pool, self.v_pool, self.block_table, self.prefix_lens, self.seq_lens)
@@ -97,6 +100,7 @@ class PagedKV:
             batch=self.batch, n_kv_heads=self.n_kv_heads, group_size=int(group_size), head_dim=self.head_dim,
             page_size=self.page_size, block_size=int(block_size), max_pages=int(self.block_table.shape[1]),
             max_blocks=int(max_blocks), dtype=_DTYPES[self.k_pool.dtype], reserved=_geom_flags(summ),
+            n_pool_pages=int(self.k_pool.shape[0] if self.n_pool_pages is None else self.n_pool_pages), reserved2=0,
             pool_page_stride=int(self.k_pool.stride(0)), pool_head_stride=int(self.k_pool.stride(1)))
 
 
@@ -449,7 +453,10 @@ def decode_attention_noalloc(
 
 
 def device_status() -> int:
-    """Read and clear the device status word (non-zero: a bounded wait inside a kernel ran out)."""
+    """Read and clear the device status word, an OR of the ``_lib.IA_DEV_STATUS_*`` masks: a bounded
+    wait inside a kernel ran out (SELECT_WAIT, GEMM_WAIT, PEER_WAIT: that result is invalid), or a
+    caller-supplied block index / block-table entry was out of range and skipped (BAD_INDEX).
+    Synchronises the device."""
     lib = _lib.load()
     v = ctypes.c_int(0)
     check(lib.ia_read_device_status(ctypes.byref(v)))

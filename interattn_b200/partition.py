@@ -26,11 +26,59 @@ block is the ``(acc, m, l)`` merge of
 
 from __future__ import annotations
 
+import os
+import threading
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
+
+# The peer buffers of the in-kernel exchange are written with plain NVLink stores only.  By default
+# torch's symmetric memory also binds every buffer to an NVSwitch multicast object; a rank that
+# exits while its memory is bound to one can fault the other ranks' GPUs, and nothing here uses
+# multimem, so the binding is switched off before the first symmetric allocation.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+
+def ordered_shutdown(graphs: Sequence = (), steps: Sequence = (), group=None, watchdog_s: float = 30.0) -> bool:
+    """Leave a multi-GPU run in the order the libraries need.
+
+    A communicator cannot be destroyed while a captured CUDA graph still holds its kernels: NCCL
+    counts every graph that captured one of its collectives as a reference on the communicator and
+    its teardown waits until those references are gone, i.e. until the graphs are destroyed - a
+    teardown issued while the Python objects holding the graphs are alive therefore never returns.
+    So: (1) destroy the graphs, (2) release the split-KV step objects (their symmetric-memory
+    handles), (3) drain the device, (4) meet the other ranks, (5) destroy the process group.  The
+    last call runs under a watchdog thread: if it has not returned after ``watchdog_s`` seconds the
+    process leaves with ``os._exit(0)`` - the device is idle at that point, so nothing is cut off.
+    Returns True when the process group was destroyed normally."""
+    for g in graphs:
+        try:
+            g.reset()
+        except Exception:
+            pass
+    for s in steps:
+        close = getattr(s, "close", None)
+        if close is not None:
+            close()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if not dist.is_initialized():
+        return True
+    dist.barrier(group)
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    done = threading.Event()
+
+    def guard():
+        if not done.wait(watchdog_s):
+            os._exit(0)
+
+    threading.Thread(target=guard, daemon=True).start()
+    dist.destroy_process_group()
+    done.set()
+    return True
 
 
 # --------------------------------------------------------------------------
@@ -217,12 +265,17 @@ class SplitKVDecodeAttentionP2P:
     ranks and merges the chunks in place.  The buffers are symmetric memory
     (``torch.distributed._symmetric_memory``), mapped once at construction; a step
     allocates nothing and keeps its step counter on the device, so it can be captured into a
-    CUDA graph.  Plain peer stores only - no multicast.  Every rank must construct the
-    object (a collective) and run the same number of steps."""
+    CUDA graph.  Plain peer stores only: the buffers are not bound to an NVSwitch multicast
+    object (``TORCH_SYMM_MEM_DISABLE_MULTICAST``).  Every rank must construct the object (a
+    collective), run the same number of steps and ``close()`` it (or leave through
+    ``ordered_shutdown``) before the process group goes away.  ``check()`` reads the device status
+    word at a point where the host waits anyway: a peer wait that ran out means ``out`` of that
+    step is invalid."""
 
     def __init__(self, kv, summ, n_q_heads: int, *, top_k=None, eps=None, rep_mode: str = "sparse_only",
                  n_splits: int = 4, group=None):
         import ctypes
+        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"   # plain peer pointers only (see the module top)
         import torch.distributed._symmetric_memory as symm_mem
         from . import _lib, ops
         self.ops, self.lib, self.kv, self.summ = ops, _lib.load(), kv, summ
@@ -264,7 +317,27 @@ class SplitKVDecodeAttentionP2P:
         self.out = torch.empty((b, self.n_q_heads, d), device=dev, dtype=kv.k_pool.dtype)
         self.geom = kv.geom(self.n_q_heads // kv.n_kv_heads, summ.block_size, nb, summ)
         self.c_summ = summ.c_struct()
+        self._group = group
         dist.barrier(group)                                # every rank's buffer is zeroed and mapped
+
+    def check(self) -> None:
+        """Synchronise and raise if a bounded wait for a peer ran out during the steps so far."""
+        from ._lib import IA_DEV_STATUS_PEER_WAIT
+        status = self.ops.device_status()
+        if status & IA_DEV_STATUS_PEER_WAIT:
+            raise RuntimeError("split-KV exchange: a wait for a peer's partials ran out; the output of that step "
+                               "is invalid (a rank is missing or far behind)")
+
+    def close(self) -> None:
+        """Release the peer mappings.  Collective: every rank drains its device and meets the others
+        first, so that no peer is still storing into or polling this rank's buffers."""
+        if getattr(self, "buf", None) is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(self._group)
+        self.handle = None
+        self.buf = None
+        self.px = None
 
     def step(self, q: torch.Tensor) -> torch.Tensor:
         from ._lib import check

@@ -73,10 +73,15 @@ class _CacheGeometry:
             self.capacity_pages = max(need, 2 * self.capacity_pages, 64)
             self.table = torch.arange(self.capacity_pages, dtype=torch.int32, device=self.device).view(1, -1)
 
-    def geom(self, k: torch.Tensor, group: int, block_size: int, max_blocks: int, summ=None) -> Geom:
+    def geom(self, k: torch.Tensor, group: int, block_size: int, max_blocks: int, summ=None,
+             n_tokens: Optional[int] = None) -> Geom:
+        """``k`` gives the base pointer and strides of the cache; ``n_tokens`` how many of its token rows
+        exist behind that pointer (prefix + suffix) - pages past them are outside the pool."""
+        n_tokens = int(k.shape[1]) if n_tokens is None else int(n_tokens)
         return Geom(batch=1, n_kv_heads=int(k.shape[0]), group_size=int(group), head_dim=int(k.shape[2]),
                     page_size=PAGE, block_size=int(block_size), max_pages=self.capacity_pages,
                     max_blocks=int(max_blocks), dtype=ops._DTYPES[k.dtype], reserved=ops._geom_flags(summ),
+                    n_pool_pages=(n_tokens + PAGE - 1) // PAGE, reserved2=0,
                     pool_page_stride=PAGE * int(k.shape[2]), pool_head_stride=int(k.stride(0)))
 
 
@@ -314,7 +319,8 @@ def _condition_block_decode_output_fused_triton(
     if term1_mass_exp:
         mode |= _lib.IA_SELECT_TERM1_MASS_EXP
     max_sel = max(nb, 1)
-    g = geo.geom(k_all, group, h.block_size, nb, h.summ)
+    g = geo.geom(k_all, group, h.block_size, nb, h.summ,
+                 n_tokens=max(int(k_all.shape[1]), h.prompt_len + int(k_suffix.shape[1])))
     ws_dict = workspace if workspace is not None else {}
     n_splits = ws_dict.get("b200_n_splits")
     if n_splits is None:
@@ -384,6 +390,12 @@ class ConditionBlockDecodeRunner:
         self.pos = int(pos if pos is not None else prompt_len)
         self.prompt_prefix_cache = {} if prompt_prefix_cache is None else prompt_prefix_cache
         self.workspace_by_layer: Dict[int, dict] = {}
+        # Per-step statistics, as the reference keeps them (core.py:1229-1231): one dict per layer and
+        # their sum, values left as GPU scalars so that a step never waits for the device; they are
+        # turned into numbers after generation (summarize_condition_block_step_metadata).
+        self.stats_by_layer: Dict[int, dict] = {}
+        self.aggregate_stats: Dict[str, object] = {}
+        self.skip_stats = os.environ.get("CONDITION_BLOCK_SKIP_STATS") == "1"
         self.static_suffix = False
         self.suffix_len_dev = torch.zeros((), dtype=torch.int32, device=device or "cuda")
 
@@ -391,9 +403,21 @@ class ConditionBlockDecodeRunner:
         inside = self.layer_idx_set is None or int(layer_idx) in self.layer_idx_set
         return inside and int(layer_idx) >= self.full_attention_layers
 
+    def summarize(self) -> dict:
+        """The step's statistics, still lazy (core.py:1250-1251, 1429-1438)."""
+        return _summarize_stats_lazy(self.aggregate_stats, self.stats_by_layer)
+
     def reset_step(self, pos) -> None:
         self.pos = int(pos)
         self.suffix_len_dev.fill_(max(self.pos + 1 - self.prompt_len, 0))
+        self.stats_by_layer.clear()
+        self.aggregate_stats.clear()
+
+    def _record(self, layer_idx, stats) -> None:
+        if stats is None:
+            return
+        self.stats_by_layer[int(layer_idx)] = stats
+        _merge_stats_lazy(self.aggregate_stats, stats)
 
     def hybrid_attention_forward(self, module, query, key, value, attention_mask, scaling, dropout=0.0, **kwargs):
         layer_idx = getattr(module, "layer_idx", None)
@@ -403,6 +427,8 @@ class ConditionBlockDecodeRunner:
             return _sdpa_prefill(query, key, value, scaling)
         if layer_idx is None or not self.should_compress(layer_idx):
             visible = self.pos + 1
+            if not self.skip_stats and layer_idx is not None:
+                self._record(layer_idx, full_attention_stats_for_heads(query.shape[1], [self.pos]))
             return _sdpa_full(query, key[:, :, :visible], value[:, :, :visible], scaling)
         if query.shape[0] != 1:
             raise ValueError("condition_block fast path expects batch_size=1 and q_len=1.")
@@ -426,8 +452,115 @@ class ConditionBlockDecodeRunner:
             page_size=self.block_size, store_selected=False, output_dtype=query.dtype,
             workspace=self.workspace_by_layer.setdefault(int(layer_idx), {}), top_k=self.top_k,
             rep_mode=self.rep_mode, kv_cache=(k_all, v_all), term1_mass_exp=self.term1_mass_exp)
+        if not self.skip_stats:
+            ws = self.workspace_by_layer[int(layer_idx)]["b200_step"]
+            self._record(layer_idx, _condition_stats_from_selection(
+                ws.sel_idx, ws.sel_count, group_size=n_heads // n_kv_heads,
+                block_size=self.block_size, prompt_len=self.prompt_len,
+                suffix_len=max(self.pos + 1 - self.prompt_len, 0), rep_mode=self.rep_mode))
         out = out.reshape(n_heads, 1, d).permute(1, 0, 2).unsqueeze(0)
         return out.to(query.dtype), None
+
+
+# --------------------------------------------------------------------------
+# statistics (core.py:1382-1523)
+# --------------------------------------------------------------------------
+
+def _condition_stats_from_selection(sel_idx, sel_count, *, group_size, block_size, prompt_len, suffix_len,
+                                    rep_mode="hybrid"):
+    """The reference's ``_condition_stats`` (core.py:1441-1456) from an index list instead of a boolean
+    mask: ``sel_idx [1, Hkv, max_sel]`` / ``sel_count [1, Hkv]`` on the device.  The reference's mask is
+    the per-kv-head selection broadcast over the G query rows, so every sum over it is G times the sum
+    over kv heads.  Tensor-valued entries stay on the device (no synchronisation here).  With
+    ``rep_mode="sparse_only"`` no representative is attended, so ``hybrid_tokens`` leaves them out."""
+    n_kv_heads = int(sel_count.shape[-1])
+    # blocks of the prompt: all full but possibly the last (host arithmetic: nothing is read back)
+    n_real = (int(prompt_len) + block_size - 1) // block_size
+    n_exist = n_real
+    tail = int(prompt_len) - (n_real - 1) * block_size if n_real else 0
+    cnt = sel_count.reshape(n_kv_heads).to(torch.int64)
+    has_last = (sel_idx.reshape(n_kv_heads, -1) == n_real - 1).any(dim=-1).to(torch.int64)
+    selected_clusters = cnt.sum() * group_size
+    selected_tokens = (cnt * block_size - has_last * (block_size - tail)).sum() * group_size
+    n_rows = n_kv_heads * group_size
+    suffix_tokens = max(int(suffix_len), 0) * n_rows
+    hybrid = selected_tokens + suffix_tokens
+    if rep_mode == "hybrid":
+        hybrid = hybrid + (n_exist * n_kv_heads - cnt.sum()) * group_size
+    return {
+        "rows": n_rows,
+        "clusters": n_exist * n_rows,
+        "selected_clusters": selected_clusters,
+        "selected_tokens": selected_tokens,
+        "hybrid_tokens": hybrid,
+        "total_available": (int(prompt_len) + max(int(suffix_len), 0)) * n_rows,
+    }
+
+
+def full_attention_stats_for_heads(n_heads, pos_list):
+    """Statistics of a dense layer-step (core.py:1463-1473): every visible token is attended."""
+    total_available = sum(int(pos) + 1 for pos in pos_list) * int(n_heads)
+    return {"rows": int(n_heads) * len(pos_list), "clusters": 0, "selected_clusters": 0,
+            "selected_tokens": total_available, "hybrid_tokens": total_available,
+            "total_available": total_available}
+
+
+def _merge_stats_lazy(total, add):
+    for key, value in add.items():
+        total[key] = total[key] + value if key in total else value
+
+
+def _summarize_stats_lazy(aggregate_stats, stats_by_layer):
+    return {"aggregate": dict(aggregate_stats),
+            "by_layer": {int(i): dict(st) for i, st in stats_by_layer.items()}}
+
+
+def _to_python_number(value):
+    if torch.is_tensor(value):
+        if value.numel() != 1:
+            raise ValueError("Expected scalar tensor in condition-block stats.")
+        return int(value.detach().cpu().item())
+    return int(value)
+
+
+def _full_generation_step_metadata(model, pos_list):
+    """Statistics of a step in which every layer attends densely (the prefill step, core.py:1476-1483)."""
+    aggregate, by_layer = {}, {}
+    n_heads = int(model.config.num_attention_heads)
+    for layer_idx in range(int(model.config.num_hidden_layers)):
+        st = full_attention_stats_for_heads(n_heads, pos_list)
+        by_layer[layer_idx] = st
+        _merge_stats_lazy(aggregate, st)
+    return _summarize_stats_lazy(aggregate, by_layer)
+
+
+def summarize_condition_block_step_metadata(step_metadata):
+    """Per-generation summary of the per-step statistics (core.py:1486-1523): the only place where the
+    lazy GPU scalars are read back.  ``condition_block_equiv_budget`` = attended entries / visible tokens."""
+    if os.environ.get("CONDITION_BLOCK_SKIP_STATS") == "1":
+        return {"condition_block_stats_disabled": True}
+    aggregate, by_step = {}, []
+    for step_idx, metadata in enumerate(step_metadata):
+        if not metadata:
+            continue
+        step_aggregate = metadata.get("aggregate", {})
+        num = _to_python_number(step_aggregate.get("hybrid_tokens", 0))
+        den = max(_to_python_number(step_aggregate.get("total_available", 0)), 1)
+        by_step.append({"step": step_idx, "equiv_budget": float(num / den)})
+        for key, value in step_aggregate.items():
+            if not key.startswith("mean_"):
+                _merge_stats_lazy(aggregate, {key: value})
+    materialized = {key: _to_python_number(value) for key, value in aggregate.items()}
+    total_available = max(int(materialized.get("total_available", 0)), 1)
+    rows = max(int(materialized.get("rows", 0)), 1)
+    hybrid_tokens = int(materialized.get("hybrid_tokens", 0))
+    equiv_budget = float(hybrid_tokens / total_available)
+    return {
+        "condition_block_equiv_budget": equiv_budget,
+        "condition_block_budget": {**materialized, "mean_hybrid_tokens": float(hybrid_tokens / rows),
+                                   "mean_budget_causal": equiv_budget, "mean_budget_visible": equiv_budget,
+                                   "by_step": by_step},
+    }
 
 
 def generate_condition_block_cached(*, model, tokenizer, input_ids, attention_mask, method, device=None,
@@ -440,7 +573,10 @@ def generate_condition_block_cached(*, model, tokenizer, input_ids, attention_ma
     ``max_new_tokens``, ``full_attention_layers``, ``condition_block_size``,
     ``condition_eps`` (and optionally ``condition_top_k`` / ``condition_rep_mode``).
     Returns ``(output_ids [1, n], metadata)``; generation stops early at the
-    tokenizer's EOS id.  Batch size 1, as in the reference."""
+    tokenizer's EOS id.  Batch size 1, as in the reference.  ``metadata`` is what the
+    reference returns (``condition_block_equiv_budget`` and ``condition_block_budget``
+    summed over the prefill and every decode step, or ``condition_block_stats_disabled``
+    under ``CONDITION_BLOCK_SKIP_STATS=1``) plus ``method`` / ``prompt_len`` / ``decode_steps``."""
     if getattr(method, "condition_delta_mode", "range_bound") != "range_bound":
         raise ValueError("condition_block only supports delta_mode='range_bound'.")
     if int(input_ids.shape[0]) != 1:
@@ -449,7 +585,10 @@ def generate_condition_block_cached(*, model, tokenizer, input_ids, attention_ma
     budget = int(method.max_new_tokens)
     meta = {"method": "condition_block_b200", "prompt_len": prompt_len, "decode_steps": 0}
     if budget <= 0:
+        meta.update(summarize_condition_block_step_metadata([]))
         return torch.empty((1, 0), device=input_ids.device, dtype=input_ids.dtype), meta
+    collect_stats = os.environ.get("CONDITION_BLOCK_SKIP_STATS") != "1"
+    step_metadata = []
     stop = set()
     eos = getattr(tokenizer, "eos_token_id", None) if tokenizer is not None else None
     if eos is not None:
@@ -457,6 +596,8 @@ def generate_condition_block_cached(*, model, tokenizer, input_ids, attention_ma
     with torch.no_grad():
         out = model(input_ids=input_ids, attention_mask=attention_mask, use_cache=True)
     cache = out.past_key_values
+    if collect_stats:
+        step_metadata.append(_full_generation_step_metadata(model, [prompt_len - 1]))
     token = torch.argmax(out.logits[:, -1, :].float(), dim=-1, keepdim=True)
     tokens = [token]
     mask = attention_mask
@@ -474,10 +615,13 @@ def generate_condition_block_cached(*, model, tokenizer, input_ids, attention_ma
             with torch.no_grad():
                 out = model(input_ids=token, attention_mask=mask, past_key_values=cache, use_cache=True)
             cache = out.past_key_values
+            if collect_stats:
+                step_metadata.append(runner.summarize())
             token = torch.argmax(out.logits[:, -1, :].float(), dim=-1, keepdim=True)
             tokens.append(token)
             total += 1
             meta["decode_steps"] += 1
+    meta.update(summarize_condition_block_step_metadata(step_metadata))
     return torch.cat(tokens, dim=1), meta
 
 

@@ -24,13 +24,22 @@ condition_block_gen``):
                              contribute one representative each) and
                              condition_block_ppl/runner_quest.py:230-239
                              (sparse-only: selected blocks + suffix)
+* ``decode_attention_dense`` - the same result in the dense masked form of
+                             IMPL/legacy.py:797-868: every prefix token is
+                             scored, unselected ones are masked (the
+                             reference's dense CPU leg, timed by the benchmark)
 * ``merge_acc_m_l``        - IMPL/legacy.py:781-793
 * ``merge_o_lse``          - the same merge written for (o, lse) partials
+* ``condition_stats``      - IMPL/core.py:1441-1456 (per-step statistics)
 
 Parity status: pinned.  ``tests/test_oracle_vs_reference.py`` checks these
 functions against the reference's own functions when the reference tree is
 importable, and ``tests/test_oracle_golden.py`` checks them against vectors
-produced by the reference and committed under ``tests/golden/``.
+produced by the reference and committed under ``tests/golden/``.  Both modes of
+``decode_attention`` are pinned: ``hybrid`` to the reference's dense function
+and to its compact-SDPA function, ``sparse_only`` to the dense function called
+with ``cluster_exists`` all false (IMPL/legacy.py:828-829 then masks every
+representative, leaving selected tokens + suffix).
 One exception - parity unpinned: the ``term1_mass_exp`` branch of
 ``score_from_stats`` restates a variant the reference has only as a Triton
 kernel (IMPL/core.py:798-803, 893-896), which cannot run where the pins run.
@@ -303,6 +312,67 @@ def decode_attention(
     return (out, lse) if return_lse else out
 
 
+def decode_attention_dense(
+    q_grouped: torch.Tensor,
+    k_all: torch.Tensor,
+    v_all: torch.Tensor,
+    prefix_len: int,
+    block_size: int,
+    mask: torch.Tensor,
+    *,
+    rep_mode: str,
+    z: Optional[torch.Tensor] = None,
+    v_bar: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``decode_attention`` in the dense masked form of IMPL/legacy.py:797-868.
+
+    Every token of the blocked prefix gets a logit (one [G, nb * B] product per
+    kv head); tokens of unselected or padded positions are masked to -inf, the
+    representatives of unselected non-empty blocks enter with logit ``z``
+    (``rep_mode="hybrid"``) or are all masked (``"sparse_only"`` - the reference
+    function called with ``cluster_exists`` all false), the suffix follows, and
+    one softmax runs over the three parts.  Same result as
+    ``decode_attention``; the cost grows with the context instead of with the
+    selection, which is what makes it the reference's *dense* CPU leg."""
+    if rep_mode not in ("hybrid", "sparse_only"):
+        raise ValueError(f"unknown rep_mode {rep_mode!r}")
+    q = q_grouped.float()
+    hkv, g, d = q.shape
+    root = d ** 0.5
+    total = int(k_all.shape[1])
+    kb, nb = _blocked(k_all[:, :prefix_len].float(), block_size)      # [Hkv, nb, B, D]
+    vb, _ = _blocked(v_all[:, :prefix_len].float(), block_size)
+    counts = block_counts(prefix_len, block_size)
+    live = torch.arange(block_size).view(1, -1) < counts.view(-1, 1)   # [nb, B]
+    tok_on = mask.view(hkv, 1, nb, 1) & live.view(1, 1, nb, block_size)
+    tok_logit = torch.einsum("hgd,hbtd->hgbt", q, kb) / root
+    tok_logit = tok_logit.masked_fill(~tok_on, float("-inf"))
+    parts = [tok_logit.flatten(2).amax(dim=-1)]
+    rep_on = None
+    if rep_mode == "hybrid":
+        rep_on = ((~mask) & (counts > 0).view(1, -1)).view(hkv, 1, nb).expand(hkv, g, nb)
+        rep_logit = z.float().masked_fill(~rep_on, float("-inf"))
+        parts.append(rep_logit.amax(dim=-1))
+    suf_logit = None
+    if total > prefix_len:
+        suf_logit = torch.einsum("hgd,htd->hgt", q, k_all[:, prefix_len:total].float()) / root
+        parts.append(suf_logit.amax(dim=-1))
+    top = torch.stack(parts, dim=0).amax(dim=0)                        # [Hkv, G]
+    safe = torch.where(torch.isfinite(top), top, torch.zeros_like(top))
+    tok_w = torch.exp(tok_logit - safe[:, :, None, None]).masked_fill(~tok_on, 0.0)
+    norm = tok_w.flatten(2).sum(dim=-1)
+    num = torch.einsum("hgbt,hbtd->hgd", tok_w, vb)
+    if rep_on is not None:
+        rep_w = torch.exp(rep_logit - safe[:, :, None]).masked_fill(~rep_on, 0.0)
+        norm = norm + rep_w.sum(dim=-1)
+        num = num + torch.einsum("hgb,hbd->hgd", rep_w, v_bar.float())
+    if suf_logit is not None:
+        suf_w = torch.exp(suf_logit - safe[:, :, None])
+        norm = norm + suf_w.sum(dim=-1)
+        num = num + torch.einsum("hgt,htd->hgd", suf_w, v_all[:, prefix_len:total].float())
+    return num / norm.clamp_min(1e-30).unsqueeze(-1)
+
+
 # --------------------------------------------------------------------------
 # split-KV merge
 # --------------------------------------------------------------------------
@@ -330,6 +400,30 @@ def merge_o_lse(o: torch.Tensor, lse: torch.Tensor) -> Tuple[torch.Tensor, torch
     total = torch.where(den > 0, safe_top[:, 0] + torch.log(den.clamp_min(1e-30)),
                         torch.full_like(den, float("-inf")))
     return out, total
+
+
+# --------------------------------------------------------------------------
+# per-step statistics
+# --------------------------------------------------------------------------
+
+def condition_stats(mask: torch.Tensor, counts: torch.Tensor, group_size: int, prompt_len: int,
+                    suffix_len: int) -> Dict[str, int]:
+    """The reference's per-layer step statistics (IMPL/core.py:1441-1456) for a per-kv-head block mask
+    [Hkv, nb] (the reference's ``selected`` is that mask broadcast over the G query rows)."""
+    hkv = int(mask.shape[0])
+    rows = hkv * int(group_size)
+    exists = counts > 0
+    selected_tokens = int((mask.long() * counts.view(1, -1)).sum()) * int(group_size)
+    reps = int(((~mask) & exists.view(1, -1)).sum()) * int(group_size)
+    suffix_tokens = max(int(suffix_len), 0) * rows
+    return {
+        "rows": rows,
+        "clusters": int(exists.sum()) * rows,
+        "selected_clusters": int(mask.sum()) * int(group_size),
+        "selected_tokens": selected_tokens,
+        "hybrid_tokens": selected_tokens + reps + suffix_tokens,
+        "total_available": (int(prompt_len) + max(int(suffix_len), 0)) * rows,
+    }
 
 
 # --------------------------------------------------------------------------

@@ -13,7 +13,12 @@ For each case the reference's own functions are called on seeded inputs
   tensor the reference averages over the query group right before comparing
   with eps (the function does not return it)
 * ``_condition_block_decode_output_dense`` -> hybrid attention output for the
-  top-k mask (score descending, block index ascending among equals)
+  top-k mask (score descending, block index ascending among equals), and the
+  sparse-only output for the same mask: the same function with
+  ``cluster_exists`` all false, which masks every representative
+  (legacy.py:828-829) and leaves selected tokens + suffix
+* ``_condition_block_decode_output_compact_sdpa`` -> the reference's sparse CPU
+  path (gather the active entries, one SDPA call) for the same mask, fp32
 * the fp32 twin ``condition_block._condition_block_decode_output`` end to end
 
 Small cases carry their inputs; for the larger fp32 configuration the inputs
@@ -115,6 +120,20 @@ def reference_vectors(core, legacy, pr1, cfg: DecodeConfig, eps_quantiles=(0.25,
             selected=mask[:, None, None, :].expand(-1, g, 1, -1),
             z_logits=z_logits, v_bar=v_bar, cluster_exists=exists)
         out[pre + "hybrid_topk_out"] = dense[:, :, 0].numpy()
+        sparse = legacy._condition_block_decode_output_dense(
+            q_grouped=qg, pos_tensor=torch.tensor([slen - 1]), prompt_prefix=prefix,
+            k_suffix=k[:, plen:].float(), v_suffix=v[:, plen:].float(),
+            block_size=cfg.block_size, prompt_len=plen,
+            selected=mask[:, None, None, :].expand(-1, g, 1, -1),
+            z_logits=z_logits, v_bar=v_bar, cluster_exists=torch.zeros_like(exists))
+        out[pre + "sparse_topk_out"] = sparse[:, :, 0].numpy()
+        compact = legacy._condition_block_decode_output_compact_sdpa(
+            q_grouped=qg, pos_tensor=torch.tensor([slen - 1]), prompt_prefix=prefix,
+            k_suffix=k[:, plen:].float(), v_suffix=v[:, plen:].float(),
+            block_size=cfg.block_size, prompt_len=plen,
+            selected=mask[:, None, None, :].expand(-1, g, 1, -1),
+            attention_dtype=torch.float32)
+        out[pre + "compact_hybrid_topk_out"] = compact[:, :, 0].numpy()
         if cfg.dtype == "float32":
             twin = pr1._build_prompt_blocks(k[:, :plen], v[:, :plen], cfg.block_size)
             eps = float(out[pre + "eps1"])

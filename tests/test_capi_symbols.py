@@ -47,8 +47,9 @@ def test_ctypes_table_matches_header(lib_path):
 
 def test_geometry_struct_layout_matches_the_header():
     from interattn_b200 import _lib
-    assert ctypes.sizeof(_lib.Geom) == 10 * 4 + 2 * 8
-    assert _lib.Geom.pool_page_stride.offset == 40
+    assert ctypes.sizeof(_lib.Geom) == 12 * 4 + 2 * 8
+    assert _lib.Geom.n_pool_pages.offset == 40
+    assert _lib.Geom.pool_page_stride.offset == 48
     assert ctypes.sizeof(_lib.Summaries) == 5 * ctypes.sizeof(ctypes.c_void_p)
     assert ctypes.sizeof(_lib.SelectAux) == 5 * ctypes.sizeof(ctypes.c_void_p)
 
@@ -67,6 +68,22 @@ def test_argument_validation_needs_no_gpu(lib_path):
     assert need > 0 and need % 256 == 0
     with pytest.raises(ValueError):
         _lib.check(lib.ia_finalize(None, None, 4, 1, 128, None, 0, None, None))
+    # the pool size the block-table entries are checked against: never negative, spare field zero
+    g.n_pool_pages = -3
+    assert lib.ia_workspace_bytes(ctypes.byref(g), 4, 2, 0) == -1
+    assert b"n_pool_pages" in lib.ia_last_error_string()
+    g.n_pool_pages, g.reserved2 = 8, 1
+    assert lib.ia_workspace_bytes(ctypes.byref(g), 4, 2, 0) == -1
+    g.reserved2 = 0
+    assert lib.ia_workspace_bytes(ctypes.byref(g), 4, 2, 0) > 0
+
+
+def test_status_masks_match_the_header():
+    from interattn_b200 import _lib
+    text = open(HEADER).read()
+    for name in ("SELECT_WAIT", "GEMM_WAIT", "PEER_WAIT", "BAD_INDEX"):
+        m = re.search(rf"#define IA_DEV_STATUS_{name} (\d+)", text)
+        assert m and int(m.group(1)) == getattr(_lib, f"IA_DEV_STATUS_{name}")
 
 
 def test_operators_have_no_cpu_path():

@@ -24,7 +24,9 @@ def _rank_main(rank, world, port, rep_mode, result_path):
     import torch.distributed as dist
     from interattn_b200 import ops, partition
     from oracle.configs import CONFIGS, make_case, scaled
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    # no NVSwitch multicast anywhere in this test: ranks may leave on an error path
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     # a short collective timeout: a rank that failed must not leave the others waiting for the job's limit
@@ -109,13 +111,15 @@ def _rank_main(rank, world, port, rep_mode, result_path):
             f.write("ok" if ok and ok_p2p else f"mismatch {float((out.float() - whole.float()).abs().max())} "
                                                f"{float((eager.float() - whole.float()).abs().max())} "
                                                f"p2p {ok_p2p} {float((direct.float() - whole.float()).abs().max())}")
-    except Exception as e:   # report and leave at once; tearing the group down could wait on the peers
+        # graphs first, then the peer mappings, a drained device, the other ranks, the communicator
+        partition.ordered_shutdown(graphs=[graph, graph2], steps=[p2p])
+        with open(f"{result_path}.{rank}.shutdown", "w") as f:
+            f.write("clean")
+    except Exception as e:   # report and leave at once; the peers' bounded waits let them return too
         with open(f"{result_path}.{rank}", "w") as f:
             f.write(f"error {type(e).__name__}: {e}"[:500])
-    # Leave without tearing the communicator down: destroying it while a captured graph still
-    # holds its collective kernels did not return on two GPUs.
-    torch.cuda.synchronize()
-    os._exit(0)
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 @pytest.mark.timeout(300)
@@ -129,6 +133,7 @@ def test_split_kv_over_nccl(tmp_path, rep_mode):
     mp.spawn(_rank_main, args=(world, _free_port(), rep_mode, result), nprocs=world, join=True)
     for r in range(world):
         assert open(f"{result}.{r}").read() == "ok"
+        assert os.path.exists(f"{result}.{r}.shutdown"), "the ordered teardown did not return"
 
 
 @pytest.mark.timeout(300)
@@ -140,3 +145,4 @@ def test_split_kv_step_as_a_group_of_one(tmp_path, rep_mode):
     result = str(tmp_path / "result")
     mp.spawn(_rank_main, args=(1, _free_port(), rep_mode, result), nprocs=1, join=True)
     assert open(f"{result}.0").read() == "ok"
+    assert os.path.exists(f"{result}.0.shutdown"), "the ordered teardown did not return"

@@ -246,6 +246,27 @@ def test_one_call_layer_step_matches_the_three_calls(bundle):
         assert torch.equal(out_host, want.cpu())
 
 
+def test_equal_share_grid_matches_the_pair_grid(bundle, monkeypatch):
+    """INTERATTN_B200_DECODE_GRID=flat: the attention kernel on a fixed grid of two CTAs per SM, every
+    CTA an equal slice of all pairs' pages (slices cross pair boundaries).  Same selection, outputs
+    within tolerance of the pair grid and of the oracle (the partition differs, so not the same bits);
+    twice in a row, because the per-pair arrival counters must come back to zero."""
+    ops = _ops()
+    cfg, case, q, kv, summ = bundle
+    for rep_mode in ("sparse_only", "hybrid"):
+        monkeypatch.delenv("INTERATTN_B200_DECODE_GRID", raising=False)
+        pairs = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode, n_splits=2)
+        want = pairs.step(q).clone()
+        monkeypatch.setenv("INTERATTN_B200_DECODE_GRID", "flat")
+        flat = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode, n_splits=2)
+        for _ in range(2):
+            got = flat.step(q).clone()
+            torch.cuda.synchronize()
+            assert torch.equal(flat.sel_idx, pairs.sel_idx)
+            torch.testing.assert_close(got.float(), want.float(), **TOL[cfg.dtype])
+        assert ops.device_status() == 0
+
+
 def test_layer_step_replays_from_a_cuda_graph():
     """The step allocates nothing and reads its per-step quantities from device
     memory, so it can be captured once and replayed (the reference's graphed
@@ -370,7 +391,8 @@ def _golden(which):
 @pytest.mark.parametrize("which", ["ragged", "cfg1"])
 def test_against_reference_vectors(which):
     """End to end against what the unmodified reference produced: top-k index
-    sets from its score, and its dense hybrid output for that selection."""
+    sets from its score, its dense hybrid output for that selection and its
+    sparse-only output (the same function with every representative masked)."""
     ops = _ops()
     case, vec = _golden(which)
     cfg = case["cfg"]
@@ -381,9 +403,16 @@ def test_against_reference_vectors(which):
     o, lse = ops.sparse_decode(q, kv, idx, cnt, block_size=cfg.block_size, max_blocks=nb, rep_mode="hybrid",
                                summ=summ, z=aux["z"], n_splits=2)
     out = ops.finalize(o, lse, torch.float32).cpu()
+    o, lse = ops.sparse_decode(q, kv, idx, cnt, block_size=cfg.block_size, max_blocks=nb, rep_mode="sparse_only",
+                               n_splits=3)
+    out_sparse = ops.finalize(o, lse, torch.float32).cpu()
+    step_sparse = ops.DecodeAttention(kv, summ, q.shape[1], top_k=cfg.top_k, rep_mode="sparse_only").step(q).float().cpu()
     idx, cnt = idx.cpu(), cnt.cpu()
     tol = dict(rtol=1e-5, atol=1e-5) if cfg.dtype == "float32" else dict(rtol=1e-2, atol=2e-2)
     for b in range(cfg.batch):
+        want_sparse = torch.from_numpy(vec[f"seq{b}_sparse_topk_out"])
+        torch.testing.assert_close(out_sparse[b].reshape(want_sparse.shape), want_sparse, **tol)
+        torch.testing.assert_close(step_sparse[b].reshape(want_sparse.shape), want_sparse, **tol)
         pre = f"seq{b}_"
         ranked = vec[pre + "topk_ranked"]
         n_blocks = vec[pre + "score"].shape[1]

@@ -295,12 +295,18 @@ def test_generate_condition_block_cached_matches_oracle_greedy_tokens():
                              condition_rep_mode="hybrid")
 
     # reference loop on the CPU: layer 0 dense, layer 1 = oracle block-sparse attention
-    state = {"pos": prompt_len, "summ": None}
+    state = {"pos": prompt_len, "summ": None, "hybrid_tokens": 0, "total_available": 0, "rows": 0,
+             "selected_tokens": 0}
+
+    def count(stats):
+        for key in ("hybrid_tokens", "total_available", "rows", "selected_tokens"):
+            state[key] += int(stats[key])
 
     def hook(module, query, key, value, attention_mask, scaling, dropout=0.0, **kw):
         if query.shape[2] != 1:
             return api._sdpa_prefill(query, key, value, scaling)
         if module.layer_idx < 1:
+            count(api.full_attention_stats_for_heads(query.shape[1], [state["pos"]]))
             return api._sdpa_full(query, key[:, :, : state["pos"] + 1], value[:, :, : state["pos"] + 1], scaling)
         hkv, hq, d = key.shape[1], query.shape[1], query.shape[3]
         k_all, v_all = key[0, :, : state["pos"] + 1], value[0, :, : state["pos"] + 1]
@@ -308,6 +314,9 @@ def test_generate_condition_block_cached_matches_oracle_greedy_tokens():
             state["summ"] = orc.block_summaries(k_all[:, :prompt_len], v_all[:, :prompt_len], block)
         out, *_ = _oracle_step(query[0].reshape(hkv, hq // hkv, 1, d), k_all, v_all, prompt_len, block, top_k=top_k,
                                summ=state["summ"])
+        terms = orc.condition_terms(query[0].reshape(hkv, hq // hkv, d), state["summ"])
+        _, mask = orc.select_topk(terms["score"], state["summ"].counts, top_k)
+        count(orc.condition_stats(mask, state["summ"].counts, hq // hkv, prompt_len, state["pos"] + 1 - prompt_len))
         return out.reshape(hq, 1, d).permute(1, 0, 2).unsqueeze(0).to(query.dtype), None
 
     want = []
@@ -315,6 +324,8 @@ def test_generate_condition_block_cached_matches_oracle_greedy_tokens():
         out = model(ids, use_cache=True)
         cache, tok = out.past_key_values, out.logits[:, -1].argmax(-1, keepdim=True)
         want.append(tok)
+        for _ in range(cfg.num_hidden_layers):      # the prefill step counts as dense in every layer
+            count(api.full_attention_stats_for_heads(cfg.num_attention_heads, [prompt_len - 1]))
         original = modeling_llama.eager_attention_forward
         modeling_llama.eager_attention_forward = hook
         try:
@@ -333,6 +344,16 @@ def test_generate_condition_block_cached_matches_oracle_greedy_tokens():
         method=method, device=DEV)
     assert got.shape == (1, new_tokens) and meta["decode_steps"] == new_tokens - 1
     assert torch.equal(got.cpu(), want)
+    # the runner's statistics (lazy GPU scalars summed per step, read back once) against the oracle's
+    budget = meta["condition_block_budget"]
+    for key in ("hybrid_tokens", "total_available", "rows", "selected_tokens"):
+        assert budget[key] == state[key], key
+    assert meta["condition_block_equiv_budget"] == pytest.approx(state["hybrid_tokens"] / state["total_available"])
+    assert len(budget["by_step"]) == new_tokens and 0 < budget["by_step"][-1]["equiv_budget"] <= 1
+    # one more step by hand: summarize() per step, stats per compressed and per dense layer, no device read
+    runner = api.ConditionBlockDecodeRunner(model=gpu_model, model_config=gpu_model.config, full_attention_layers=1,
+                                            block_size=block, eps=0.0, prompt_len=prompt_len, top_k=top_k)
+    assert runner.summarize() == {"aggregate": {}, "by_layer": {}} and not runner.skip_stats
     with pytest.raises(ValueError):
         api.generate_condition_block_cached(model=gpu_model, tokenizer=None, input_ids=ids.repeat(2, 1).to(DEV),
                                             attention_mask=None, method=method, device=DEV)

@@ -54,6 +54,21 @@ def test_oracle_reproduces_reference_vectors(name, case, vec):
         got = orc.decode_attention(qg, k, v, plen, cfg.block_size, mask, rep_mode="hybrid",
                                    z=terms["z"], v_bar=summ.v_bar)
         np.testing.assert_allclose(got.numpy(), vec[pre + "hybrid_topk_out"], rtol=1e-5, atol=2e-6)
+        # the dense-form port (every prefix token scored, then masked) against the same reference vectors
+        got_dense = orc.decode_attention_dense(qg, k, v, plen, cfg.block_size, mask, rep_mode="hybrid",
+                                               z=terms["z"], v_bar=summ.v_bar)
+        np.testing.assert_allclose(got_dense.numpy(), vec[pre + "hybrid_topk_out"], rtol=1e-5, atol=2e-6)
+        # sparse-only (the benchmark's mode): the reference's dense function with every representative masked
+        for fn in (orc.decode_attention, orc.decode_attention_dense):
+            got = fn(qg, k, v, plen, cfg.block_size, mask, rep_mode="sparse_only")
+            np.testing.assert_allclose(got.numpy(), vec[pre + "sparse_topk_out"], rtol=1e-5, atol=2e-6)
+        # The reference's compact-SDPA path recomputes the representatives' logits from k_bar cast to the
+        # cache dtype (legacy.py:917) and runs one SDPA call; with a bf16 cache that rounding of k_bar is
+        # the whole difference from the dense form, hence the looser tolerance there.
+        got = orc.decode_attention(qg, k, v, plen, cfg.block_size, mask, rep_mode="hybrid",
+                                   z=terms["z"], v_bar=summ.v_bar)
+        loose = dict(rtol=1e-5, atol=2e-6) if cfg.dtype == "float32" else dict(rtol=2e-3, atol=2e-3)
+        np.testing.assert_allclose(got.numpy(), vec[pre + "compact_hybrid_topk_out"], **loose)
         if pre + "pr1_eps1_out" in vec.files:
             eps = float(vec[pre + "eps1"])
             m2 = orc.select_threshold(terms["score"], summ.counts, eps)

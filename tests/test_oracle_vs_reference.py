@@ -122,7 +122,7 @@ def test_score_known_answer_from_reference_pytest(ref):
 
 
 @pytest.mark.parametrize("name,shrink,suffix", CASES)
-@pytest.mark.parametrize("rep_mode", ["hybrid"])
+@pytest.mark.parametrize("rep_mode", ["hybrid", "sparse_only"])
 def test_attention_matches_reference_dense(ref, name, shrink, suffix, rep_mode):
     pr1, core, legacy = ref
     cfg = CONFIGS[name] if not shrink else scaled(CONFIGS[name], suffix=suffix, **shrink)
@@ -144,10 +144,22 @@ def test_attention_matches_reference_dense(ref, name, shrink, suffix, rep_mode):
             k_suffix=k[:, plen:].float(), v_suffix=v[:, plen:].float(),
             block_size=cfg.block_size, prompt_len=plen, selected=selected,
             z_logits=terms["z"][:, :, None], v_bar=v_bar,
-            cluster_exists=(summ.counts > 0).view(1, -1))
-        got = orc.decode_attention(qg[:, :, 0], k, v, plen, cfg.block_size, mask,
-                                   rep_mode="hybrid", z=terms["z"], v_bar=summ.v_bar)
-        assert torch.allclose(got, want[:, :, 0], rtol=1e-5, atol=2e-6)
+            # sparse-only = the same reference function with every representative masked (legacy.py:828-829)
+            cluster_exists=(summ.counts > 0).view(1, -1) if rep_mode == "hybrid"
+            else torch.zeros((1, summ.n_blocks), dtype=torch.bool))
+        for fn in (orc.decode_attention, orc.decode_attention_dense):
+            got = fn(qg[:, :, 0], k, v, plen, cfg.block_size, mask, rep_mode=rep_mode, z=terms["z"],
+                     v_bar=summ.v_bar)
+            assert torch.allclose(got, want[:, :, 0], rtol=1e-5, atol=2e-6)
+        if rep_mode == "hybrid":
+            # the reference's sparse CPU path (compact + one SDPA call); fp32 attention dtype.  With a bf16
+            # cache it rounds k_bar to bf16 for the representatives' logits (legacy.py:917): looser there.
+            compact = legacy._condition_block_decode_output_compact_sdpa(
+                q_grouped=qg, pos_tensor=torch.tensor([slen - 1]), prompt_prefix=theirs,
+                k_suffix=k[:, plen:].float(), v_suffix=v[:, plen:].float(), block_size=cfg.block_size,
+                prompt_len=plen, selected=selected, attention_dtype=torch.float32)
+            tol = dict(rtol=1e-5, atol=2e-6) if cfg.dtype == "float32" else dict(rtol=2e-3, atol=2e-3)
+            assert torch.allclose(got, compact[:, :, 0], **tol)
 
 
 def test_threshold_end_to_end_matches_pr1_reference(ref):
@@ -187,3 +199,19 @@ def test_merge_matches_reference_math():
     lse = m + torch.log(l)
     got, _ = orc.merge_o_lse(o, lse)
     assert torch.allclose(got, want, rtol=1e-5, atol=1e-6)
+
+
+def test_step_statistics_match_reference(ref):
+    """oracle.condition_stats against core._condition_stats on a ragged prompt (last block partial)."""
+    _, core, _ = ref
+    torch.manual_seed(9)
+    hkv, g, block, prompt_len, suffix_len = 2, 4, 64, 331, 5
+    counts = orc.block_counts(prompt_len, block)
+    nb = counts.numel()
+    mask = torch.rand(hkv, nb) > 0.5
+    mask[0, nb - 1] = True
+    selected = mask[:, None, None, :].expand(-1, g, 1, -1)
+    want = core._condition_stats(selected=selected, size=counts.view(1, -1), cluster_exists=(counts > 0).view(1, -1),
+                                 prompt_len=prompt_len, suffix_len=suffix_len)
+    got = orc.condition_stats(mask, counts, g, prompt_len, suffix_len)
+    assert {k: int(v) for k, v in want.items()} == got
