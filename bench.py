@@ -578,74 +578,91 @@ def llama_decode_line(steps):
 
 def split_kv_record(args, torch, dist, regions, world, rank, local_rank, device):
     """Long-context split-KV (strong scaling): the blocks of every sequence are cut into contiguous
-    ranges, one per rank; a step is the whole exchange, captured per layer pool into a CUDA graph
-    unless --no-graph is given or the capture fails."""
+    ranges, one per rank; a step is the whole exchange (selection, attention, merge), captured per
+    layer pool into a CUDA graph unless --no-graph is given or the capture fails.  With the in-kernel
+    exchange both forms of the selection are timed - distributed (every rank streams its own
+    summaries, two small exchanges inside the selection kernel) and replicated (every rank streams
+    all summaries, no exchange) - and the faster one is the record's value."""
     from interattn_b200 import ops, partition
     from interattn_b200.workloads import CONFIGS
     workload = "cfg4_longctx_128k"
     cfg = CONFIGS[workload]
     nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
     n_pools = max(1, args.layer_pools)
-    steps_obj = []
+    K, R = args.steps, max(1, args.repeats)
+    pools = []
     for l in range(n_pools):
         kv = make_device_layer(cfg, device, seed=l)      # same seed on every rank: a rank reads only its range
         summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb,
                                    k_bar_dtype=torch.bfloat16 if args.kbar_bf16 else torch.float32)
         g = torch.Generator(device=device).manual_seed(77 + l)
         q = torch.randn((cfg.batch, cfg.n_q_heads, cfg.head_dim), generator=g, device=device).to(cfg.torch_dtype)
-        cls = partition.SplitKVDecodeAttentionP2P if args.exchange == "p2p" else partition.SplitKVDecodeAttention
-        step = cls(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode="sparse_only", n_splits=args.n_splits or 4)
-        steps_obj.append((step, q))
-    K, R = args.steps, max(1, args.repeats)
-    for step, q in steps_obj:          # communicator set-up and first launches outside any capture
-        step.step(q)
-    torch.cuda.synchronize()
-    graphs = None
-    if not args.no_graph:
-        try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
+        pools.append((kv, summ, q))
+
+    def time_form(make_step):
+        steps_obj = [(make_step(kv, summ), q) for kv, summ, q in pools]
+        for step, q in steps_obj:          # communicator set-up and first launches outside any capture
+            step.step(q)
+        torch.cuda.synchronize()
+        graphs = None
+        if not args.no_graph:
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    for step, q in steps_obj:
+                        step.step(q)
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                graphs = []
                 for step, q in steps_obj:
-                    step.step(q)
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            graphs = []
-            for step, q in steps_obj:
-                g_ = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g_, capture_error_mode="thread_local"):
-                    step.step(q)
-                graphs.append(g_)
-        except Exception as e:   # every rank runs the same code, so every rank falls back together
-            print(f"[bench] graph capture of the split-KV step failed ({type(e).__name__}: {e}); running eagerly",
-                  file=sys.stderr, flush=True)
-            graphs = None
-    run_step = (lambda i: graphs[i % n_pools].replay()) if graphs is not None else (
-        lambda i: steps_obj[i % n_pools][0].step(steps_obj[i % n_pools][1]))
-    for i in range(max(args.warmup, 3)):
-        run_step(i)
-    ms = regions.run(run_step, K, R)
-    status = ops.device_status()
-    step_us = summarise(ms, K)
-    rec = {
+                    g_ = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g_, capture_error_mode="thread_local"):
+                        step.step(q)
+                    graphs.append(g_)
+            except Exception as e:   # every rank runs the same code, so every rank falls back together
+                print(f"[bench] graph capture of the split-KV step failed ({type(e).__name__}: {e}); running eagerly",
+                      file=sys.stderr, flush=True)
+                graphs = None
+        run_step = (lambda i: graphs[i % n_pools].replay()) if graphs is not None else (
+            lambda i: steps_obj[i % n_pools][0].step(steps_obj[i % n_pools][1]))
+        for i in range(max(args.warmup, 3)):
+            run_step(i)
+        ms = regions.run(run_step, K, R)
+        status = ops.device_status()
+        # graphs that captured NCCL kernels keep the communicator referenced: destroy them before anything else
+        for g_ in graphs or []:
+            g_.reset()
+        for step, _ in steps_obj:
+            close = getattr(step, "close", None)
+            if close is not None:
+                close()
+        return {"us_per_layer": summarise(ms, K), "cuda_graph": graphs is not None, "device_status": status,
+                "gpu_launches_per_step": getattr(steps_obj[0][0], "launches_per_step", 4)}
+
+    n_splits = args.n_splits or 4
+    forms = {}
+    if args.exchange == "p2p":
+        for selection in ("distributed", "replicated"):
+            forms[selection] = time_form(lambda kv, summ, sel=selection: partition.SplitKVDecodeAttentionP2P(
+                kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode="sparse_only", n_splits=n_splits, selection=sel))
+    else:
+        forms["replicated"] = time_form(lambda kv, summ: partition.SplitKVDecodeAttention(
+            kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode="sparse_only", n_splits=n_splits))
+    best = min(forms, key=lambda k: forms[k]["us_per_layer"]["median"])
+    step_us = forms[best]["us_per_layer"]
+    return {
         "value": cfg.batch / (step_us["median"] * 1e-6), "unit": UNIT, "us_per_layer": step_us["median"],
         "us_per_layer_stats": step_us, "scaling": "strong",
         "config": {"workload": workload, "batch": cfg.batch, "context": max(cfg.prefix_lens), "top_k": cfg.top_k,
                    "parallelism": f"split-kv x{world}",
                    "exchange": ("peer stores of the (o, lse) partials from the attention kernel + flags"
                                 if args.exchange == "p2p" else "NCCL all_gather of the (o, lse) partials"),
-                   "selection": getattr(steps_obj[0][0], "selection", "replicated"),
-                   "cuda_graph": graphs is not None},
-        "gpu_launches_per_step": getattr(steps_obj[0][0], "launches_per_step", 3), "device_status": status,
+                   "selection": best, "cuda_graph": forms[best]["cuda_graph"]},
+        "selection_forms_us": {k: v["us_per_layer"]["median"] for k, v in forms.items()},
+        "gpu_launches_per_step": forms[best]["gpu_launches_per_step"],
+        "device_status": max(v["device_status"] for v in forms.values()),
     }
-    # graphs that captured NCCL kernels keep the communicator referenced: destroy them before anything else
-    for g_ in graphs or []:
-        g_.reset()
-    for step, _ in steps_obj:
-        close = getattr(step, "close", None)
-        if close is not None:
-            close()
-    return rec
 
 
 def run_split_kv_arm(args):

@@ -24,7 +24,7 @@
  *   ia_decode_attention <- _condition_block_decode_output_fused_triton
  *                            IMPL/core.py:1035-1155 (the launches of one layer-step)
  *   ia_update_summaries <- no counterpart (the reference never re-blocks its suffix)
- *   ia_sparse_decode_exchange, ia_finalize_exchange, ia_finalize_gathered
+ *   ia_select_split, ia_sparse_decode_exchange, ia_finalize_exchange, ia_finalize_gathered
  *                       <- no counterpart (split-KV across GPUs; the reference has one GPU)
  *   ia_llama_*          <- the Hugging Face modules the reference replays around its hook in
  *                          the captured decode step, IMPL/core.py:190-316
@@ -130,7 +130,7 @@ const char* ia_last_error_string(void);
  *                              out: that launch's selection is invalid
  *   IA_DEV_STATUS_GEMM_WAIT    the same inside ia_llama_gemm: that product is invalid
  *   IA_DEV_STATUS_PEER_WAIT    a bounded wait for another GPU's flag ran out (ia_finalize_exchange,
- *                              ia_select_exchange): that step's output is invalid
+ *                              ia_select_split): that step's output is invalid
  *   IA_DEV_STATUS_BAD_INDEX    a selected block index outside [0, max_blocks), a block-table entry
  *                              outside [0, n_pool_pages), a logical page outside the table row, or an
  *                              index list that is not ascending was met.  The access was skipped
@@ -224,6 +224,37 @@ typedef struct ia_peer_exchange {
   int32_t* step_counter;
   int32_t* grid_counter;
 } ia_peer_exchange;
+/* Split-KV selection: every rank owns a contiguous range [block_lo, block_hi) of the logical blocks of
+ * every sequence (block_lo a multiple of 32; block_hi a multiple of 32 or >= max_blocks) and only its
+ * own range of the summary arrays needs to be valid.  No counterpart in the reference (one GPU; its
+ * building blocks are the chunk partials of IMPL/core.py:806-814 and their re-reduction in
+ * IMPL/page_attention.py:106-124).  The kernel streams the rank's summaries, exchanges the per-row
+ * softmax normalisers with the other ranks, scores its blocks with the global normalisers, exchanges
+ * its top_k best (score, block) candidates and takes the top_k of all candidates: sel_idx / sel_count
+ * receive the global selection, identical on every rank and - up to the rounding of the normalisers'
+ * merge order - the one ia_select computes from all blocks.  Both exchanges are plain peer stores
+ * into the buffers below plus flags polled in the rank's own memory (bounded waits:
+ * IA_DEV_STATUS_PEER_WAIT); no collective call, no multicast.  IA_SELECT_TOPK only.  The grid
+ * (pairs x cluster) must fit the SMs at once.
+ *   norm[w]   rank w's float [2][n_pairs][n_ranks][16][4]          (two step parities)
+ *   cand[w]   rank w's float [2][n_pairs][n_ranks][max_sel + 1][2]
+ *   flags[w]  rank w's int32 [2][2][n_pairs][n_ranks], zero at start
+ *             n_pairs = batch * n_kv_heads; entry my_rank is this rank's own memory, the others are
+ *             peer mappings of the same allocations
+ *   step_counter, grid_counter  this rank's own int32 words, zero at start */
+typedef struct ia_select_exchange {
+  int32_t n_ranks, my_rank;
+  float* norm[8];
+  float* cand[8];
+  int32_t* flags[8];
+  int32_t* step_counter;
+  int32_t* grid_counter;
+} ia_select_exchange;
+int ia_select_split(const void* q, const ia_summaries* summaries, const int32_t* prefix_lens,
+                    const ia_geom* geom, int top_k, int max_sel, int block_lo, int block_hi,
+                    int32_t* sel_idx, int32_t* sel_count, const ia_select_aux* aux,
+                    const ia_select_exchange* exchange, ia_stream_t stream);
+
 int ia_sparse_decode_exchange(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
                               const int32_t* prefix_lens, const int32_t* seq_lens, const int32_t* sel_idx,
                               const int32_t* sel_count, int max_sel, const ia_summaries* summaries, const float* z,
@@ -286,7 +317,10 @@ int ia_decode_attention_timed(const void* q, const void* k_pool, const void* v_p
  * pool and the summaries on the device: copies q_host -> device (async on
  * stream), runs ia_decode_attention, copies the output back into out_host and
  * waits for the stream.  q_dev/out_dev are caller-owned device staging
- * buffers of the same sizes; q_host/out_host should be pinned. */
+ * buffers of the same sizes; q_host/out_host should be pinned.  Pinned, 16-byte
+ * aligned host buffers that the device can address are read and written by the
+ * kernels directly (the query rows and the output rows cross PCIe without a copy
+ * operation on the stream); anything else is staged through q_dev / out_dev. */
 int ia_decode_attention_host(const void* q_host, void* q_dev, const void* k_pool,
                              const void* v_pool, const int32_t* block_table,
                              const int32_t* prefix_lens, const int32_t* seq_lens,

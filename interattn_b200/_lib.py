@@ -54,6 +54,11 @@ class PeerExchange(Structure):
                 ("grid_counter", c_void_p)]
 
 
+class SelectExchange(Structure):
+    _fields_ = [("n_ranks", c_int32), ("my_rank", c_int32), ("norm", c_void_p * 8), ("cand", c_void_p * 8),
+                ("flags", c_void_p * 8), ("step_counter", c_void_p), ("grid_counter", c_void_p)]
+
+
 # name -> (restype, argtypes); mirrors include/interattn_b200.h one to one
 SIGNATURES = {
     "ia_abi_version": (c_int, []),
@@ -64,6 +69,8 @@ SIGNATURES = {
                                     c_void_p]),
     "ia_select": (c_int, [c_void_p, POINTER(Summaries), c_void_p, POINTER(Geom), c_int, c_int, c_float, c_int,
                           c_void_p, c_void_p, POINTER(SelectAux), c_void_p]),
+    "ia_select_split": (c_int, [c_void_p, POINTER(Summaries), c_void_p, POINTER(Geom), c_int, c_int, c_int, c_int,
+                                c_void_p, c_void_p, POINTER(SelectAux), POINTER(SelectExchange), c_void_p]),
     "ia_sparse_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int, POINTER(Summaries), c_void_p, POINTER(Geom), c_int, c_int, c_int, c_int,
                                  c_int, c_void_p, c_void_p, c_void_p]),

@@ -179,6 +179,31 @@ int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefi
                        aux ? *aux : none, nullptr, (cudaStream_t)stream);
 }
 
+int ia_select_split(const void* q, const ia_summaries* summaries, const int32_t* prefix_lens, const ia_geom* geom,
+                    int top_k, int max_sel, int block_lo, int block_hi, int32_t* sel_idx, int32_t* sel_count,
+                    const ia_select_aux* aux, const ia_select_exchange* x, ia_stream_t stream) {
+  if (int s = check_geom(geom)) return s;
+  if (int s = check_summaries(summaries)) return s;
+  if (!q || !prefix_lens || !sel_idx || !sel_count || !x) return fail(IA_ERR_BAD_ARG, "select_split: null argument");
+  if (max_sel <= 0 || top_k < 0 || top_k > max_sel)
+    return fail(IA_ERR_BAD_ARG, "select_split: top_k %d outside [0, max_sel %d]", top_k, max_sel);
+  if (x->n_ranks < 1 || x->n_ranks > 8 || x->my_rank < 0 || x->my_rank >= x->n_ranks)
+    return fail(IA_ERR_BAD_ARG, "select_split: rank %d of %d (at most 8)", x->my_rank, x->n_ranks);
+  for (int w = 0; w < x->n_ranks; ++w)
+    if (!x->norm[w] || !x->cand[w] || !x->flags[w] || (reinterpret_cast<uintptr_t>(x->norm[w]) & 15u) != 0 ||
+        (reinterpret_cast<uintptr_t>(x->cand[w]) & 7u) != 0)
+      return fail(IA_ERR_BAD_ARG, "select_split: null or misaligned buffer of rank %d", w);
+  if (!x->step_counter || !x->grid_counter) return fail(IA_ERR_BAD_ARG, "select_split: null counter");
+  if (block_lo < 0 || block_hi < block_lo || block_lo % 32 != 0 || (block_hi % 32 != 0 && block_hi < geom->max_blocks))
+    return fail(IA_ERR_BAD_ARG, "select_split: block range [%d, %d) must start on a multiple of 32 and end on one "
+                "(or at max_blocks %d)", block_lo, block_hi, geom->max_blocks);
+  if ((int64_t)x->n_ranks * max_sel > 4096)
+    return fail(IA_ERR_UNSUPPORTED, "select_split: %d ranks x max_sel %d candidates (at most 4096)", x->n_ranks, max_sel);
+  ia_select_aux none{};
+  return launch_select(q, *summaries, prefix_lens, *geom, IA_SELECT_TOPK, top_k, 0.f, max_sel, sel_idx, sel_count,
+                       aux ? *aux : none, nullptr, (cudaStream_t)stream, x, block_lo, block_hi);
+}
+
 static int check_exchange(const ia_peer_exchange* px, int64_t n_rows, int n_parts, int head_dim) {
   if (!px) return fail(IA_ERR_BAD_ARG, "exchange: null argument");
   if (px->n_ranks < 1 || px->n_ranks > 8 || px->my_rank < 0 || px->my_rank >= px->n_ranks)
@@ -398,6 +423,23 @@ int ia_decode_attention_timed(const void* q, const void* k_pool, const void* v_p
                                events, stream);
 }
 
+// Device alias of a host buffer the GPU can address directly (pinned, mapped host memory under
+// unified addressing), or null.  INTERATTN_B200_HOST_STAGING=1 turns the direct path off (A/B runs).
+static void* device_alias_of_host(const void* host) {
+  static const bool off = [] {
+    const char* v = getenv("INTERATTN_B200_HOST_STAGING");
+    return v != nullptr && v[0] == '1';
+  }();
+  if (off) return nullptr;
+  cudaPointerAttributes a{};
+  if (cudaPointerGetAttributes(&a, host) != cudaSuccess) {
+    cudaGetLastError();  // pageable memory the runtime has never seen: not an error of this call
+    return nullptr;
+  }
+  if (a.type != cudaMemoryTypeHost || a.devicePointer == nullptr) return nullptr;
+  return (reinterpret_cast<uintptr_t>(a.devicePointer) & 15u) == 0 ? a.devicePointer : nullptr;
+}
+
 int ia_decode_attention_host(const void* q_host, void* q_dev, const void* k_pool, const void* v_pool,
                              const int32_t* block_table, const int32_t* prefix_lens, const int32_t* seq_lens,
                              const ia_summaries* summaries, const ia_geom* geom, int mode, int top_k, float eps,
@@ -408,13 +450,22 @@ int ia_decode_attention_host(const void* q_host, void* q_dev, const void* k_pool
   const size_t esz = geom->dtype == IA_BF16 ? 2 : 4;
   const size_t bytes = (size_t)geom->batch * geom->n_kv_heads * geom->group_size * geom->head_dim * esz;
   cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t e = cudaMemcpyAsync(q_dev, q_host, bytes, cudaMemcpyHostToDevice, st);
-  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "decode_attention_host: h2d: %s", cudaGetErrorString(e));
-  if (int s = ia_decode_attention(q_dev, k_pool, v_pool, block_table, prefix_lens, seq_lens, summaries, geom, mode,
-                                  top_k, eps, max_sel, rep_mode, n_splits, workspace, workspace_bytes, nullptr,
-                                  nullptr, out_dev, stream))
+  // Pinned host buffers are addressable from the device: the kernels then read the query rows and
+  // write the output rows across PCIe themselves (a kilobyte per (sequence, kv head), fetched while
+  // the first summaries and pages are in flight), which spares the two copy operations and their
+  // latency on the stream.  Pageable buffers go through the caller's staging buffers instead.
+  void* q_direct = device_alias_of_host(q_host);
+  void* out_direct = device_alias_of_host(out_host);
+  cudaError_t e = cudaSuccess;
+  if (q_direct == nullptr) {
+    e = cudaMemcpyAsync(q_dev, q_host, bytes, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "decode_attention_host: h2d: %s", cudaGetErrorString(e));
+  }
+  if (int s = ia_decode_attention(q_direct ? q_direct : q_dev, k_pool, v_pool, block_table, prefix_lens, seq_lens,
+                                  summaries, geom, mode, top_k, eps, max_sel, rep_mode, n_splits, workspace,
+                                  workspace_bytes, nullptr, nullptr, out_direct ? out_direct : out_dev, stream))
     return s;
-  e = cudaMemcpyAsync(out_host, out_dev, bytes, cudaMemcpyDeviceToHost, st);
+  if (out_direct == nullptr) e = cudaMemcpyAsync(out_host, out_dev, bytes, cudaMemcpyDeviceToHost, st);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "decode_attention_host: d2h: %s", cudaGetErrorString(e));
   return IA_OK;

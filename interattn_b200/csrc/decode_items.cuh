@@ -49,7 +49,32 @@ struct DecodeParams {
   float* flat_o;
   float* flat_lse;
   int n_pairs;
+#ifdef IA_DECODE_TRACE
+  float* trace;  // profiling build: 16 floats per CTA, time stamps of the kernel's phases
+#endif
 };
+
+// Profiling build (-DIA_DECODE_TRACE): thread 0 of every CTA leaves time stamps (microseconds since the
+// CTA started, from the nanosecond global timer) in a buffer whose address the environment variable
+// IA_TRACE_PTR gives - a timeline of the attention kernel's phases without a profiler.
+#ifdef IA_DECODE_TRACE
+__device__ __forceinline__ unsigned long long decode_trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define IA_DTRACE_BEGIN()                                                                           \
+  const unsigned long long dtrace_t0 = decode_trace_now();                                           \
+  if (threadIdx.x == 0 && p.trace != nullptr) p.trace[(int64_t)blockIdx.x * 16 + 15] = (float)(dtrace_t0 & 0xffffffull)
+#define IA_DTRACE(i)                                                                                 \
+  do {                                                                                               \
+    if (threadIdx.x == 0 && p.trace != nullptr)                                                      \
+      p.trace[(int64_t)blockIdx.x * 16 + (i)] = (float)(decode_trace_now() - dtrace_t0) * 1e-3f;     \
+  } while (0)
+#else
+#define IA_DTRACE_BEGIN() do { } while (0)
+#define IA_DTRACE(i) do { } while (0)
+#endif
 
 enum : int { ITEM_PAGE = 0, ITEM_REP_TILE = 1 };
 constexpr int kRepTile = 16;     // blocks per representative tile (= page_size rows of v_bar)
@@ -79,26 +104,34 @@ __device__ __forceinline__ ItemRange item_range(const DecodeParams& p, int seq, 
   const int pair = seq * p.n_kv_heads + head;
   const int count = min(p.sel_count[pair], p.max_sel);
   const int32_t* idx = p.sel_idx + (int64_t)pair * p.max_sel;
-  if (threadIdx.x < 2) scratch[threadIdx.x] = 0;
-  __syncthreads();
-  // The list is ascending (ia_select writes it so; the header asks it of callers): the entries of the
-  // block range are then the run [#(b < lo), #(b < hi)).  A list out of order - an entry that follows
-  // a larger one - or an entry outside [0, max_blocks) is reported in the status word; the result is
-  // then unspecified but every access stays guarded.
-  int below_lo = 0, below_hi = 0, disorder = 0;
-  for (int i = threadIdx.x; i < count; i += blockDim.x) {
-    const int b = idx[i];
-    below_lo += (b < r.lo_b);
-    below_hi += (b < r.hi_b);
-    disorder |= (i > 0 && idx[i - 1] >= b) || b < 0 || b >= p.max_blocks;  // out of range: dropped by the range below
+  int n_sel;
+  if (r.lo_b == 0 && r.hi_b >= r.nb_eff) {
+    // every block is in range: the whole list, no counting pass (and none of its barriers); entries
+    // out of range or out of order are caught where they are resolved
+    r.sel_first = 0;
+    n_sel = max(count, 0);
+  } else {
+    if (threadIdx.x < 2) scratch[threadIdx.x] = 0;
+    __syncthreads();
+    // The list is ascending (ia_select writes it so; the header asks it of callers): the entries of the
+    // block range are then the run [#(b < lo), #(b < hi)).  A list out of order - an entry that follows
+    // a larger one - or an entry outside [0, max_blocks) is reported in the status word; the result is
+    // then unspecified but every access stays guarded.
+    int below_lo = 0, below_hi = 0, disorder = 0;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+      const int b = idx[i];
+      below_lo += (b < r.lo_b);
+      below_hi += (b < r.hi_b);
+      disorder |= (i > 0 && idx[i - 1] >= b) || b < 0 || b >= p.max_blocks;  // out of range: dropped by the range below
+    }
+    if (below_lo) atomicAdd(&scratch[0], below_lo);
+    if (below_hi) atomicAdd(&scratch[1], below_hi);
+    if (disorder && p.status != nullptr) atomicOr(p.status, DEV_STATUS_BAD_INDEX);
+    __syncthreads();
+    r.sel_first = scratch[0];
+    n_sel = max(scratch[1] - scratch[0], 0);
+    __syncthreads();
   }
-  if (below_lo) atomicAdd(&scratch[0], below_lo);
-  if (below_hi) atomicAdd(&scratch[1], below_hi);
-  if (disorder && p.status != nullptr) atomicOr(p.status, DEV_STATUS_BAD_INDEX);
-  __syncthreads();
-  r.sel_first = scratch[0];
-  const int n_sel = max(scratch[1] - scratch[0], 0);
-  __syncthreads();
   const int ppb = p.block_size / p.page_size;
   r.n_sel_items = n_sel * ppb;
   r.n_rep = (p.rep_mode == IA_REP_HYBRID && r.hi_b > r.lo_b) ? (r.hi_b - r.lo_b + kRepTile - 1) / kRepTile : 0;
@@ -143,9 +176,12 @@ __device__ __forceinline__ ResolvedItem resolve_one(const DecodeParams& p, const
     it.lo = 0;
     it.hi = 0;
     it.first = 0;
-    if (blk < 0 || blk >= p.max_blocks) {
+    const int at = sel_first + i / ppb;
+    const bool disorder = i % ppb == 0 && at > 0 && idx[at - 1] >= blk;  // checked once per block
+    if (blk < 0 || blk >= p.max_blocks || disorder) {
       if (p.status != nullptr) atomicOr(p.status, DEV_STATUS_BAD_INDEX);
-    } else {
+    }
+    if (blk >= 0 && blk < p.max_blocks) {
       const int lpage = blk * ppb + i % ppb;
       const int tok0 = lpage * p.page_size;
       it.hi = max(min(p.page_size, prefix - tok0), 0);

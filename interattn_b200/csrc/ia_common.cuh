@@ -157,9 +157,11 @@ int launch_build_summaries(const void* k_pool, const void* v_pool, const int32_t
                            const ia_summaries& out, cudaStream_t stream);
 // split_counters (may be null): one int per (sequence, kv head), cleared by the selection
 // kernel for the attention kernel's fused finalize
+// exchange (may be null) + block range: split-KV across GPUs, this rank scores blocks [block_lo, block_hi)
 int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_lens, const ia_geom& g,
                   int mode, int top_k, float eps, int max_sel, int32_t* sel_idx, int32_t* sel_count,
-                  const ia_select_aux& aux, int* split_counters, cudaStream_t stream);
+                  const ia_select_aux& aux, int* split_counters, cudaStream_t stream,
+                  const ia_select_exchange* exchange = nullptr, int block_lo = 0, int block_hi = 0);
 // Fused finalize of the attention kernel: the last CTA of a (sequence, kv head) merges the splits.
 struct FusedFinalize {
   void* out;            // [batch, rows, D]

@@ -133,6 +133,11 @@ struct SelectParams {
   int n_stages, nb_cap;
   int cluster;     // CTAs per (sequence, kv head): a thread-block cluster splits the blocks
   int nb_loc_cap;  // row stride of the per-CTA (row, block) arrays
+  // Split-KV across GPUs: this rank scores the blocks [block_lo, block_hi) only and exchanges the row
+  // normalisers and its top-k candidates with the other ranks (xch.n_ranks == 0: one GPU, all blocks).
+  ia_select_exchange xch;
+  int block_lo, block_hi;
+  int n_pairs;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -266,6 +271,21 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// ---- exchange with peer GPUs (plain peer stores and flags; no multicast) -----------------
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait until *flag reaches `want` (about a second); false when it did not.
+__device__ __forceinline__ bool wait_flag(const int* flag, int want) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (ld_acquire_sys(flag) - want >= 0) return true;
+    __nanosleep(200);
+  }
+  return false;
+}
+
 // barrier among the 128 threads of one warp group (ids 1..kGroups; 0 is __syncthreads)
 __device__ __forceinline__ void group_sync(int group) {
   asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kGroupWarps * 32) : "memory");
@@ -328,9 +348,10 @@ template <int D, int G, bool MMA, int NG> struct SmemPlan {
   static constexpr size_t qrows = 2 * (size_t)G * D * 4;
   static constexpr size_t part = MMA ? 0 : (size_t)kConsumerWarps * 3 * G * 32 * 4;
   static constexpr size_t xch = 8 * 16 * 3 * 4;  // [cluster rank][row][m, l, d]
-  static constexpr size_t fixed = bars + hist + scan + red + norm + state + qrows + part + xch;
-  static size_t per_blocks(int nb_cap, int nb_loc_cap) {
-    return (size_t)nb_cap * 4 * 2 + (size_t)nb_loc_cap * 4 * 2 * G;
+  static constexpr size_t xst = 16 * 4 * 4;      // [row][m, l, d, b_all] of this GPU, on its way to the peers
+  static constexpr size_t fixed = bars + hist + scan + red + norm + state + qrows + part + xch + xst;
+  static size_t per_blocks(int nb_cap, int nb_loc_cap, int n_candidates = 0) {
+    return (size_t)nb_cap * 4 * 2 + (size_t)nb_loc_cap * 4 * 2 * G + (size_t)n_candidates * 8;
   }
 };
 
@@ -364,13 +385,20 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   IA_TRACE(0);
   const int prefix = p.prefix_lens[seq];
   const int nb = min((prefix + p.block_size - 1) / p.block_size, p.max_blocks);
-  const int n_tiles = (nb + kTileBlocks - 1) / kTileBlocks;
   const int nb_cap = p.nb_cap;
-  // this CTA scores the tiles [t_lo, t_hi) = blocks [b_lo, b_hi); rank 0 routes for the pair
-  const int t_lo = n_tiles * crank / C, t_hi = n_tiles * (crank + 1) / C;
+  // Blocks of this GPU: all of them, or the rank's range [block_lo, block_hi) in split-KV (tile
+  // aligned).  This CTA scores the tiles [t_lo, t_hi) = blocks [b_lo, b_hi) of them; cluster rank 0
+  // routes for the pair.
+  const bool xch_on = p.xch.n_ranks > 0;
+  const int r_lo = xch_on ? min(p.block_lo, nb) : 0, r_hi = xch_on ? min(p.block_hi, nb) : nb;
+  const int rt_lo = r_lo / kTileBlocks;
+  const int n_tiles = max((r_hi + kTileBlocks - 1) / kTileBlocks - rt_lo, 0);
+  const int t_lo = rt_lo + n_tiles * crank / C, t_hi = rt_lo + n_tiles * (crank + 1) / C;
   const int n_my_tiles = t_hi - t_lo;
-  const int b_lo = t_lo * kTileBlocks, b_hi = min(t_hi * kTileBlocks, nb);
+  const int b_lo = t_lo * kTileBlocks, b_hi = min(t_hi * kTileBlocks, r_hi);
   const int nbl = p.nb_loc_cap;
+  const int xstep = xch_on ? *p.xch.step_counter + 1 : 0;  // advanced by the last CTA to leave
+  const int xpar = xstep & 1;
   // Ring geometry.  The consumers of a stage are "slots" (two tensor-core warps, or a group of four
   // CUDA-core warps) that walk the tiles round robin.  A parity wait can only tell a phase from its
   // neighbour, so the slot that waits for use u of a stage must know that use u - 1 has completed:
@@ -396,12 +424,16 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   float* aq_s = q_s + G * D;                           sp += P::qrows;  // |q|
   float* part_s = reinterpret_cast<float*>(sp);        sp += P::part;   // [consumer warp][3G][32]
   float* xch_s = reinterpret_cast<float*>(sp);         sp += P::xch;    // [cluster rank][16][3], written by peers
+  float* xst_s = reinterpret_cast<float*>(sp);         sp += P::xst;    // [16][4] this GPU's row normalisers
   float* vn_s = reinterpret_cast<float*>(sp);                           // [nb_cap]
   float* score_s = vn_s + nb_cap;                                       // [nb_cap]
   float* z_s = score_s + nb_cap;                                        // [G][nbl]: z = s + log count (own blocks)
   float* d_s = z_s + (size_t)G * nbl;                                   // [G][nbl]: delta (range bound)
+  // split-KV: the ranks' top-k candidates, gathered: [n_ranks * max_sel] scores and block indices
+  float* cand_s = d_s + (size_t)G * nbl;
+  int* candb_s = reinterpret_cast<int*>(cand_s + (xch_on ? p.xch.n_ranks * p.max_sel : 0));
   unsigned char* stage_base = reinterpret_cast<unsigned char*>(
-      (reinterpret_cast<uintptr_t>(d_s + (size_t)G * nbl) + 1023) & ~uintptr_t(1023));
+      (reinterpret_cast<uintptr_t>(candb_s + (xch_on ? p.xch.n_ranks * p.max_sel : 0)) + 1023) & ~uintptr_t(1023));
 
   const int64_t sum_row0 = (int64_t)pair * p.max_blocks;  // first summary row of this pair
   // one ring stage: the TMA box copies of 32 blocks' summaries, completing on the stage's barrier
@@ -427,7 +459,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   // the ring with the first tiles of the pair's rows of the summary arrays (they exist up to
   // max_blocks whatever the length; a tile past the sequence's last block is awaited and skipped),
   // so the length's load latency is off the path to the first data.
-  const int n_primed = C == 1 ? min(n_stages, nb_cap / kTileBlocks) : min(n_stages, n_my_tiles);
+  const int n_primed = (C == 1 && !xch_on) ? min(n_stages, nb_cap / kTileBlocks) : min(n_stages, n_my_tiles);
   if (warp == kConsumerWarps) {
     if (lane == 0) {
       for (int s = 0; s < n_stages; ++s) {
@@ -461,7 +493,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         for (int j = 0; j < 4; ++j) {
           const int b = base + j * kStride;
           if (b < p.max_blocks) vn_s[b] = v[j];
-          if (b < nb) bmax = fmaxf(bmax, v[j]);
+          if (b >= r_lo && b < r_hi) bmax = fmaxf(bmax, v[j]);
         }
       }
       bmax = warp_max(bmax);
@@ -799,7 +831,10 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     if (C > 1) norm_reduce_lanes<1, 8>(tot);
     float b_all = lane < kWarps ? redb_s[lane] : 0.f;
     b_all = warp_max(b_all);
-
+    if (xch_on) {  // this GPU's share of row g: parked for the exchange below
+      if (lane == 0) { xst_s[g * 4] = tot.m; xst_s[g * 4 + 1] = tot.l; xst_s[g * 4 + 2] = tot.d; xst_s[g * 4 + 3] = b_all; }
+      continue;
+    }
     if (lane == 0) {
       const float denom = fmaxf(tot.d / tot.l, 1e-30f);  // sum_b softmax(z)_b cosh(delta_b)
       norm_s[g] = tot.m;
@@ -815,6 +850,59 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         gl[1 * rows] = tot.l;
         gl[2 * rows] = tot.m;
         gl[3 * rows] = tot.d;
+      }
+    }
+  }
+  if (xch_on) {
+    // Exchange of the row normalisers between the GPUs of a split-KV group.  Cluster rank 0 stores
+    // this GPU's (m, l, d, b_all) of every row into the buffer of every GPU (plain peer stores), fences
+    // at system scope and raises its flag there; every CTA of the pair then waits - bounded - for the
+    // flags of all GPUs in its own memory and merges the W shares, in rank order on every GPU.
+    const int W = p.xch.n_ranks, me = p.xch.my_rank;
+    const int64_t slot0 = ((int64_t)xpar * p.n_pairs + pair) * W;
+    __syncthreads();
+    if (crank == 0) {
+      for (int i = tid; i < G * W; i += kThreads) {
+        const int g = i % G, w = i / G;
+        const float4 v = *reinterpret_cast<const float4*>(xst_s + g * 4);
+        *reinterpret_cast<float4*>(p.xch.norm[w] + ((slot0 + me) * 16 + g) * 4) = v;
+      }
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence_system();
+        for (int w = 0; w < W; ++w) {
+          volatile int32_t* f = p.xch.flags[w] + ((int64_t)(xpar * 2 + 0) * p.n_pairs + pair) * W + me;
+          *f = xstep;
+        }
+      }
+    }
+    if (tid < W && !wait_flag(p.xch.flags[me] + ((int64_t)(xpar * 2 + 0) * p.n_pairs + pair) * W + tid, xstep))
+      atomicOr(&g_device_status, DEV_STATUS_PEER_WAIT_TIMEOUT);
+    __syncthreads();
+    for (int g = warp; g < G; g += kWarps) {
+      RowNorm tot{-INFINITY, 0.f, 0.f};
+      float b_all = 0.f;
+      if (lane < W) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.xch.norm[me] + ((slot0 + lane) * 16 + g) * 4));
+        tot = RowNorm{v.x, v.y, v.z};
+        b_all = v.w;
+      }
+      norm_reduce_lanes<1, 8>(tot);
+      b_all = warp_max(b_all);
+      if (lane == 0) {
+        const float denom = fmaxf(tot.d / tot.l, 1e-30f);
+        norm_s[g] = tot.m;
+        norm_s[16 + g] = 1.f / tot.l;
+        norm_s[32 + g] = 2.f * b_all / denom;
+        if (p.aux.globals != nullptr && crank == 0) {
+          const int rows = p.n_kv_heads * G;
+          const int head = pair - seq * p.n_kv_heads;
+          float* gl = p.aux.globals + (int64_t)seq * 4 * rows + head * G + g;
+          gl[0 * rows] = tot.m;
+          gl[1 * rows] = tot.l;
+          gl[2 * rows] = tot.m;
+          gl[3 * rows] = tot.d;
+        }
       }
     }
   }
@@ -846,127 +934,191 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   if (C > 1) cluster_sync_all();
   else __syncthreads();
   IA_TRACE(6);
-  if (crank != 0) return;  // nobody reads this CTA's shared memory any more
+  // Split-KV bookkeeping: the CTA that leaves last advances this GPU's step number (every CTA has
+  // read it by then), so that the next launch - also a replay of a captured graph - uses the next one.
+  auto leave = [&]() {
+    if (xch_on && tid == 0) {
+      const unsigned done = atomicAdd(reinterpret_cast<unsigned*>(p.xch.grid_counter), 1u);
+      if (done == gridDim.x - 1) {
+        *p.xch.grid_counter = 0;
+        *p.xch.step_counter = xstep;
+      }
+    }
+  };
+  if (crank != 0) {  // nobody reads this CTA's shared memory any more
+    leave();
+    return;
+  }
 
   // ---- phase 4: routing ----------------------------------------------------------------
-  int32_t* out_idx = p.sel_idx + (int64_t)pair * p.max_sel;
-  uint32_t thr_key = 0, thr_mask = 0xffffffffu;  // keys are compared on the digits resolved so far
-  int take_equal = 0;
-  const int k_eff = (p.mode == IA_SELECT_TOPK) ? min(min(p.top_k, nb), p.max_sel) : 0;
-  if (k_eff > 0 && k_eff < nb) {
-    // Radix select of the k_eff-th largest key, 8 bits per pass.  Three
-    // histograms rotate: pass p fills hist[p % 3] and clears hist[(p + 1) % 3]
-    // (last read two passes ago), and every warp resolves the digit for itself
-    // from the finished histogram - so a pass needs one barrier.
-    uint32_t fixed = 0, fixed_mask = 0;
-    int remaining = k_eff;
-    for (int i = tid; i < 256; i += kThreads) hist[i] = 0;
-    __syncthreads();
-#pragma unroll 1  // executed once per launch: keep the cold code short (it is fetched from L2)
-    for (int pass = 0; pass < 4; ++pass) {
-      const int shift = 24 - 8 * pass;
-      int* h = hist + (pass % 3) * 256;
-      int* h_next = hist + ((pass + 1) % 3) * 256;
-      for (int i = tid; i < 256; i += kThreads) h_next[i] = 0;
-      for (int base = 0; base < nb; base += kThreads) {
-        const int b = base + tid;
-        const uint32_t key = b < nb ? order_key(score_s[b]) : 0u;
-        const bool live = b < nb && (key & fixed_mask) == fixed;
-        const uint32_t digit = (key >> shift) & 255u;
-        // scores cluster in a few bins: the lanes that share a digit send one atomic together
-        const uint32_t peers = __match_any_sync(0xffffffffu, live ? digit : 0xffffffffu);
-        if (live && lane == __ffs(peers) - 1) atomicAdd(&h[digit], __popc(peers));
-      }
+  // route(sc, n, emit): among the n scores sc[0..n) pick the top_k best (higher score first, lower
+  // position first among equal scores) or, in epsilon mode, every score above eps; emit(slot, j) is
+  // called once per picked position j with its output slot - slots ascend with j.  Returns how
+  // many were picked.  Every thread of the CTA calls it (it contains CTA barriers).
+  auto route = [&](const float* sc, int n, auto emit) -> int {
+    uint32_t thr_key = 0, thr_mask = 0xffffffffu;  // keys are compared on the digits resolved so far
+    int take_equal = 0;
+    const int k_eff = (p.mode == IA_SELECT_TOPK) ? min(min(p.top_k, n), p.max_sel) : 0;
+    if (k_eff > 0 && k_eff < n) {
+      // Radix select of the k_eff-th largest key, 8 bits per pass.  Three
+      // histograms rotate: pass p fills hist[p % 3] and clears hist[(p + 1) % 3]
+      // (last read two passes ago), and every warp resolves the digit for itself
+      // from the finished histogram - so a pass needs one barrier.
+      uint32_t fixed = 0, fixed_mask = 0;
+      int remaining = k_eff;
+      for (int i = tid; i < 256; i += kThreads) hist[i] = 0;
       __syncthreads();
-      // lane owns bins [8 lane, 8 lane + 8); `above` = keys in the bins of higher lanes
-      int c[8], mine = 0;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { c[i] = h[lane * 8 + i]; mine += c[i]; }
-      int incl = mine;  // inclusive suffix sum over lanes
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_down_sync(0xffffffffu, incl, o);
-        if (lane + o < 32) incl += v;
-      }
-      const int above = incl - mine;
-      const bool owner = (above < remaining) && (incl >= remaining);
-      int digit = 0, left = 0, in_bin = 0;
-      if (owner) {
-        int acc = above;
-#pragma unroll
-        for (int i = 7; i >= 0; --i) {
-          if (acc + c[i] >= remaining) { digit = lane * 8 + i; in_bin = c[i]; break; }
-          acc += c[i];
+#pragma unroll 1  // executed once per launch: keep the cold code short (it is fetched from L2)
+      for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        int* h = hist + (pass % 3) * 256;
+        int* h_next = hist + ((pass + 1) % 3) * 256;
+        for (int i = tid; i < 256; i += kThreads) h_next[i] = 0;
+        for (int base = 0; base < n; base += kThreads) {
+          const int b = base + tid;
+          const uint32_t key = b < n ? order_key(sc[b]) : 0u;
+          const bool live = b < n && (key & fixed_mask) == fixed;
+          const uint32_t digit = (key >> shift) & 255u;
+          // scores cluster in a few bins: the lanes that share a digit send one atomic together
+          const uint32_t peers = __match_any_sync(0xffffffffu, live ? digit : 0xffffffffu);
+          if (live && lane == __ffs(peers) - 1) atomicAdd(&h[digit], __popc(peers));
         }
-        left = remaining - acc;
+        __syncthreads();
+        // lane owns bins [8 lane, 8 lane + 8); `above` = keys in the bins of higher lanes
+        int c[8], mine = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { c[i] = h[lane * 8 + i]; mine += c[i]; }
+        int incl = mine;  // inclusive suffix sum over lanes
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_down_sync(0xffffffffu, incl, o);
+          if (lane + o < 32) incl += v;
+        }
+        const int above = incl - mine;
+        const bool owner = (above < remaining) && (incl >= remaining);
+        int digit = 0, left = 0, in_bin = 0;
+        if (owner) {
+          int acc = above;
+#pragma unroll
+          for (int i = 7; i >= 0; --i) {
+            if (acc + c[i] >= remaining) { digit = lane * 8 + i; in_bin = c[i]; break; }
+            acc += c[i];
+          }
+          left = remaining - acc;
+        }
+        const int src = max(__ffs(__ballot_sync(0xffffffffu, owner)) - 1, 0);  // exactly one owner lane
+        digit = __shfl_sync(0xffffffffu, digit, src);
+        remaining = __shfl_sync(0xffffffffu, left, src);
+        in_bin = __shfl_sync(0xffffffffu, in_bin, src);
+        fixed |= (uint32_t)digit << shift;
+        fixed_mask |= 255u << shift;
+        // every key of the threshold bin is wanted: the remaining digits cannot change the outcome
+        if (in_bin == remaining) break;
       }
-      const int src = max(__ffs(__ballot_sync(0xffffffffu, owner)) - 1, 0);  // exactly one owner lane
-      digit = __shfl_sync(0xffffffffu, digit, src);
-      remaining = __shfl_sync(0xffffffffu, left, src);
-      in_bin = __shfl_sync(0xffffffffu, in_bin, src);
-      fixed |= (uint32_t)digit << shift;
-      fixed_mask |= 255u << shift;
-      // every key of the threshold bin is wanted: the remaining digits cannot change the outcome
-      if (in_bin == remaining) break;
+      thr_key = fixed;
+      thr_mask = fixed_mask;
+      take_equal = remaining;
     }
     IA_TRACE(7);
-    thr_key = fixed;
-    thr_mask = fixed_mask;
-    take_equal = remaining;
-  }
 
-  // Ordered compaction.  Selected = key above the threshold, plus the first
-  // `take_equal` keys equal to it in index order; one block scan of the packed
-  // counts (greater: low 16 bits, equal: high 16 bits) gives every output slot.
-  int n_written = 0;
-  const bool any = (p.mode == IA_SELECT_EPS) ? (nb > 0) : (k_eff > 0);
-  if (any) {
-    const bool everything = (p.mode == IA_SELECT_TOPK) && (k_eff >= nb);
-    int gt_seen = 0, eq_seen = 0;
-    for (int base = 0; base < nb; base += kThreads) {
-      const int b = base + tid;
-      const bool in = b < nb;
-      const float sc = in ? score_s[b] : 0.f;
-      bool gt, eq = false;
-      if (p.mode == IA_SELECT_EPS) {
-        gt = in && (sc > p.eps);
-      } else if (everything) {
-        gt = in;
-      } else {
-        const uint32_t key = order_key(sc) & thr_mask;
-        gt = in && key > thr_key;
-        eq = in && key == thr_key;
-      }
-      // exclusive scan of (gt, eq) over the block
-      const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
-      const uint32_t below = (1u << lane) - 1u;
-      if (lane == 0) scan_scratch[warp] = __popc(bg) | (__popc(be) << 16);
-      __syncthreads();
-      int packed_before = 0, packed_total = 0;
+    // Ordered compaction.  Selected = key above the threshold, plus the first
+    // `take_equal` keys equal to it in index order; one block scan of the packed
+    // counts (greater: low 16 bits, equal: high 16 bits) gives every output slot.
+    int n_written = 0;
+    const bool any = (p.mode == IA_SELECT_EPS) ? (n > 0) : (k_eff > 0);
+    if (any) {
+      const bool everything = (p.mode == IA_SELECT_TOPK) && (k_eff >= n);
+      int gt_seen = 0, eq_seen = 0;
+      for (int base = 0; base < n; base += kThreads) {
+        const int b = base + tid;
+        const bool in = b < n;
+        const float v = in ? sc[b] : 0.f;
+        bool gt, eq = false;
+        if (p.mode == IA_SELECT_EPS) {
+          gt = in && (v > p.eps);
+        } else if (everything) {
+          gt = in;
+        } else {
+          const uint32_t key = order_key(v) & thr_mask;
+          gt = in && key > thr_key;
+          eq = in && key == thr_key;
+        }
+        // exclusive scan of (gt, eq) over the block
+        const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
+        const uint32_t below = (1u << lane) - 1u;
+        if (lane == 0) scan_scratch[warp] = __popc(bg) | (__popc(be) << 16);
+        __syncthreads();
+        int packed_before = 0, packed_total = 0;
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        const int c = scan_scratch[w];
-        if (w < warp) packed_before += c;
-        packed_total += c;
+        for (int w = 0; w < kWarps; ++w) {
+          const int c = scan_scratch[w];
+          if (w < warp) packed_before += c;
+          packed_total += c;
+        }
+        __syncthreads();
+        const int gt_before = gt_seen + (packed_before & 0xffff) + __popc(bg & below);
+        const int eq_before = eq_seen + (packed_before >> 16) + __popc(be & below);
+        const bool take = gt || (eq && eq_before < take_equal);
+        const int pos = gt_before + min(eq_before, take_equal);
+        if (take && pos >= 0 && pos < p.max_sel) emit(pos, b);
+        gt_seen += packed_total & 0xffff;
+        eq_seen += packed_total >> 16;
       }
-      __syncthreads();
-      const int gt_before = gt_seen + (packed_before & 0xffff) + __popc(bg & below);
-      const int eq_before = eq_seen + (packed_before >> 16) + __popc(be & below);
-      const bool take = gt || (eq && eq_before < take_equal);
-      const int pos = gt_before + min(eq_before, take_equal);
-      if (take && pos >= 0 && pos < p.max_sel) out_idx[pos] = b;
-      gt_seen += packed_total & 0xffff;
-      eq_seen += packed_total >> 16;
+      n_written = gt_seen + min(eq_seen, take_equal);
     }
-    n_written = gt_seen + min(eq_seen, take_equal);
+    return max(min(n_written, p.max_sel), 0);
+  };
+
+  int32_t* out_idx = p.sel_idx + (int64_t)pair * p.max_sel;
+  int n_written;
+  if (!xch_on) {
+    n_written = route(score_s, nb, [&](int slot, int b) { out_idx[slot] = b; });
+  } else {
+    // Split-KV: the k best of this GPU's blocks are candidates - (score, block index) in block order -
+    // and go to every GPU; the k best of all candidates, taken in rank order (= block order, the
+    // ranks own ascending ranges), are the selection, identical on every GPU.
+    const int W = p.xch.n_ranks, me = p.xch.my_rank, kc = p.max_sel;
+    const int64_t slot0 = ((int64_t)xpar * p.n_pairs + pair) * W;
+    const int n_mine = route(score_s + r_lo, max(r_hi - r_lo, 0), [&](int slot, int j) {
+      const float2 c = make_float2(score_s[r_lo + j], __int_as_float(r_lo + j));
+      for (int w = 0; w < W; ++w) reinterpret_cast<float2*>(p.xch.cand[w])[(slot0 + me) * (kc + 1) + slot] = c;
+    });
+    if (tid == 0)
+      for (int w = 0; w < W; ++w)
+        reinterpret_cast<float2*>(p.xch.cand[w])[(slot0 + me) * (kc + 1) + kc] = make_float2(__int_as_float(n_mine), 0.f);
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence_system();
+      for (int w = 0; w < W; ++w) {
+        volatile int32_t* f = p.xch.flags[w] + ((int64_t)(xpar * 2 + 1) * p.n_pairs + pair) * W + me;
+        *f = xstep;
+      }
+    }
+    if (tid < W && !wait_flag(p.xch.flags[me] + ((int64_t)(xpar * 2 + 1) * p.n_pairs + pair) * W + tid, xstep))
+      atomicOr(&g_device_status, DEV_STATUS_PEER_WAIT_TIMEOUT);
+    __syncthreads();
+    const float2* mine = reinterpret_cast<const float2*>(p.xch.cand[me]);
+    int n_all = 0;
+    for (int w = 0; w < W; ++w) {  // rank order; every thread walks the W counts
+      const int n_w = min(max(__float_as_int(__ldcg(&mine[(slot0 + w) * (kc + 1) + kc]).x), 0), kc);
+      for (int i = tid; i < n_w; i += kThreads) {
+        const float2 c = __ldcg(&mine[(slot0 + w) * (kc + 1) + i]);
+        cand_s[n_all + i] = c.x;
+        candb_s[n_all + i] = __float_as_int(c.y);
+      }
+      n_all += n_w;
+    }
+    __syncthreads();
+    n_written = route(cand_s, n_all, [&](int slot, int j) { out_idx[slot] = candb_s[j]; });
   }
   IA_TRACE(8);
-  const int count = max(min(n_written, p.max_sel), 0);
+  const int count = n_written;
   for (int i = count + tid; i < p.max_sel; i += kThreads) out_idx[i] = -1;
   if (tid == 0) {
     p.sel_count[pair] = count;
     if (p.split_counters != nullptr) p.split_counters[pair] = 0;
   }
+  leave();
 }
 
 // cuTensorMapEncodeTiled lives in the driver library; fetch it through the
@@ -1048,7 +1200,11 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   // thread-block cluster shares each pair: double the cluster while the grid still fits
   // the SMs and every CTA keeps at least two 32-block tiles.
   // INTERATTN_B200_SELECT_CLUSTER pins it.
-  const int max_tiles = p.nb_cap / kTileBlocks;
+  // tiles of a pair that this GPU scores: all of them, or those of its block range (split-KV)
+  const bool xch_on = p.xch.n_ranks > 0;
+  const int max_tiles = xch_on ? (min(p.block_hi, p.nb_cap) - p.block_lo + kTileBlocks - 1) / kTileBlocks
+                               : p.nb_cap / kTileBlocks;
+  const int n_cand = xch_on ? p.xch.n_ranks * p.max_sel : 0;
   int cluster = 1;
   while (cluster < 8 && n_pairs * cluster * 2 <= sms && max_tiles / (cluster * 2) >= 2) cluster *= 2;
   if (const char* force = getenv("INTERATTN_B200_SELECT_CLUSTER")) {
@@ -1072,6 +1228,11 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   // INTERATTN_B200_SELECT_SHAPE=wide|narrow (+ INTERATTN_B200_SELECT_CLUSTER) pin the choice where it fits.
   const char* shape = getenv("INTERATTN_B200_SELECT_SHAPE");
   const bool want_narrow = shape != nullptr ? strcmp(shape, "narrow") == 0 : n_pairs > sms;
+  if (xch_on && (want_narrow || n_pairs * cluster > sms))
+    // the CTAs of a split-KV selection wait for their peers on the other GPUs: all of them must be
+    // resident at once (one wide CTA per SM), or a CTA could wait for one that is not scheduled yet
+    return fail(IA_ERR_UNSUPPORTED, "select (split-KV): %d (sequence, kv head) pairs x cluster %d exceed the %d SMs",
+                n_pairs, cluster, sms);
   if (want_narrow) {
     for (int c = cluster; c <= 8; c *= 2) {
       p.cluster = c;
@@ -1094,7 +1255,7 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
     p.cluster = cluster;  // no narrow form fits: the wide shape with the cluster chosen above
     p.nb_loc_cap = (max_tiles / cluster + 1) * kTileBlocks;
   }
-  const size_t fixed = PW::fixed + PW::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
+  const size_t fixed = PW::fixed + PW::per_blocks(p.nb_cap, p.nb_loc_cap, n_cand) + 1024;
   if ((size_t)max_smem < fixed + 2 * (size_t)L::bytes)
     return fail(IA_ERR_UNSUPPORTED, "select: %d blocks x %d query rows per kv head do not fit in shared memory",
                 p.max_blocks, G);
@@ -1120,8 +1281,15 @@ static int launch_group(const SelectParams& p, int n_pairs, int group, cudaStrea
 
 int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_lens, const ia_geom& g,
                   int mode, int top_k, float eps, int max_sel, int32_t* sel_idx, int32_t* sel_count,
-                  const ia_select_aux& aux, int* split_counters, cudaStream_t stream) {
+                  const ia_select_aux& aux, int* split_counters, cudaStream_t stream,
+                  const ia_select_exchange* exchange, int block_lo, int block_hi) {
   SelectParams p{};
+  if (exchange != nullptr) {
+    p.xch = *exchange;
+    p.block_lo = block_lo;
+    p.block_hi = block_hi < g.max_blocks ? block_hi : g.max_blocks;
+  }
+  p.n_pairs = g.batch * g.n_kv_heads;
   p.q = q; p.k_bar = s.k_bar; p.k_max = s.k_max; p.k_min = s.k_min; p.v_norm_max = s.v_norm_max;
   p.prefix_lens = prefix_lens;
   p.n_kv_heads = g.n_kv_heads; p.max_blocks = g.max_blocks; p.block_size = g.block_size;

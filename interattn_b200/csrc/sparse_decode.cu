@@ -196,6 +196,9 @@ int launch_sparse_decode(const void* q, const void* k_pool, const void* v_pool,
   p.n_pool_pages = g.n_pool_pages;
   p.status = device_status_address();
   p.n_pairs = g.batch * g.n_kv_heads;
+#ifdef IA_DECODE_TRACE
+  p.trace = getenv("IA_TRACE_PTR") ? reinterpret_cast<float*>(strtoull(getenv("IA_TRACE_PTR"), nullptr, 16)) : nullptr;
+#endif
   p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.block_table = block_table;
   p.prefix_lens = prefix_lens; p.seq_lens = seq_lens; p.sel_idx = sel_idx; p.sel_count = sel_count;
   p.v_bar = summaries ? summaries->v_bar : nullptr;

@@ -291,11 +291,14 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
 
   // Let the next kernel on the stream start filling SMs as this grid drains, then wait
   // for the selection kernel: everything below reads what it wrote.
+  IA_DTRACE_BEGIN();
   grid_launch_dependents();
   grid_dependency_wait();
+  IA_DTRACE(0);
   ExchangeView xv{};
   if (p.px.n_ranks > 0) xv = exchange_view(p);
   const ItemRange r = item_range(p, seq, head, split, scratch);
+  IA_DTRACE(1);
   if (p.rep_mode == IA_REP_HYBRID) {
     const int words = (p.max_blocks + 31) / 32;
     for (int i = threadIdx.x; i < words; i += blockDim.x) sel_bits[i] = 0u;
@@ -338,6 +341,7 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
     const int chunk_end = min(chunk + kItemChunk, r.end);
     __syncthreads();  // every warp is done with the previous descriptors
     resolve_items(p, r, seq, head, chunk, chunk_end, items_s);
+    IA_DTRACE(2);
     const int n_mine = (chunk_end - chunk - warp + kWarps - 1) / kWarps;  // items warp, warp+4, ...
 #pragma unroll
     for (int s = 0; s < NS - 1; ++s) {
@@ -350,14 +354,17 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
       cp_async_commit();
       cp_async_wait<NS - 1>();
       __syncwarp();
+      if (n == 0) IA_DTRACE(3);
       consume(items_s[warp + n * kWarps], n % NS);
       __syncwarp();
     }
     cp_async_wait<0>();
   }
+  IA_DTRACE(4);
 
   // ---- merge the four warps ------------------------------------------------------------
   __syncthreads();  // all rings idle: reuse them as merge buffers
+  IA_DTRACE(5);
   float* mo = reinterpret_cast<float*>(w.ring);               // [16][D]
   float* mm = reinterpret_cast<float*>(w.ring + 16 * D * 4);  // m[16], l[16]
   w.reduce_l();
@@ -400,11 +407,13 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
       if (d == 0) p.lse_partial[orow] = lv;
     }
   }
+  IA_DTRACE(6);
   if (p.px.n_ranks > 0) {
     exchange_publish(p, xv);
     return;
   }
   finish_pair<D>(p, seq, head, G, scratch);
+  IA_DTRACE(7);
 }
 
 // ---- flat grid: equal contiguous shares of all pairs' items -------------------------------

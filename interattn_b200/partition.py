@@ -85,11 +85,48 @@ def ordered_shutdown(graphs: Sequence = (), steps: Sequence = (), group=None, wa
 # plans (pure host arithmetic)
 # --------------------------------------------------------------------------
 
-def plan_block_ranges(n_blocks: int, world: int) -> List[Tuple[int, int]]:
-    """Contiguous, near-equal block ranges [lo, hi) for ranks 0..world-1 (some may be empty)."""
-    if world <= 0 or n_blocks < 0:
-        raise ValueError("world must be positive and n_blocks non-negative")
-    return [(n_blocks * r // world, n_blocks * (r + 1) // world) for r in range(world)]
+def plan_block_ranges(n_blocks: int, world: int, align: int = 1) -> List[Tuple[int, int]]:
+    """Contiguous, near-equal block ranges [lo, hi) for ranks 0..world-1 (some may be empty).
+    ``align``: every boundary but the last is a multiple of it (the split-KV selection kernel
+    streams summaries in tiles of 32 blocks, so its ranges are cut with ``align=32``)."""
+    if world <= 0 or n_blocks < 0 or align <= 0:
+        raise ValueError("world and align must be positive and n_blocks non-negative")
+    units = (n_blocks + align - 1) // align
+    cuts = [min(units * r // world * align, n_blocks) for r in range(world + 1)]
+    cuts[-1] = n_blocks
+    return [(cuts[r], cuts[r + 1]) for r in range(world)]
+
+
+# --------------------------------------------------------------------------
+# split-KV selection: what the ranks exchange, as host arithmetic
+# --------------------------------------------------------------------------
+# The selection kernel of a split-KV group (ia_select_split) exchanges two small things between the
+# GPUs: per query row the softmax normalisers of its own blocks, and its own top-k candidates.  The
+# two merges below are the same arithmetic on the host - for tests on any backend, and as the
+# definition of what the kernel must compute.
+
+def merge_row_normalisers(m: torch.Tensor, l: torch.Tensor, d: torch.Tensor, b_all: torch.Tensor):
+    """Per-rank running-softmax states of every query row -> the global ones.
+
+    ``m, l, d, b_all``: [world, rows]; on each rank ``m`` = max of z over its blocks, ``l`` = sum of
+    e^(z - m), ``d`` = sum of e^(z - m) cosh(delta), ``b_all`` = its largest value norm (a rank
+    without blocks has m = -inf, l = d = 0).  Returns ``(M, L, D, B)`` [rows] with the same meaning
+    over all blocks; ranks are summed in rank order."""
+    top = m.amax(dim=0)
+    safe = torch.where(torch.isfinite(top), top, torch.zeros_like(top))
+    w = torch.where(torch.isfinite(m), torch.exp(m - safe), torch.zeros_like(m))
+    return top, (l * w).sum(dim=0), (d * w).sum(dim=0), b_all.amax(dim=0)
+
+
+def merge_topk_candidates(scores: Sequence[torch.Tensor], blocks: Sequence[torch.Tensor], k: int) -> torch.Tensor:
+    """Per-rank candidate lists (scores and ascending global block indices, ranks in ascending block
+    order) -> the global top-k block indices, ascending.  Higher score first; among equal scores
+    the lower block index, which is the earlier position of the concatenated list."""
+    sc = torch.cat([x.flatten() for x in scores])
+    bl = torch.cat([x.flatten() for x in blocks])
+    k_eff = min(int(k), int(sc.numel()))
+    order = torch.sort(sc, descending=True, stable=True).indices[:k_eff]
+    return torch.sort(bl[order]).values
 
 
 def unit_costs(prefix_lens: Sequence[int], n_kv_heads: int, block_size: int, top_k: int,
@@ -256,24 +293,31 @@ class SplitKVDecodeAttention:
 
 
 class SplitKVDecodeAttentionP2P:
-    """The split-KV layer-step with the exchange inside the kernels: three launches
-    (selection, attention, merge) and no collective call.
+    """The split-KV layer-step with every exchange inside the kernels: three launches (selection,
+    attention, merge) and no collective call.
 
-    The attention kernel stores every partial into the gather buffer of every rank through
-    peer pointers (NVLink stores) and its last CTA publishes the step number in a flag on
-    every rank; the merge kernel waits - bounded, about a second - for the flags of all
-    ranks and merges the chunks in place.  The buffers are symmetric memory
-    (``torch.distributed._symmetric_memory``), mapped once at construction; a step
-    allocates nothing and keeps its step counter on the device, so it can be captured into a
-    CUDA graph.  Plain peer stores only: the buffers are not bound to an NVSwitch multicast
-    object (``TORCH_SYMM_MEM_DISABLE_MULTICAST``).  Every rank must construct the object (a
-    collective), run the same number of steps and ``close()`` it (or leave through
-    ``ordered_shutdown``) before the process group goes away.  ``check()`` reads the device status
-    word at a point where the host waits anyway: a peer wait that ran out means ``out`` of that
-    step is invalid."""
+    ``selection="distributed"`` (default): every rank streams only the block summaries of its own
+    range; the selection kernel exchanges the row normalisers and each rank's top-k candidates with
+    the other ranks and every rank ends up with the same global selection (``ia_select_split``) -
+    the selection's HBM traffic and time shrink with the number of GPUs.  ``"replicated"``: every
+    rank holds all summaries and selects on its own (no exchange, no shrinking).
+
+    The attention kernel stores every partial into the gather buffer of every rank through peer
+    pointers (NVLink stores) and its last CTA publishes the step number in a flag on every rank;
+    the merge kernel waits - bounded, about a second - for the flags of all ranks and merges the
+    chunks in place.  All buffers are one block of symmetric memory
+    (``torch.distributed._symmetric_memory``), mapped once at construction; a step allocates
+    nothing and keeps its step counters on the device, so it can be captured into a CUDA graph.
+    Plain peer stores only: the buffers are not bound to an NVSwitch multicast object
+    (``TORCH_SYMM_MEM_DISABLE_MULTICAST``).  Every rank must construct the object (a collective),
+    run the same number of steps and ``close()`` it (or leave through ``ordered_shutdown``) before
+    the process group goes away.  ``check()`` reads the device status word at a point where the
+    host waits anyway: a peer wait that ran out means ``out`` of that step is invalid."""
+
+    launches_per_step = 3
 
     def __init__(self, kv, summ, n_q_heads: int, *, top_k=None, eps=None, rep_mode: str = "sparse_only",
-                 n_splits: int = 4, group=None):
+                 n_splits: int = 4, group=None, selection: str = "distributed"):
         import ctypes
         os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"   # plain peer pointers only (see the module top)
         import torch.distributed._symmetric_memory as symm_mem
@@ -283,12 +327,20 @@ class SplitKVDecodeAttentionP2P:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         if self.world > 8:
             raise ValueError("at most 8 ranks")
+        if selection not in ("distributed", "replicated"):
+            raise ValueError("selection must be 'distributed' or 'replicated'")
+        if selection == "distributed" and top_k is None:
+            raise ValueError("the distributed selection is built for top-k routing; use selection='replicated' "
+                             "with the epsilon rule")
+        self.selection = selection
         self.top_k, self.eps, self.rep_mode, self.n_splits = top_k, eps, rep_mode, int(n_splits)
         nb = summ.max_blocks
-        self.block_range = plan_block_ranges(nb, self.world)[self.rank]
+        lo, hi = plan_block_ranges(nb, self.world, align=32)[self.rank]
+        self.block_range = (lo, nb if hi >= nb else hi)
         self.with_suffix = self.rank == self.world - 1
         b, d = kv.batch, kv.head_dim
         self.n_q_heads, self.rows = int(n_q_heads), b * int(n_q_heads)
+        pairs = b * kv.n_kv_heads
         dev = kv.k_pool.device
         max_sel = max(int(top_k), 1) if top_k is not None else nb
         self.sel_idx = torch.empty((b, kv.n_kv_heads, max_sel), device=dev, dtype=torch.int32)
@@ -296,27 +348,46 @@ class SplitKVDecodeAttentionP2P:
         self.aux = {}
         if rep_mode == "hybrid":
             self.aux["z"] = torch.full((b, self.n_q_heads, nb), float("-inf"), device=dev, dtype=torch.float32)
+        # one symmetric buffer (floats): attention partials | attention flags | normalisers | candidates | flags
+        W = self.world
         n_o = self.rows * self.n_splits * d
         chunk = (n_o + self.rows * self.n_splits + 3) // 4 * 4
-        flag_floats = 64                                   # flags [2][world] int32 at the tail, 256-byte slot
-        self.buf = symm_mem.empty(2 * self.world * chunk + flag_floats, dtype=torch.float32, device=dev)
+
+        def take(n_floats, at=[0]):
+            start = at[0]
+            at[0] = (start + n_floats + 63) // 64 * 64          # 256-byte slots
+            return start
+        off_gather = take(2 * W * chunk)
+        off_aflags = take(2 * W)
+        off_norm = take(2 * pairs * W * 64)
+        off_cand = take(2 * pairs * W * (max_sel + 1) * 2)
+        off_sflags = take(2 * 2 * pairs * W)
+        total = take(0)
+        self.buf = symm_mem.empty(total, dtype=torch.float32, device=dev)
         self.buf.zero_()
         torch.cuda.synchronize(dev)
         self.handle = symm_mem.rendezvous(self.buf, group=group.group_name)
-        self.counters = torch.zeros(2, device=dev, dtype=torch.int32)       # step counter, grid counter
-        px = _lib.PeerExchange()
-        px.n_ranks, px.my_rank = self.world, self.rank
-        for w in range(self.world):
+        self.counters = torch.zeros(4, device=dev, dtype=torch.int32)   # attention step / grid, selection step / grid
+        px, sx = _lib.PeerExchange(), _lib.SelectExchange()
+        px.n_ranks, px.my_rank = W, self.rank
+        sx.n_ranks, sx.my_rank = W, self.rank
+        for w in range(W):
             base = int(self.handle.buffer_ptrs[w])
-            px.gather[w] = base
-            px.flags[w] = base + 2 * self.world * chunk * 4
+            px.gather[w] = base + 4 * off_gather
+            px.flags[w] = base + 4 * off_aflags
+            sx.norm[w] = base + 4 * off_norm
+            sx.cand[w] = base + 4 * off_cand
+            sx.flags[w] = base + 4 * off_sflags
         px.chunk_floats, px.lse_offset = chunk, n_o
         px.step_counter = self.counters.data_ptr()
         px.grid_counter = self.counters.data_ptr() + 4
-        self.px, self._byref = px, ctypes.byref
+        sx.step_counter = self.counters.data_ptr() + 8
+        sx.grid_counter = self.counters.data_ptr() + 12
+        self.px, self.sx, self._byref = px, sx, ctypes.byref
         self.out = torch.empty((b, self.n_q_heads, d), device=dev, dtype=kv.k_pool.dtype)
         self.geom = kv.geom(self.n_q_heads // kv.n_kv_heads, summ.block_size, nb, summ)
         self.c_summ = summ.c_struct()
+        self.c_aux = _lib.SelectAux(None, self.aux["z"].data_ptr() if "z" in self.aux else None, None, None, None)
         self._group = group
         dist.barrier(group)                                # every rank's buffer is zeroed and mapped
 
@@ -325,8 +396,8 @@ class SplitKVDecodeAttentionP2P:
         from ._lib import IA_DEV_STATUS_PEER_WAIT
         status = self.ops.device_status()
         if status & IA_DEV_STATUS_PEER_WAIT:
-            raise RuntimeError("split-KV exchange: a wait for a peer's partials ran out; the output of that step "
-                               "is invalid (a rank is missing or far behind)")
+            raise RuntimeError("split-KV exchange: a wait for a peer ran out; the output of that step is invalid "
+                               "(a rank is missing or far behind)")
 
     def close(self) -> None:
         """Release the peer mappings.  Collective: every rank drains its device and meets the others
@@ -337,19 +408,25 @@ class SplitKVDecodeAttentionP2P:
         dist.barrier(self._group)
         self.handle = None
         self.buf = None
-        self.px = None
+        self.px = self.sx = None
 
     def step(self, q: torch.Tensor) -> torch.Tensor:
         from ._lib import check
         ops, kv = self.ops, self.kv
-        kw = dict(top_k=self.top_k) if self.top_k is not None else dict(eps=self.eps)
-        ops.select_blocks(q, self.summ, kv.prefix_lens, out_idx=self.sel_idx, out_count=self.sel_count,
-                          max_sel=int(self.sel_idx.shape[-1]), want=tuple(self.aux), aux_buffers=self.aux, **kw)
         p, s = ops._ptr, ops._stream()
         lo, hi = self.block_range
+        max_sel = int(self.sel_idx.shape[-1])
+        if self.selection == "distributed":
+            check(self.lib.ia_select_split(
+                p(q), self._byref(self.c_summ), p(kv.prefix_lens), self._byref(self.geom), int(self.top_k), max_sel,
+                int(lo), int(hi), p(self.sel_idx), p(self.sel_count), self._byref(self.c_aux), self._byref(self.sx), s))
+        else:
+            kw = dict(top_k=self.top_k) if self.top_k is not None else dict(eps=self.eps)
+            ops.select_blocks(q, self.summ, kv.prefix_lens, out_idx=self.sel_idx, out_count=self.sel_count,
+                              max_sel=max_sel, want=tuple(self.aux), aux_buffers=self.aux, **kw)
         check(self.lib.ia_sparse_decode_exchange(
             p(q), p(kv.k_pool), p(kv.v_pool), p(kv.block_table), p(kv.prefix_lens), p(kv.seq_lens),
-            p(self.sel_idx), p(self.sel_count), int(self.sel_idx.shape[-1]), self._byref(self.c_summ),
+            p(self.sel_idx), p(self.sel_count), max_sel, self._byref(self.c_summ),
             p(self.aux.get("z")), self._byref(self.geom), ops._REP[self.rep_mode], self.n_splits, int(lo), int(hi),
             int(self.with_suffix), self._byref(self.px), s))
         check(self.lib.ia_finalize_exchange(self._byref(self.px), self.rows, self.n_splits, kv.head_dim,

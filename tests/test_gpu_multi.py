@@ -84,12 +84,45 @@ def _rank_main(rank, world, port, rep_mode, result_path):
         graph.replay()
         torch.cuda.synchronize()
         ok = ok and torch.equal(fast.out, eager)
-        # the same step with the exchange inside the kernels (peer stores + flags, no collective call)
-        p2p = partition.SplitKVDecodeAttentionP2P(local, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode,
-                                                  n_splits=3)
+        # The same step with every exchange inside the kernels (peer stores + flags, no collective call),
+        # selection included: this rank's summaries are NaN outside its own (32-aligned) block range, so
+        # the global selection can only come out right through the normaliser and candidate exchange.
+        s_lo, s_hi = partition.plan_block_ranges(nb, world, align=32)[rank]
+
+        def own_range_only(t):
+            keep_blocks = torch.zeros(nb, dtype=torch.bool, device=dev)
+            keep_blocks[s_lo:s_hi] = True
+            shape = (1, 1, nb) + (1,) * (t.dim() - 3)
+            return torch.where(keep_blocks.view(shape), t.float(), torch.tensor(float("nan"), device=dev)).to(t.dtype)
+
+        summ_mine = ops.BlockSummaries(own_range_only(summ.k_bar), own_range_only(summ.k_max),
+                                       own_range_only(summ.k_min), own_range_only(summ.v_bar),
+                                       own_range_only(summ.v_norm_max), summ.block_size)
+        # this rank's pool for the aligned ranges (they differ from the unaligned ones above)
+        keep2 = torch.zeros(case["k_pool"].shape[0], dtype=torch.bool)
+        for b in range(cfg.batch):
+            n_prefix_pages = (cfg.prefix_lens[b] + cfg.page_size - 1) // cfg.page_size
+            mine = [pg for pg in range(s_lo * ppb, min(s_hi * ppb, n_prefix_pages))]
+            if rank == world - 1:
+                mine += list(range(cfg.prefix_lens[b] // cfg.page_size,
+                                   (cfg.prefix_lens[b] + cfg.suffix_lens[b] - 1) // cfg.page_size + 1))
+            keep2[case["block_table"][b, mine].long()] = True
+        nan = torch.tensor(float("nan"))
+        local2 = ops.PagedKV(torch.where(keep2[:, None, None, None], case["k_pool"].float(), nan).to(q.dtype).to(dev),
+                             torch.where(keep2[:, None, None, None], case["v_pool"].float(), nan).to(q.dtype).to(dev),
+                             table, full.prefix_lens, full.seq_lens)
+        p2p = partition.SplitKVDecodeAttentionP2P(local2, summ_mine, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode,
+                                                  n_splits=3, selection="distributed")
         direct = p2p.step(q).clone()
         torch.cuda.synchronize()
-        ok_p2p = torch.allclose(direct.float(), whole.float(), rtol=1e-2, atol=3e-3)
+        want_idx, want_cnt, _ = ops.select_blocks(q, summ, full.prefix_lens, top_k=cfg.top_k)
+        ok_p2p = torch.equal(p2p.sel_idx, want_idx) and torch.equal(p2p.sel_count, want_cnt)   # the global selection
+        ok_p2p = ok_p2p and torch.allclose(direct.float(), whole.float(), rtol=1e-2, atol=3e-3)
+        # and with replicated summaries, every rank selecting on its own
+        rep = partition.SplitKVDecodeAttentionP2P(local2, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode,
+                                                  n_splits=2, selection="replicated")
+        ok_p2p = ok_p2p and torch.allclose(rep.step(q).float(), whole.float(), rtol=1e-2, atol=3e-3)
+        torch.cuda.synchronize()
         for _ in range(3):                                # consecutive steps alternate the two buffer parities
             again = p2p.step(q)
         torch.cuda.synchronize()
@@ -112,7 +145,7 @@ def _rank_main(rank, world, port, rep_mode, result_path):
                                                f"{float((eager.float() - whole.float()).abs().max())} "
                                                f"p2p {ok_p2p} {float((direct.float() - whole.float()).abs().max())}")
         # graphs first, then the peer mappings, a drained device, the other ranks, the communicator
-        partition.ordered_shutdown(graphs=[graph, graph2], steps=[p2p])
+        partition.ordered_shutdown(graphs=[graph, graph2], steps=[p2p, rep])
         with open(f"{result_path}.{rank}.shutdown", "w") as f:
             f.write("clean")
     except Exception as e:   # report and leave at once; the peers' bounded waits let them return too

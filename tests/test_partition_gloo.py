@@ -112,6 +112,105 @@ def test_split_kv_exchange_two_gloo_ranks(tmp_path, rep_mode, world):
         assert open(f"{result}.{r}").read() == "ok"
 
 
+def test_aligned_block_ranges():
+    for n, w in ((2048, 8), (2048, 2), (100, 4), (33, 2), (0, 2), (94, 8), (513, 3)):
+        r = partition.plan_block_ranges(n, w, align=32)
+        assert len(r) == w and r[0][0] == 0 and r[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(r, r[1:]))
+        assert all(lo % 32 == 0 for lo, hi in r if lo < n)           # every start on a 32-block tile
+        assert all(hi % 32 == 0 or hi == n for lo, hi in r)
+
+
+def _distributed_selection_rank(rank, world, port, result_path):
+    """What ia_select_split does, with the oracle's per-block terms and the host-side merges of
+    interattn_b200.partition, over two all-gathers: every rank scores only its own block range and
+    all ranks end up with the oracle's global top-k."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg = scaled(CONFIGS["cfg4_longctx_128k"], batch=1, max_len=6000, suffix=0, top_k=12)
+        case = make_case(cfg)
+        g = cfg.group_size
+        plen = int(case["prefix_lens"][0])
+        k = orc.gather_logical(case["k_pool"], case["block_table"][0], plen)
+        v = orc.gather_logical(case["v_pool"], case["block_table"][0], plen)
+        summ = orc.block_summaries(k, v, cfg.block_size, storage="mixed")
+        qg = case["q"][0].reshape(cfg.n_kv_heads, g, cfg.head_dim).float()
+        nb = summ.n_blocks
+        lo, hi = partition.plan_block_ranges(nb, world, align=32)[rank]
+        # this rank's summaries only: the other blocks are NaN and must never matter
+        mine = orc.Summaries(summ.k_bar[:, lo:hi], summ.v_bar[:, lo:hi], summ.k_max[:, lo:hi], summ.k_min[:, lo:hi],
+                             summ.v_norm_max[:, lo:hi], summ.counts[lo:hi], summ.block_size)
+        rows = cfg.n_kv_heads * g
+        if hi > lo:
+            t = orc.condition_terms(qg, mine)                       # z, delta of the own blocks (its p / score are local: unused)
+            z, delta = t["z"].reshape(rows, -1), t["delta"].reshape(rows, -1)
+            m = z.amax(dim=1)
+            w = torch.exp(z - m[:, None])
+            l, d = w.sum(dim=1), (w * torch.cosh(delta)).sum(dim=1)
+            b_all = mine.v_norm_max.float().amax(dim=1).repeat_interleave(g)
+        else:
+            z = delta = torch.zeros((rows, 0))
+            m, l, d, b_all = torch.full((rows,), float("-inf")), torch.zeros(rows), torch.zeros(rows), torch.zeros(rows)
+        # exchange 1: the row normalisers
+        packed = torch.stack([m, l, d, b_all])                     # [4, rows]
+        gathered = [torch.empty_like(packed) for _ in range(world)]
+        dist.all_gather(gathered, packed)
+        allp = torch.stack(gathered)                                # [world, 4, rows]
+        M, L, D, B = partition.merge_row_normalisers(allp[:, 0], allp[:, 1], allp[:, 2], allp[:, 3])
+        # scores of the own blocks with the global normalisers (the reference's condition score)
+        p_soft = torch.exp(z - M[:, None]) / L[:, None]
+        denom = (D / L).clamp_min(1e-30)
+        b_c = mine.v_norm_max.float().repeat_interleave(g, dim=0) if hi > lo else torch.zeros((rows, 0))
+        cond = p_soft * (2.0 * B[:, None] * (torch.cosh(delta) - 1.0) / denom[:, None] + 2.0 * b_c * torch.tanh(delta / 2.0))
+        score = cond.reshape(cfg.n_kv_heads, g, -1).mean(dim=1)      # [Hkv, own blocks]
+        # exchange 2: the own top-k candidates (score, global block), padded to k
+        kk = cfg.top_k
+        cand_s = torch.full((cfg.n_kv_heads, kk), float("-inf"))
+        cand_b = torch.full((cfg.n_kv_heads, kk), -1, dtype=torch.long)
+        for h in range(cfg.n_kv_heads):
+            ranked, _ = orc.select_topk(score[h:h + 1], mine.counts, kk)
+            chosen = sorted(ranked[0])
+            cand_s[h, : len(chosen)] = score[h, chosen]
+            cand_b[h, : len(chosen)] = torch.tensor(chosen, dtype=torch.long) + lo
+        gs = [torch.empty_like(cand_s) for _ in range(world)]
+        gb = [torch.empty_like(cand_b) for _ in range(world)]
+        dist.all_gather(gs, cand_s)
+        dist.all_gather(gb, cand_b)
+        # the oracle's selection from all blocks at once
+        terms = orc.condition_terms(qg, summ)
+        want, _ = orc.select_topk(terms["score"], summ.counts, kk)
+        ok = True
+        for h in range(cfg.n_kv_heads):
+            sc = [x[h][y[h] >= 0] for x, y in zip(gs, gb)]
+            bl = [y[h][y[h] >= 0] for y in gb]
+            got = partition.merge_topk_candidates(sc, bl, kk).tolist()
+            ok = ok and got == sorted(want[h])
+        with open(f"{result_path}.{rank}", "w") as f:
+            f.write("ok" if ok else "mismatch")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_distributed_selection_protocol_gloo_ranks(tmp_path, world):
+    port = _free_port()
+    result = str(tmp_path / "result")
+    mp.spawn(_distributed_selection_rank, args=(world, port, result), nprocs=world, join=True)
+    for r in range(world):
+        assert open(f"{result}.{r}").read() == "ok"
+
+
+def test_candidate_merge_breaks_ties_towards_the_lower_block():
+    got = partition.merge_topk_candidates([torch.tensor([3.0, 1.0]), torch.tensor([3.0, 3.0])],
+                                          [torch.tensor([2, 5]), torch.tensor([40, 41])], 2)
+    assert got.tolist() == [2, 40]
+    M, L, D, B = partition.merge_row_normalisers(
+        torch.tensor([[0.0], [float("-inf")]]), torch.tensor([[2.0], [0.0]]), torch.tensor([[3.0], [0.0]]),
+        torch.tensor([[1.5], [0.0]]))
+    assert (float(M), float(L), float(D), float(B)) == (0.0, 2.0, 3.0, 1.5)      # a rank without blocks adds nothing
+
+
 def test_allgather_partials_layout_single_rank(tmp_path):
     port = _free_port()
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
