@@ -225,30 +225,8 @@ class ClockSampler:
 # ----------------------------------------------------------------------------
 
 def make_device_layer(cfg, device, seed):
-    """One layer's paged KV cache for the whole batch, generated on the device:
-    N(0,1) K/V (K channels scaled by a log-normal factor), a random permutation
-    as the block table."""
-    import torch
-    from interattn_b200 import ops
-    g = torch.Generator(device=device).manual_seed(seed)
-    P, D, hkv = cfg.page_size, cfg.head_dim, cfg.n_kv_heads
-    pages_per_seq = [(n + s + P - 1) // P for n, s in zip(cfg.prefix_lens, cfg.suffix_lens)]
-    n_pages, max_pages = sum(pages_per_seq), max(pages_per_seq)
-    dt = cfg.torch_dtype
-    k_pool = torch.randn((n_pages, hkv, P, D), generator=g, device=device, dtype=torch.float32)
-    if cfg.k_channel_sigma > 0:
-        k_pool *= torch.exp(cfg.k_channel_sigma * torch.randn((D,), generator=g, device=device))
-    k_pool = k_pool.to(dt)
-    v_pool = torch.randn((n_pages, hkv, P, D), generator=g, device=device, dtype=torch.float32).to(dt)
-    perm = torch.randperm(n_pages, generator=g, device=device).to(torch.int32)
-    table = torch.zeros((cfg.batch, max_pages), dtype=torch.int32, device=device)
-    at = 0
-    for b, n in enumerate(pages_per_seq):
-        table[b, :n] = perm[at: at + n]
-        at += n
-    prefix = torch.tensor(cfg.prefix_lens, dtype=torch.int32, device=device)
-    seq = torch.tensor([p + s for p, s in zip(cfg.prefix_lens, cfg.suffix_lens)], dtype=torch.int32, device=device)
-    return ops.PagedKV(k_pool, v_pool, table, prefix, seq)
+    from interattn_b200.workloads import make_device_layer as make
+    return make(cfg, device, seed)
 
 
 def hbm_peak():
@@ -272,8 +250,9 @@ def committed_traffic(workload, kernel):
     return None
 
 
-def algorithmic_bytes(cfg, rep_mode, kbar_bf16):
-    """(attention kernel, selection kernel) algorithmic bytes per launch."""
+def algorithmic_bytes(cfg, rep_mode, kbar_bf16, bound="range"):
+    """(attention kernel, selection kernel) algorithmic bytes per launch.  The selection reads, per block,
+    k_bar and either (k_max, k_min) or, with the diagonal-ellipsoid bound, (w, rho)."""
     esz = 2 if cfg.dtype == "bfloat16" else 4
     blocks = [(n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens]
     tokens_sel = sum(min(cfg.top_k * cfg.block_size, n) for n in cfg.prefix_lens) * cfg.n_kv_heads
@@ -281,7 +260,8 @@ def algorithmic_bytes(cfg, rep_mode, kbar_bf16):
     kv_bytes = (tokens_sel + suffix_tok) * cfg.head_dim * 2 * esz
     if rep_mode == "hybrid":  # one v_bar row per unselected block
         kv_bytes += sum(max(nb - cfg.top_k, 0) for nb in blocks) * cfg.n_kv_heads * cfg.head_dim * esz
-    sel_bytes = sum(blocks) * cfg.n_kv_heads * (cfg.head_dim * (2 if kbar_bf16 else 4) + 2 * cfg.head_dim * esz + 4)
+    bound_bytes = 2 * cfg.head_dim * esz if bound == "range" else cfg.head_dim * esz + 4
+    sel_bytes = sum(blocks) * cfg.n_kv_heads * (cfg.head_dim * (2 if kbar_bf16 else 4) + bound_bytes + 4)
     return kv_bytes, sel_bytes
 
 
@@ -341,22 +321,24 @@ def kernel_times(torch, steppers, qs, K, repeats):
     return sel, att
 
 
-def variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summaries, n_splits, K, R, workload):
+def variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summaries, n_splits, K, R, workload,
+                   bound="range"):
     """One sub-record: the layer-step in another mode / summary layout, with its own roofline."""
     from interattn_b200 import ops
-    steppers = [ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode, n_splits=n_splits)
+    steppers = [ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode, n_splits=n_splits,
+                                    bound=bound)
                 for (kv, _), summ in zip(layers, summaries)]
     n_pools = len(steppers)
     for i in range(8):
         steppers[i % n_pools].step(qs[i % n_pools])
     ms = regions.run(lambda i: steppers[i % n_pools].step(qs[i % n_pools]), K, R)
     sel_us, att_us = kernel_times(torch, steppers, qs, K, max(1, R // 5))
-    kv_bytes, sel_bytes = algorithmic_bytes(cfg, rep_mode, kbar_bf16)
+    kv_bytes, sel_bytes = algorithmic_bytes(cfg, rep_mode, kbar_bf16, bound)
     peak, src = hbm_peak()
     att_gbs, sel_gbs = kv_bytes / (att_us * 1e-6) / 1e9, sel_bytes / (sel_us * 1e-6) / 1e9
     return {
         "us_per_layer": summarise(ms, K), "kernel_us": {"select": sel_us, "sparse_decode": att_us},
-        "config": {"rep_mode": rep_mode, "k_bar": "bf16" if kbar_bf16 else "f32"},
+        "config": {"rep_mode": rep_mode, "k_bar": "bf16" if kbar_bf16 else "f32", "bound": bound},
         "roofline": {"bound": "hbm", "kernel": "condition_block_finalize_attention_kernel", "achieved": att_gbs,
                      "peak": peak, "peak_source": src, "unit": "GB/s", "frac": att_gbs / peak,
                      "bytes_per_launch": kv_bytes, "traffic": committed_traffic(workload, f"sparse_decode_{rep_mode}")},
@@ -540,6 +522,12 @@ def layer_step_record(args, workload, torch, dist, regions, world, rank, local_r
                          for kv, _ in layers]
             line["kbar_bf16"] = variant_record(torch, regions, cfg, layers, qs, args.rep_mode, True, summ_bf16,
                                                n_splits, K, Rv, workload)
+            del summ_bf16
+            # the diagonal-ellipsoid bound: (k_bar, w, rho) per block instead of (k_bar, k_max, k_min)
+            summ_ell = [ops.build_summaries(kv, cfg.block_size, max_blocks=nb, diag_ell=True) for kv, _ in layers]
+            line["diag_ell"] = variant_record(torch, regions, cfg, layers, qs, args.rep_mode, False, summ_ell,
+                                              n_splits, K, Rv, workload, bound="diag_ell")
+            del summ_ell
     return line
 
 

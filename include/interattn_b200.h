@@ -97,6 +97,13 @@ typedef struct ia_geom {
  * approximate with respect to the fp32 k_bar and may rank near-equal blocks differently.  768
  * instead of 1024 summary bytes per block and kv head at head_dim 128. */
 #define IA_GEOM_KBAR_BF16 1
+/* ia_geom.reserved flag: the selection bounds |q . (k - k_bar)| with the diagonal-ellipsoid summaries
+ * (ia_summaries.w, .rho) instead of the coordinate range (k_max, k_min) - the "diag_ell" bound of the
+ * reference's condition_block_ball study (condition_block_ball/gen_selection.py:21-87, verdict in
+ * condition_block_ball/README.md:228-241): w = max(k_max - k_bar, k_bar - k_min) clamped at 1e-6,
+ * rho = max_t |(k_t - k_bar) / w|, delta = rho |q * w| / sqrt(D).  Two vectors and a scalar per block
+ * instead of three vectors; k_max / k_min are then not read by ia_select (and may be null there). */
+#define IA_GEOM_DIAG_ELL 2
 
 /* Block summaries, "mixed" storage of the reference (IMPL/core.py:411-446):
  * means accumulated in fp32, k_bar kept in fp32, the rest in the KV dtype
@@ -107,6 +114,12 @@ typedef struct ia_summaries {
   void* k_min;       /* same shape, dtype */
   void* v_bar;       /* same shape, dtype */
   float* v_norm_max; /* [batch, n_kv_heads, max_blocks] f32: max token |v|_2 in the block */
+  /* Optional (null: not kept): the diagonal-ellipsoid pair of IA_GEOM_DIAG_ELL.  w in the KV dtype -
+   * with bf16 pools rounded up by 1 + 2^-7 before the cast, the reference's
+   * CONDITION_BLOCK_BALL_W_DTYPE=bfloat16 option, so that the bound stays strict - and rho computed
+   * from the stored w.  ia_build_summaries / ia_update_summaries fill them when both are given. */
+  void* w;           /* [batch, n_kv_heads, max_blocks, head_dim] dtype */
+  float* rho;        /* [batch, n_kv_heads, max_blocks] f32 */
 } ia_summaries;
 
 /* Optional diagnostics of ia_select; any pointer may be null. */
@@ -118,7 +131,8 @@ typedef struct ia_select_aux {
   float* globals; /* [batch, 4, rows]  z_m, z_l, c_m, c_l (online-softmax normalisers) */
 } ia_select_aux;
 
-/* Version of this ABI; bumped on any incompatible change (2: ia_geom carries n_pool_pages). */
+/* Version of this ABI; bumped on any incompatible change (2: ia_geom carries n_pool_pages; 3: ia_summaries
+ * carries the optional diagonal-ellipsoid pair w, rho). */
 int ia_abi_version(void);
 
 /* Message for the last non-OK status returned on the calling thread. */

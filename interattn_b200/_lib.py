@@ -23,8 +23,9 @@ IA_F32, IA_BF16 = 0, 1
 IA_SELECT_TOPK, IA_SELECT_EPS = 0, 1
 IA_SELECT_TERM1_MASS_EXP = 0x100   # OR-ed into the mode
 IA_GEOM_KBAR_BF16 = 1              # ia_geom.reserved flag: k_bar stored in bf16
+IA_GEOM_DIAG_ELL = 2               # ia_geom.reserved flag: the selection uses the (w, rho) bound
 IA_REP_SPARSE_ONLY, IA_REP_HYBRID = 0, 1
-ABI_VERSION = 2
+ABI_VERSION = 3
 # masks of the device status word (ia_read_device_status)
 IA_DEV_STATUS_SELECT_WAIT, IA_DEV_STATUS_GEMM_WAIT, IA_DEV_STATUS_PEER_WAIT, IA_DEV_STATUS_BAD_INDEX = 1, 2, 4, 8
 
@@ -40,7 +41,7 @@ class Geom(Structure):
 
 class Summaries(Structure):
     _fields_ = [("k_bar", c_void_p), ("k_max", c_void_p), ("k_min", c_void_p), ("v_bar", c_void_p),
-                ("v_norm_max", c_void_p)]
+                ("v_norm_max", c_void_p), ("w", c_void_p), ("rho", c_void_p)]
 
 
 class SelectAux(Structure):

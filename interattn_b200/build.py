@@ -1,6 +1,7 @@
 """In-tree build of libinterattn_b200.so (nvcc, sm_100a only).
 
     python -m interattn_b200.build [--force] [--verbose]
+    python -m interattn_b200.build --define IA_SELECT_TRACE --define IA_DECODE_TRACE --output <path>.so
 
 The shared library lands next to this file so that it travels with the source
 tree; nothing is installed into site-packages and nothing is JIT-compiled at
@@ -48,16 +49,24 @@ def _stale(target: str, deps) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    os.makedirs(OBJ_DIR, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, defines=(), output: str = None) -> str:
+    """Compile the library.  ``defines`` / ``output`` build a variant beside the normal one (its
+    objects in their own folder), e.g. the phase-trace build: ``defines=("IA_SELECT_TRACE",
+    "IA_DECODE_TRACE"), output=".../libinterattn_b200_trace.so"``."""
+    variant = "_".join(sorted(defines))
+    obj_dir = OBJ_DIR if not variant else OBJ_DIR + "_" + variant.lower()
+    lib_path = output or LIB_PATH
+    if variant and output is None:
+        raise ValueError("a variant build needs its own output path")
+    os.makedirs(obj_dir, exist_ok=True)
     nvcc = _nvcc()
     objs = []
     jobs = []
     for src in SOURCES:
-        obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
+        obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
         objs.append(obj)
         if force or _stale(obj, _deps(src)):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", os.path.join(CSRC, src), "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")
@@ -73,14 +82,16 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if jobs:
         with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 1)) as pool:
             list(pool.map(run, jobs))
-    if jobs or force or _stale(LIB_PATH, objs):
-        run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB_PATH, *objs, "-lcudart"])
-    return LIB_PATH
+    if jobs or force or _stale(lib_path, objs):
+        run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", lib_path, *objs, "-lcudart"])
+    return lib_path
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--define", action="append", default=[], help="preprocessor symbol of a variant build")
+    ap.add_argument("--output", default=None, help="where a variant build goes")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose))
+    print(build(force=a.force, verbose=a.verbose, defines=tuple(a.define), output=a.output))

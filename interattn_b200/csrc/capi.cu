@@ -64,17 +64,24 @@ int check_geom(const ia_geom* g) {
   const int64_t esz = g->dtype == IA_BF16 ? 2 : 4;
   if ((g->pool_head_stride * esz) % 16 != 0 || (g->pool_page_stride * esz) % 16 != 0)
     return fail(IA_ERR_BAD_ARG, "geom: pool strides must be multiples of 16 bytes");
+  if (g->reserved & ~(IA_GEOM_KBAR_BF16 | IA_GEOM_DIAG_ELL))
+    return fail(IA_ERR_BAD_ARG, "geom: unknown flag bits in reserved (%d)", g->reserved);
   if (g->n_pool_pages < 0 || g->reserved2 != 0)
     return fail(IA_ERR_BAD_ARG, "geom: n_pool_pages %d (0 = unknown), reserved2 %d (must be 0)", g->n_pool_pages,
                 g->reserved2);
   return IA_OK;
 }
 
-static int check_summaries(const ia_summaries* s) {
+// diag_ell: the selection reads (k_bar, w, rho) and k_max / k_min may be absent; building summaries
+// always needs k_max / k_min as outputs (w is derived from them)
+static int check_summaries(const ia_summaries* s, const ia_geom* g = nullptr, bool building = false) {
   if (s == nullptr) return fail(IA_ERR_BAD_ARG, "summaries is null");
-  if (!s->k_bar || !s->k_max || !s->k_min || !s->v_bar || !s->v_norm_max)
-    return fail(IA_ERR_BAD_ARG, "summaries: null member");
-  if (!aligned16(s->k_bar) || !aligned16(s->k_max) || !aligned16(s->k_min) || !aligned16(s->v_bar))
+  const bool diag = g != nullptr && (g->reserved & IA_GEOM_DIAG_ELL) != 0;
+  if (!s->k_bar || !s->v_bar || !s->v_norm_max) return fail(IA_ERR_BAD_ARG, "summaries: null member");
+  if ((!diag || building) && (!s->k_max || !s->k_min)) return fail(IA_ERR_BAD_ARG, "summaries: null k_max / k_min");
+  if ((diag || s->w || s->rho) && (!s->w || !s->rho))
+    return fail(IA_ERR_BAD_ARG, "summaries: the diagonal-ellipsoid bound needs both w and rho");
+  if (!aligned16(s->k_bar) || !aligned16(s->k_max) || !aligned16(s->k_min) || !aligned16(s->v_bar) || !aligned16(s->w))
     return fail(IA_ERR_BAD_ARG, "summaries: arrays must be 16-byte aligned");
   return IA_OK;
 }
@@ -125,7 +132,7 @@ using namespace ia;
 
 extern "C" {
 
-int ia_abi_version(void) { return 2; }
+int ia_abi_version(void) { return 3; }
 
 const char* ia_last_error_string(void) { return tls_error; }
 
@@ -140,7 +147,7 @@ int ia_build_summaries(const void* k_pool, const void* v_pool, const int32_t* bl
                        const int32_t* prefix_lens, const ia_geom* geom, const ia_summaries* out,
                        ia_stream_t stream) {
   if (int s = check_geom(geom)) return s;
-  if (int s = check_summaries(out)) return s;
+  if (int s = check_summaries(out, geom, true)) return s;
   if (!k_pool || !v_pool || !block_table || !prefix_lens) return fail(IA_ERR_BAD_ARG, "build_summaries: null argument");
   if (!aligned16(k_pool) || !aligned16(v_pool)) return fail(IA_ERR_BAD_ARG, "build_summaries: pools must be 16-byte aligned");
   return launch_build_summaries(k_pool, v_pool, block_table, prefix_lens, nullptr, *geom, *out, (cudaStream_t)stream);
@@ -150,7 +157,7 @@ int ia_update_summaries(const void* k_pool, const void* v_pool, const int32_t* b
                         const int32_t* prefix_lens, const int32_t* first_blocks, const ia_geom* geom,
                         const ia_summaries* out, ia_stream_t stream) {
   if (int s = check_geom(geom)) return s;
-  if (int s = check_summaries(out)) return s;
+  if (int s = check_summaries(out, geom, true)) return s;
   if (!k_pool || !v_pool || !block_table || !prefix_lens || !first_blocks)
     return fail(IA_ERR_BAD_ARG, "update_summaries: null argument");
   if (!aligned16(k_pool) || !aligned16(v_pool)) return fail(IA_ERR_BAD_ARG, "update_summaries: pools must be 16-byte aligned");
@@ -162,7 +169,7 @@ int ia_select(const void* q, const ia_summaries* summaries, const int32_t* prefi
               const ia_geom* geom, int mode, int top_k, float eps, int max_sel, int32_t* sel_idx,
               int32_t* sel_count, const ia_select_aux* aux, ia_stream_t stream) {
   if (int s = check_geom(geom)) return s;
-  if (int s = check_summaries(summaries)) return s;
+  if (int s = check_summaries(summaries, geom)) return s;
   if (!q || !prefix_lens || !sel_idx || !sel_count) return fail(IA_ERR_BAD_ARG, "select: null argument");
   const int full_mode = mode;
   mode &= 0xff;  // the high bits carry the score variant (IA_SELECT_TERM1_MASS_EXP)
@@ -183,7 +190,7 @@ int ia_select_split(const void* q, const ia_summaries* summaries, const int32_t*
                     int top_k, int max_sel, int block_lo, int block_hi, int32_t* sel_idx, int32_t* sel_count,
                     const ia_select_aux* aux, const ia_select_exchange* x, ia_stream_t stream) {
   if (int s = check_geom(geom)) return s;
-  if (int s = check_summaries(summaries)) return s;
+  if (int s = check_summaries(summaries, geom)) return s;
   if (!q || !prefix_lens || !sel_idx || !sel_count || !x) return fail(IA_ERR_BAD_ARG, "select_split: null argument");
   if (max_sel <= 0 || top_k < 0 || top_k > max_sel)
     return fail(IA_ERR_BAD_ARG, "select_split: top_k %d outside [0, max_sel %d]", top_k, max_sel);
@@ -371,7 +378,7 @@ static int decode_attention_impl(const void* q, const void* k_pool, const void* 
   // kernel (which also clears the per-pair split counters) and the attention kernel
   // with the fused finalize - the CTA that finishes a (sequence, kv head) last merges
   // its splits and writes `out`, so no third kernel is needed.
-  if (int s = check_summaries(summaries)) return s;
+  if (int s = check_summaries(summaries, geom)) return s;
   if (!q || !k_pool || !v_pool || !block_table || !prefix_lens || !seq_lens)
     return fail(IA_ERR_BAD_ARG, "decode_attention: null argument");
   if (!aligned16(k_pool) || !aligned16(v_pool) || !aligned16(q) || !aligned16(out))

@@ -170,8 +170,11 @@ __device__ __forceinline__ ResolvedItem resolve_one(const DecodeParams& p, const
                                                     int hi_b, int suf_first_page, int prefix, int seq_len) {
   const int ppb = p.block_size / p.page_size;
   ResolvedItem it;
+  // The index entry is fetched before `i < n_sel_items` is known (the position is clamped into the
+  // list): when the caller has not waited for the count yet, the two loads overlap instead of chaining.
+  const int blk_spec = idx[min(max(sel_first + i / ppb, 0), p.max_sel - 1)];
   if (i < n_sel_items) {
-    const int blk = idx[sel_first + i / ppb];
+    const int blk = blk_spec;
     it.kind = ITEM_PAGE;
     it.lo = 0;
     it.hi = 0;

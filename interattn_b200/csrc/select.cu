@@ -121,6 +121,7 @@ struct SelectParams {
   const void* k_max;
   const void* k_min;
   const float* v_norm_max;
+  const float* rho;  // diag_ell bound only: [pairs, max_blocks]; tm_kmax then describes w
   const int32_t* prefix_lens;
   int n_kv_heads, max_blocks, block_size;
   int mode, top_k, max_sel;
@@ -317,13 +318,14 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&o)[8]) {
 // 128-byte swizzle: the 16-byte chunk c of row r lands at chunk c ^ (r & 7).
 // Lane r walking its own row therefore hits eight different bank groups per
 // quarter-warp - no padding, no conflicts.
-template <typename T, int D, typename KB = float> struct TileLayout {
+// DIAG: the stage holds k_bar and w (the diagonal-ellipsoid bound) instead of k_bar, k_max and k_min.
+template <typename T, int D, typename KB = float, bool DIAG = false> struct TileLayout {
   static constexpr int box_bytes = 128 * kTileBlocks;
   static constexpr int kbar_boxes = D * (int)sizeof(KB) / 128;
   static constexpr int bnd_boxes = D * (int)sizeof(T) / 128;
   static constexpr int kbar_bytes = kbar_boxes * box_bytes;
   static constexpr int bnd_bytes = bnd_boxes * box_bytes;
-  static constexpr int bytes = kbar_bytes + 2 * bnd_bytes;
+  static constexpr int bytes = kbar_bytes + (DIAG ? 1 : 2) * bnd_bytes;
   static constexpr int kbar_box_cols = 128 / (int)sizeof(KB);  // k_bar elements per 128 bytes
   static constexpr int bnd_box_cols = 128 / (int)sizeof(T);
 };
@@ -351,18 +353,19 @@ template <int D, int G, bool MMA, int NG> struct SmemPlan {
   static constexpr size_t xst = 16 * 4 * 4;      // [row][m, l, d, b_all] of this GPU, on its way to the peers
   static constexpr size_t fixed = bars + hist + scan + red + norm + state + qrows + part + xch + xst;
   static size_t per_blocks(int nb_cap, int nb_loc_cap, int n_candidates = 0) {
-    return (size_t)nb_cap * 4 * 2 + (size_t)nb_loc_cap * 4 * 2 * G + (size_t)n_candidates * 8;
+    return (size_t)nb_cap * 4 * 3 + (size_t)nb_loc_cap * 4 * 2 * G + (size_t)n_candidates * 8;
   }
 };
 
-template <typename T, int D, int G, int NG, typename KB>
+template <typename T, int D, int G, int NG, typename KB, bool DIAG>
 __global__ void __launch_bounds__(Shape<NG>::threads, Shape<NG>::min_ctas)
 condition_block_select_kernel(const __grid_constant__ SelectParams p) {
-  using L = TileLayout<T, D, KB>;
+  using L = TileLayout<T, D, KB, DIAG>;
   using P = SmemPlan<D, G, kUseMma<T, G>, NG>;
   constexpr int kGroups = NG, kConsumerWarps = Shape<NG>::consumer_warps, kWarps = Shape<NG>::warps,
                 kThreads = Shape<NG>::threads;
   constexpr int DQ = D / kGroupWarps;  // head_dim slice of one warp of a group
+  static_assert(kWarps <= 16, "a scratch row of the compaction holds 16 warps");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int C = p.cluster;
@@ -427,7 +430,8 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
   float* xst_s = reinterpret_cast<float*>(sp);         sp += P::xst;    // [16][4] this GPU's row normalisers
   float* vn_s = reinterpret_cast<float*>(sp);                           // [nb_cap]
   float* score_s = vn_s + nb_cap;                                       // [nb_cap]
-  float* z_s = score_s + nb_cap;                                        // [G][nbl]: z = s + log count (own blocks)
+  float* rho_s = score_s + nb_cap;                                      // [nb_cap] (diag_ell bound only)
+  float* z_s = rho_s + nb_cap;                                          // [G][nbl]: z = s + log count (own blocks)
   float* d_s = z_s + (size_t)G * nbl;                                   // [G][nbl]: delta (range bound)
   // split-KV: the ranks' top-k candidates, gathered: [n_ranks * max_sel] scores and block indices
   float* cand_s = d_s + (size_t)G * nbl;
@@ -448,8 +452,9 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
 #pragma unroll
     for (int j = 0; j < L::bnd_boxes; ++j) {
       tma_load_2d(st + L::kbar_bytes + j * L::box_bytes, &p.tm_kmax, j * L::bnd_box_cols, y, &full_bar[stage]);
-      tma_load_2d(st + L::kbar_bytes + L::bnd_bytes + j * L::box_bytes, &p.tm_kmin, j * L::bnd_box_cols, y,
-                  &full_bar[stage]);
+      if constexpr (!DIAG)
+        tma_load_2d(st + L::kbar_bytes + L::bnd_bytes + j * L::box_bytes, &p.tm_kmin, j * L::bnd_box_cols, y,
+                    &full_bar[stage]);
     }
   };
   // The producer lane owns the barriers: it initialises them and fills the ring's first uses while
@@ -475,7 +480,7 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     for (int i = tid; i < G * D; i += kConsumerWarps * 32) {
       const float v = to_f32(qrow[i]);
       q_s[i] = v;
-      aq_s[i] = fabsf(v);
+      aq_s[i] = DIAG ? v * v : fabsf(v);  // what the CUDA-core form multiplies the bound vector with
     }
   }
   const float* vn_g = p.v_norm_max + (int64_t)pair * p.max_blocks;
@@ -494,6 +499,12 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           const int b = base + j * kStride;
           if (b < p.max_blocks) vn_s[b] = v[j];
           if (b >= r_lo && b < r_hi) bmax = fmaxf(bmax, v[j]);
+        }
+        if constexpr (DIAG) {
+          const float* rho_g = p.rho + (int64_t)pair * p.max_blocks;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (base + j * kStride < p.max_blocks) rho_s[base + j * kStride] = rho_g[base + j * kStride];
         }
       }
       bmax = warp_max(bmax);
@@ -544,6 +555,24 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         const float x1 = n < G ? q_s[n * D + kk * 16 + h * 8 + kq * 2 + 1] : 0.f;
         bp[kk][h] = pack_bf16(fmaxf(x0, 0.f), fmaxf(x1, 0.f));
         bm[kk][h] = pack_bf16(fminf(x0, 0.f), fminf(x1, 0.f));
+      }
+    }
+    // diag_ell bound: sum_d q_d^2 w_d^2 on the tensor cores with exact operands - the square of a
+    // bf16 value has 16 significant bits and splits exactly into two bf16 pieces, for q^2 (here, once)
+    // and for w^2 (below, per tile); the four partial products are accumulated in fp32.
+    uint32_t bq2h[D / 16][2], bq2l[D / 16][2];
+    if constexpr (DIAG) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float x0 = n < G ? q_s[n * D + kk * 16 + h * 8 + kq * 2] : 0.f;
+          const float x1 = n < G ? q_s[n * D + kk * 16 + h * 8 + kq * 2 + 1] : 0.f;
+          const float s0 = x0 * x0, s1 = x1 * x1;
+          const float h0 = __bfloat162float(__float2bfloat16_rn(s0)), h1 = __bfloat162float(__float2bfloat16_rn(s1));
+          bq2h[kk][h] = pack_bf16(h0, h1);
+          bq2l[kk][h] = pack_bf16(s0 - h0, s1 - h1);
+        }
       }
     }
     // ldmatrix row addressing: matrix m of the x4 = (rows 8 (m & 1) .., 16-byte chunk (m >> 1))
@@ -601,11 +630,28 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         const uint32_t off = (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4);
         uint32_t a[4];
         ldmatrix_x4(st + L::kbar_bytes + off, a);
-        mma_bf16(xp, a, bp[kk]);
-        mma_bf16(xm, a, bm[kk]);
-        ldmatrix_x4(st + L::kbar_bytes + L::bnd_bytes + off, a);
-        mma_bf16(np_, a, bp[kk]);
-        mma_bf16(nm, a, bm[kk]);
+        if constexpr (DIAG) {
+          // a = 16 x 16 fragment of w; square it in registers and split each square into two bf16 pieces
+          uint32_t ah[4], al[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float w0 = bf16lo(a[i]), w1 = bf16hi(a[i]);
+            const float s0 = w0 * w0, s1 = w1 * w1;
+            const float h0 = __bfloat162float(__float2bfloat16_rn(s0)), h1 = __bfloat162float(__float2bfloat16_rn(s1));
+            ah[i] = pack_bf16(h0, h1);
+            al[i] = pack_bf16(s0 - h0, s1 - h1);
+          }
+          mma_bf16(xp, ah, bq2h[kk]);
+          mma_bf16(xp, ah, bq2l[kk]);
+          mma_bf16(xp, al, bq2h[kk]);
+          mma_bf16(xp, al, bq2l[kk]);
+        } else {
+          mma_bf16(xp, a, bp[kk]);
+          mma_bf16(xm, a, bm[kk]);
+          ldmatrix_x4(st + L::kbar_bytes + L::bnd_bytes + off, a);
+          mma_bf16(np_, a, bp[kk]);
+          mma_bf16(nm, a, bm[kk]);
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp is done with the stage
@@ -616,9 +662,14 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         if (g < G && b < nb) {
           const int count = min(p.block_size, prefix - b * p.block_size);
           const float s = dotv / root;
-          const float upper = up / root;  // sum_d max(q k_max, q k_min)
-          const float lower = lw / root;  // sum_d min(q k_max, q k_min)
-          const float delta = fmaxf(fabsf(upper - s), fabsf(lower - s));
+          float delta;
+          if constexpr (DIAG) {  // up = sum_d q_d^2 w_d^2 (condition_block_ball/gen_selection.py:82-87)
+            delta = rho_s[b] * sqrtf(fmaxf(up, 0.f)) / root;
+          } else {
+            const float upper = up / root;  // sum_d max(q k_max, q k_min)
+            const float lower = lw / root;  // sum_d min(q k_max, q k_min)
+            delta = fmaxf(fabsf(upper - s), fabsf(lower - s));
+          }
           const float z = (count == p.block_size ? log_full : logf((float)count)) + s;
           float ch, a_term, th;
           delta_terms(delta, p.mass_exp, ch, a_term, th);
@@ -716,16 +767,22 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         }
         if constexpr (sizeof(T) == 2) {
           load8(swz<T>(kmax_v, lane, e0), hi);
-          load8(swz<T>(kmin_v, lane, e0), lo);
+          if constexpr (!DIAG) load8(swz<T>(kmin_v, lane, e0), lo);
         } else {
           load4(swz<float>(kmax_v, lane, e0), hi);
           load4(swz<float>(kmax_v, lane, e0 + 4), hi + 4);
-          load4(swz<float>(kmin_v, lane, e0), lo);
-          load4(swz<float>(kmin_v, lane, e0 + 4), lo + 4);
+          if constexpr (!DIAG) {
+            load4(swz<float>(kmin_v, lane, e0), lo);
+            load4(swz<float>(kmin_v, lane, e0 + 4), lo + 4);
+          }
         }
+        // range bound: centre and span of [k_min, k_max]; diag_ell bound: hi holds w, span = w^2 meets q^2
         float ctr[8], span[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { ctr[i] = hi[i] + lo[i]; span[i] = hi[i] - lo[i]; }
+        for (int i = 0; i < 8; ++i) {
+          if constexpr (DIAG) { ctr[i] = 0.f; span[i] = hi[i] * hi[i]; }
+          else { ctr[i] = hi[i] + lo[i]; span[i] = hi[i] - lo[i]; }
+        }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
           float qv[8], av[8];
@@ -761,11 +818,16 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
             for (int w = 0; w < kGroupWarps; ++w) acc += grp_part[((size_t)w * 3 * G + g * 3 + j) * 32 + lane];
             v[j] = acc;
           }
-          // sum_d max(q k_max, q k_min) = (mid + wid) / 2, sum_d min(...) = (mid - wid) / 2
           const float s = v[0] / root;
-          const float upper = (0.5f * (v[1] + v[2])) / root;
-          const float lower = (0.5f * (v[1] - v[2])) / root;
-          const float delta = fmaxf(fabsf(upper - s), fabsf(lower - s));
+          float delta;
+          if constexpr (DIAG) {  // v[2] = sum_d q_d^2 w_d^2
+            delta = rho_s[b] * sqrtf(fmaxf(v[2], 0.f)) / root;
+          } else {
+            // sum_d max(q k_max, q k_min) = (mid + wid) / 2, sum_d min(...) = (mid - wid) / 2
+            const float upper = (0.5f * (v[1] + v[2])) / root;
+            const float lower = (0.5f * (v[1] - v[2])) / root;
+            delta = fmaxf(fabsf(upper - s), fabsf(lower - s));
+          }
           const float z = logc + s;
           float ch, a_term, th;
           delta_terms(delta, p.mass_exp, ch, a_term, th);
@@ -979,15 +1041,30 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
           const uint32_t key = b < n ? order_key(sc[b]) : 0u;
           const bool live = b < n && (key & fixed_mask) == fixed;
           const uint32_t digit = (key >> shift) & 255u;
-          // scores cluster in a few bins: the lanes that share a digit send one atomic together
-          const uint32_t peers = __match_any_sync(0xffffffffu, live ? digit : 0xffffffffu);
-          if (live && lane == __ffs(peers) - 1) atomicAdd(&h[digit], __popc(peers));
+          // Bin d lives at word (d & 7) * 32 + (d >> 3): the eight bins a lane scans below are then in
+          // eight different rows of 32 consecutive words, so the scan's loads are free of bank conflicts
+          // (a [256] array read as h[8 lane + i] is an 8-way conflict, paid by every warp in every pass).
+          // The leading digit (sign and high exponent bits) is shared by most keys: there the lanes of
+          // a warp that share a digit send one atomic together; the later digits are spread, and finding
+          // equal ones costs more than the few conflicts it would save.
+          if (pass == 0) {
+            const uint32_t peers = __match_any_sync(0xffffffffu, live ? digit : 0xffffffffu);
+            if (live && lane == __ffs(peers) - 1) atomicAdd(&h[(digit & 7u) * 32u + (digit >> 3)], __popc(peers));
+          } else if (live) {
+            atomicAdd(&h[(digit & 7u) * 32u + (digit >> 3)], 1);
+          }
         }
+#ifdef IA_SELECT_TRACE_FINE
+        if (pass < 2) IA_TRACE(9 + 3 * pass);
+#endif
         __syncthreads();
+#ifdef IA_SELECT_TRACE_FINE
+        if (pass < 2) IA_TRACE(10 + 3 * pass);
+#endif
         // lane owns bins [8 lane, 8 lane + 8); `above` = keys in the bins of higher lanes
         int c[8], mine = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { c[i] = h[lane * 8 + i]; mine += c[i]; }
+        for (int i = 0; i < 8; ++i) { c[i] = h[i * 32 + lane]; mine += c[i]; }
         int incl = mine;  // inclusive suffix sum over lanes
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -1012,6 +1089,11 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         in_bin = __shfl_sync(0xffffffffu, in_bin, src);
         fixed |= (uint32_t)digit << shift;
         fixed_mask |= 255u << shift;
+#ifdef IA_SELECT_TRACE_FINE
+        if (pass < 2) IA_TRACE(11 + 3 * pass);
+#else
+        IA_TRACE(9 + pass);
+#endif
         // every key of the threshold bin is wanted: the remaining digits cannot change the outcome
         if (in_bin == remaining) break;
       }
@@ -1046,16 +1128,18 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
         // exclusive scan of (gt, eq) over the block
         const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
         const uint32_t below = (1u << lane) - 1u;
-        if (lane == 0) scan_scratch[warp] = __popc(bg) | (__popc(be) << 16);
+        // two scratch rows used alternately: the row of this iteration is not rewritten before every
+        // warp has passed the barrier of the next one, so one barrier per iteration is enough
+        int* scan_row = scan_scratch + ((base / kThreads) & 1) * 16;
+        if (lane == 0) scan_row[warp] = __popc(bg) | (__popc(be) << 16);
         __syncthreads();
         int packed_before = 0, packed_total = 0;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
-          const int c = scan_scratch[w];
+          const int c = scan_row[w];
           if (w < warp) packed_before += c;
           packed_total += c;
         }
-        __syncthreads();
         const int gt_before = gt_seen + (packed_before & 0xffff) + __popc(bg & below);
         const int eq_before = eq_seen + (packed_before >> 16) + __popc(be & below);
         const bool take = gt || (eq && eq_before < take_equal);
@@ -1170,9 +1254,9 @@ static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t 
   return IA_OK;
 }
 
-template <typename T, int D, int G, int NG, typename KB>
+template <typename T, int D, int G, int NG, typename KB, bool DIAG>
 static int launch_shaped(const SelectParams& p, int n_pairs, size_t smem, cudaStream_t stream) {
-  auto kern = condition_block_select_kernel<T, D, G, NG, KB>;
+  auto kern = condition_block_select_kernel<T, D, G, NG, KB, DIAG>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "select: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   e = launch_overlapped(kern, (unsigned)(n_pairs * p.cluster), (unsigned)Shape<NG>::threads, smem, stream, p,
@@ -1181,9 +1265,9 @@ static int launch_shaped(const SelectParams& p, int n_pairs, size_t smem, cudaSt
   return check_launch("condition_block_select_kernel");
 }
 
-template <typename T, int D, int G, typename KB>
+template <typename T, int D, int G, typename KB, bool DIAG>
 static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stream) {
-  using L = TileLayout<T, D, KB>;
+  using L = TileLayout<T, D, KB, DIAG>;
   using PW = SmemPlan<D, G, kUseMma<T, G>, kWideGroups>;
   using PN = SmemPlan<D, G, kUseMma<T, G>, kNarrowGroups>;
   SelectParams p = base;
@@ -1216,8 +1300,8 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   const int64_t rows = (int64_t)n_pairs * p.max_blocks;
   if (rows > 0x7fffffff) return fail(IA_ERR_UNSUPPORTED, "select: %lld summary rows exceed the TMA coordinate range", (long long)rows);
   if (int s = encode_rows(&p.tm_kbar, p.k_bar, sizeof(KB) == 2, rows, D)) return s;
-  if (int s = encode_rows(&p.tm_kmax, p.k_max, sizeof(T) == 2, rows, D)) return s;
-  if (int s = encode_rows(&p.tm_kmin, p.k_min, sizeof(T) == 2, rows, D)) return s;
+  if (int s = encode_rows(&p.tm_kmax, p.k_max, sizeof(T) == 2, rows, D)) return s;  // diag_ell: k_max is w
+  if (int s = encode_rows(&p.tm_kmin, DIAG ? p.k_max : p.k_min, sizeof(T) == 2, rows, D)) return s;
 
   // Narrow shape: more pairs than SMs and room for two or three CTAs per SM (each CTA pays 1 KB of
   // reserved shared memory) with a ring of at least two stages.  A cluster of narrow CTAs per pair
@@ -1248,7 +1332,7 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
         if (stages > my_tiles) stages = my_tiles < 2 ? 2 : my_tiles;
         if (stages > kMaxStages) stages = kMaxStages;
         p.n_stages = stages;
-        return launch_shaped<T, D, G, kNarrowGroups, KB>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
+        return launch_shaped<T, D, G, kNarrowGroups, KB, DIAG>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
       }
       break;  // the narrow shape is only ever tried with the cluster chosen above (1 unless pinned)
     }
@@ -1262,19 +1346,24 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   int stages = (int)(((size_t)max_smem - fixed) / L::bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.n_stages = stages;
-  return launch_shaped<T, D, G, kWideGroups, KB>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
+  return launch_shaped<T, D, G, kWideGroups, KB, DIAG>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
 }
 
-template <typename T, int D, typename KB = float>
-static int launch_group(const SelectParams& p, int n_pairs, int group, cudaStream_t stream) {
+template <typename T, int D, typename KB, bool DIAG>
+static int launch_group_bound(const SelectParams& p, int n_pairs, int group, cudaStream_t stream) {
   switch (group) {
-    case 1: return launch_typed<T, D, 1, KB>(p, n_pairs, stream);
-    case 2: return launch_typed<T, D, 2, KB>(p, n_pairs, stream);
-    case 4: return launch_typed<T, D, 4, KB>(p, n_pairs, stream);
-    case 8: return launch_typed<T, D, 8, KB>(p, n_pairs, stream);
-    case 16: return launch_typed<T, D, 16, KB>(p, n_pairs, stream);
+    case 1: return launch_typed<T, D, 1, KB, DIAG>(p, n_pairs, stream);
+    case 2: return launch_typed<T, D, 2, KB, DIAG>(p, n_pairs, stream);
+    case 4: return launch_typed<T, D, 4, KB, DIAG>(p, n_pairs, stream);
+    case 8: return launch_typed<T, D, 8, KB, DIAG>(p, n_pairs, stream);
+    case 16: return launch_typed<T, D, 16, KB, DIAG>(p, n_pairs, stream);
     default: return fail(IA_ERR_UNSUPPORTED, "select: group_size %d not built (1, 2, 4, 8, 16)", group);
   }
+}
+template <typename T, int D, typename KB = float>
+static int launch_group(const SelectParams& p, int n_pairs, int group, cudaStream_t stream) {
+  return p.rho != nullptr ? launch_group_bound<T, D, KB, true>(p, n_pairs, group, stream)
+                          : launch_group_bound<T, D, KB, false>(p, n_pairs, group, stream);
 }
 
 }  // namespace
@@ -1291,6 +1380,11 @@ int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_le
   }
   p.n_pairs = g.batch * g.n_kv_heads;
   p.q = q; p.k_bar = s.k_bar; p.k_max = s.k_max; p.k_min = s.k_min; p.v_norm_max = s.v_norm_max;
+  if (g.reserved & IA_GEOM_DIAG_ELL) {  // the diagonal-ellipsoid bound: w takes the place of k_max, k_min is not read
+    p.k_max = s.w;
+    p.k_min = s.w;
+    p.rho = s.rho;
+  }
   p.prefix_lens = prefix_lens;
   p.n_kv_heads = g.n_kv_heads; p.max_blocks = g.max_blocks; p.block_size = g.block_size;
   p.mode = mode & 0xff; p.mass_exp = (mode & IA_SELECT_TERM1_MASS_EXP) != 0;

@@ -402,6 +402,13 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
     if (p.px.n_ranks > 0) {
       exchange_store(p, xv, orow * D + d, ov);
       if (d == 0) exchange_store(p, xv, p.px.lse_offset + orow, lv);
+    } else if (p.final_out != nullptr && p.n_splits == 1) {
+      // the pair's only part, inside the one-call step: this is the output row - same value, same
+      // rounding as the merge of a single part (weight e^0 = 1, denominator 1), without the round
+      // trip of the partial through global memory
+      const int64_t at = ((int64_t)seq * rows + head * G + g) * D + d;
+      if (p.final_dtype == IA_BF16) static_cast<bf16*>(p.final_out)[at] = __float2bfloat16_rn(ov);
+      else static_cast<float*>(p.final_out)[at] = ov;
     } else {
       p.o_partial[orow * D + d] = ov;
       if (d == 0) p.lse_partial[orow] = lv;
@@ -412,7 +419,7 @@ condition_block_finalize_attention_kernel(DecodeParams p) {
     exchange_publish(p, xv);
     return;
   }
-  finish_pair<D>(p, seq, head, G, scratch);
+  if (p.n_splits > 1) finish_pair<D>(p, seq, head, G, scratch);
   IA_DTRACE(7);
 }
 

@@ -4,6 +4,8 @@
 // (llama/script/analysis/condition_block_gen/methods/condition_block_triton_impl/core.py:449-500):
 // per (kv head, block) the fp32 mean of K and of V over the block's valid
 // tokens, the per-coordinate max / min of K, and the largest token |v|_2.
+// Optionally also the diagonal-ellipsoid pair (w, rho) of the reference's
+// condition_block_ball study (a second walk over the block's keys).
 // The reference runs this as a chain of PyTorch ops over a padded
 // [Hkv, nb, B, D] view; here one warp owns one (sequence, kv head, block),
 // walks the block's physical pages through the block table and keeps every
@@ -85,6 +87,41 @@ condition_block_build_summaries_kernel(const T* __restrict__ k_pool, const T* __
   store_vec<VEC>(reinterpret_cast<T*>(out.k_max) + row, kmax);
   store_vec<VEC>(reinterpret_cast<T*>(out.k_min) + row, kmin);
   if (lane == 0) out.v_norm_max[unit] = sqrtf(vn2max);
+  if (out.w == nullptr || out.rho == nullptr) return;
+
+  // Diagonal-ellipsoid pair (condition_block_ball/gen_selection.py:53-73): w from the stored mean and
+  // the range, rounded up before a bf16 cast; rho = max_t |(k_t - k_bar) / w| from the stored w, which
+  // needs the finished mean and therefore a second walk over the block's keys (they are in L2 now).
+  float kc[VEC], inv_w2[VEC], wv[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    kc[i] = kb[i];
+    if (g.reserved & IA_GEOM_KBAR_BF16) kc[i] = __bfloat162float(__float2bfloat16_rn(kb[i]));  // the stored mean
+    float wi = fmaxf(fmaxf(kmax[i] - kc[i], kc[i] - kmin[i]), 1e-6f);
+    if (sizeof(T) == 2) wi = __bfloat162float(__float2bfloat16_rn(wi * (1.f + 0.0078125f)));
+    wv[i] = wi;
+    inv_w2[i] = 1.f / (wi * wi);
+  }
+  store_vec<VEC>(reinterpret_cast<T*>(out.w) + row, wv);
+  float d2max = 0.f;
+  for (int p = 0; p < n_pages; ++p) {
+    const int page = table[first / g.page_size + p];
+    const int64_t base = (int64_t)page * g.pool_page_stride + head_off;
+    const int rows = min(g.page_size, count - p * g.page_size);
+#pragma unroll 4
+    for (int t = 0; t < rows; ++t) {
+      float kv[VEC];
+      load_vec<VEC>(k_pool + base + (int64_t)t * D, kv);
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float c = kv[i] - kc[i];
+        sq = fmaf(c * c, inv_w2[i], sq);
+      }
+      d2max = fmaxf(d2max, warp_sum(sq));
+    }
+  }
+  if (lane == 0) out.rho[unit] = sqrtf(d2max);
 }
 
 template <typename T, int D>

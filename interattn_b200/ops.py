@@ -45,9 +45,17 @@ def _need_cuda(*tensors: torch.Tensor) -> None:
             raise ValueError("interattn_b200 operators take CUDA tensors only (there is no CPU path)")
 
 
-def _geom_flags(summ) -> int:
-    """Geometry flags implied by how the summaries are stored (bf16 k_bar: IA_GEOM_KBAR_BF16)."""
-    return _lib.IA_GEOM_KBAR_BF16 if summ is not None and summ.k_bar.dtype == torch.bfloat16 else 0
+def _geom_flags(summ, bound: str = "range") -> int:
+    """Geometry flags: how the summaries are stored (bf16 k_bar: IA_GEOM_KBAR_BF16) and which bound
+    the selection uses (``bound="diag_ell"``: IA_GEOM_DIAG_ELL, needs summaries built with w and rho)."""
+    if bound not in ("range", "diag_ell"):
+        raise ValueError("bound must be 'range' or 'diag_ell'")
+    flags = _lib.IA_GEOM_KBAR_BF16 if summ is not None and summ.k_bar.dtype == torch.bfloat16 else 0
+    if bound == "diag_ell":
+        if summ is None or summ.w is None or summ.rho is None:
+            raise ValueError("the diag_ell bound needs summaries built with diag_ell=True (w and rho)")
+        flags |= _lib.IA_GEOM_DIAG_ELL
+    return flags
 
 
 @dataclass
@@ -95,11 +103,12 @@ class PagedKV:
     def head_dim(self) -> int:
         return int(self.k_pool.shape[3])
 
-    def geom(self, group_size: int, block_size: int, max_blocks: int, summ: Optional["BlockSummaries"] = None) -> Geom:
+    def geom(self, group_size: int, block_size: int, max_blocks: int, summ: Optional["BlockSummaries"] = None,
+             bound: str = "range") -> Geom:
         return Geom(
             batch=self.batch, n_kv_heads=self.n_kv_heads, group_size=int(group_size), head_dim=self.head_dim,
             page_size=self.page_size, block_size=int(block_size), max_pages=int(self.block_table.shape[1]),
-            max_blocks=int(max_blocks), dtype=_DTYPES[self.k_pool.dtype], reserved=_geom_flags(summ),
+            max_blocks=int(max_blocks), dtype=_DTYPES[self.k_pool.dtype], reserved=_geom_flags(summ, bound),
             n_pool_pages=int(self.k_pool.shape[0] if self.n_pool_pages is None else self.n_pool_pages), reserved2=0,
             pool_page_stride=int(self.k_pool.stride(0)), pool_head_stride=int(self.k_pool.stride(1)))
 
@@ -115,6 +124,9 @@ class BlockSummaries:
     v_bar: torch.Tensor
     v_norm_max: torch.Tensor  # [B, Hkv, nb] f32
     block_size: int
+    # optional diagonal-ellipsoid pair (the reference's condition_block_ball "diag_ell" bound):
+    w: Optional[torch.Tensor] = None     # [B, Hkv, nb, D] KV dtype, max_t |k_t - k_bar| (rounded up in bf16)
+    rho: Optional[torch.Tensor] = None   # [B, Hkv, nb] f32, max_t |(k_t - k_bar) / w|
 
     @property
     def max_blocks(self) -> int:
@@ -122,11 +134,13 @@ class BlockSummaries:
 
     def c_struct(self) -> Summaries:
         return Summaries(self.k_bar.data_ptr(), self.k_max.data_ptr(), self.k_min.data_ptr(),
-                         self.v_bar.data_ptr(), self.v_norm_max.data_ptr())
+                         self.v_bar.data_ptr(), self.v_norm_max.data_ptr(),
+                         None if self.w is None else self.w.data_ptr(),
+                         None if self.rho is None else self.rho.data_ptr())
 
     @staticmethod
     def empty(batch: int, n_kv_heads: int, max_blocks: int, head_dim: int, dtype: torch.dtype, device,
-              block_size: int, k_bar_dtype: torch.dtype = torch.float32) -> "BlockSummaries":
+              block_size: int, k_bar_dtype: torch.dtype = torch.float32, diag_ell: bool = False) -> "BlockSummaries":
         shape = (batch, n_kv_heads, max_blocks, head_dim)
         if k_bar_dtype not in (torch.float32, torch.bfloat16) or (k_bar_dtype != torch.float32 and dtype != torch.bfloat16):
             raise ValueError("k_bar is float32, or bfloat16 next to bfloat16 pools")
@@ -136,14 +150,19 @@ class BlockSummaries:
             k_min=torch.zeros(shape, device=device, dtype=dtype),
             v_bar=torch.zeros(shape, device=device, dtype=dtype),
             v_norm_max=torch.zeros(shape[:3], device=device, dtype=torch.float32),
-            block_size=int(block_size))
+            block_size=int(block_size),
+            w=torch.zeros(shape, device=device, dtype=dtype) if diag_ell else None,
+            rho=torch.zeros(shape[:3], device=device, dtype=torch.float32) if diag_ell else None)
 
 
 def build_summaries(kv: PagedKV, block_size: int, max_blocks: Optional[int] = None,
                     out: Optional[BlockSummaries] = None,
                     first_blocks: Optional[torch.Tensor] = None,
-                    k_bar_dtype: torch.dtype = torch.float32) -> BlockSummaries:
+                    k_bar_dtype: torch.dtype = torch.float32, diag_ell: bool = False) -> BlockSummaries:
     """Block summaries of every sequence's prefix (reference: ``_build_prompt_blocks``).
+    ``diag_ell=True`` also keeps the diagonal-ellipsoid pair ``w, rho`` (the reference's
+    ``condition_block_ball`` bound; ``select_blocks(..., bound="diag_ell")`` then reads two vectors and a
+    scalar per block instead of three vectors).
 
     ``first_blocks`` (int32 [B], device; needs ``out``) makes it an incremental
     update: only blocks ``b >= first_blocks[seq]`` are recomputed - used when
@@ -166,7 +185,7 @@ def build_summaries(kv: PagedKV, block_size: int, max_blocks: Optional[int] = No
             1, (int(kv.block_table.shape[1]) * kv.page_size + block_size - 1) // block_size)
     if out is None:
         out = BlockSummaries.empty(kv.batch, kv.n_kv_heads, max_blocks, kv.head_dim, kv.k_pool.dtype,
-                                   kv.k_pool.device, block_size, k_bar_dtype)
+                                   kv.k_pool.device, block_size, k_bar_dtype, diag_ell)
     g = kv.geom(1, block_size, max_blocks, out)
     s = out.c_struct()
     check(lib.ia_build_summaries(_ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),
@@ -186,9 +205,13 @@ def select_blocks(
     q: torch.Tensor, summ: BlockSummaries, prefix_lens: torch.Tensor, *,
     top_k: Optional[int] = None, eps: Optional[float] = None, max_sel: Optional[int] = None,
     want: Sequence[str] = (), out_idx: Optional[torch.Tensor] = None, out_count: Optional[torch.Tensor] = None,
-    aux_buffers: Optional[Dict[str, torch.Tensor]] = None, term1_mass_exp: bool = False,
+    aux_buffers: Optional[Dict[str, torch.Tensor]] = None, term1_mass_exp: bool = False, bound: str = "range",
 ) -> Tuple[torch.Tensor, torch.Tensor, Dict[str, torch.Tensor]]:
     """Score every block and route.
+
+    ``bound="diag_ell"`` bounds the in-block spread of the logits with the diagonal-ellipsoid pair
+    ``(w, rho)`` of the summaries instead of the coordinate range ``(k_max, k_min)`` (the reference's
+    ``condition_block_ball`` variant, ``gen_selection.py:82-87``).
 
     ``term1_mass_exp`` switches the first term of the score to ``2 b_all softmax(z + delta)``
     (the reference's variant of the same name, ``core.py:798-803``).
@@ -229,7 +252,7 @@ def select_blocks(
         aux[name] = buf
     c_aux = SelectAux(*[aux[n].data_ptr() if n in aux else None for n in ("score", "z", "s", "delta", "globals")])
     g = Geom(batch=b, n_kv_heads=hkv, group_size=group, head_dim=d, page_size=16, block_size=summ.block_size,
-             max_pages=1, max_blocks=nb, dtype=_DTYPES[q.dtype], reserved=_geom_flags(summ),
+             max_pages=1, max_blocks=nb, dtype=_DTYPES[q.dtype], reserved=_geom_flags(summ, bound),
              pool_page_stride=16 * d, pool_head_stride=16 * d)
     s = summ.c_struct()
     check(lib.ia_select(_ptr(q), ctypes.byref(s), _ptr(prefix_lens), ctypes.byref(g), mode,
@@ -331,7 +354,7 @@ class DecodeAttention:
     def __init__(self, kv: PagedKV, summ: BlockSummaries, n_q_heads: int, *, top_k: Optional[int] = None,
                  eps: Optional[float] = None, rep_mode: str = "sparse_only", n_splits: Optional[int] = None,
                  max_sel: Optional[int] = None, expected_blocks: Optional[int] = None,
-                 term1_mass_exp: bool = False):
+                 term1_mass_exp: bool = False, bound: str = "range"):
         self.lib = _lib.load()
         if (top_k is None) == (eps is None):
             raise ValueError("give exactly one of top_k and eps")
@@ -347,7 +370,7 @@ class DecodeAttention:
         self.top_k, self.eps = int(top_k or 0), float(eps or 0.0)
         nb = summ.max_blocks
         self.max_sel = int(max_sel) if max_sel is not None else (max(self.top_k, 1) if top_k is not None else nb)
-        self.geom = kv.geom(self.group, summ.block_size, nb, summ)
+        self.geom = kv.geom(self.group, summ.block_size, nb, summ, bound)
         if n_splits is None:   # wave-aware choice for this device
             expect = expected_blocks or (min(self.top_k, nb) if top_k is not None else max(1, nb // 16))
             n_splits = self.lib.ia_suggest_splits(ctypes.byref(self.geom), int(max(1, expect)))

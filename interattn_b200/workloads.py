@@ -92,3 +92,29 @@ def scaled(cfg: DecodeConfig, *, batch: Optional[int] = None, max_len: int = 204
         cfg, name=cfg.name + "_small", batch=b, prefix_lens=tuple(lens),
         suffix_lens=(suffix,) * b, top_k=max(1, min(k, max(1, nb_min // 2))),
     )
+
+
+def make_device_layer(cfg: DecodeConfig, device, seed: int):
+    """One layer's paged KV cache for the whole batch of ``cfg``, generated on the device: N(0,1) K/V
+    (K channels scaled by a log-normal factor where the configuration asks for it), a random
+    permutation as the block table.  Returns an ``ops.PagedKV``."""
+    from . import ops
+    g = torch.Generator(device=device).manual_seed(seed)
+    P, D, hkv = cfg.page_size, cfg.head_dim, cfg.n_kv_heads
+    pages_per_seq = [(n + s + P - 1) // P for n, s in zip(cfg.prefix_lens, cfg.suffix_lens)]
+    n_pages, max_pages = sum(pages_per_seq), max(pages_per_seq)
+    dt = cfg.torch_dtype
+    k_pool = torch.randn((n_pages, hkv, P, D), generator=g, device=device, dtype=torch.float32)
+    if cfg.k_channel_sigma > 0:
+        k_pool *= torch.exp(cfg.k_channel_sigma * torch.randn((D,), generator=g, device=device))
+    k_pool = k_pool.to(dt)
+    v_pool = torch.randn((n_pages, hkv, P, D), generator=g, device=device, dtype=torch.float32).to(dt)
+    perm = torch.randperm(n_pages, generator=g, device=device).to(torch.int32)
+    table = torch.zeros((cfg.batch, max_pages), dtype=torch.int32, device=device)
+    at = 0
+    for b, n in enumerate(pages_per_seq):
+        table[b, :n] = perm[at: at + n]
+        at += n
+    prefix = torch.tensor(cfg.prefix_lens, dtype=torch.int32, device=device)
+    seq = torch.tensor([p + s for p, s in zip(cfg.prefix_lens, cfg.suffix_lens)], dtype=torch.int32, device=device)
+    return ops.PagedKV(k_pool, v_pool, table, prefix, seq)

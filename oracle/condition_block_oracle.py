@@ -15,6 +15,9 @@ condition_block_gen``):
 * ``condition_terms``      - IMPL/core.py:509-546, stopping before the
                              ``> eps`` comparison
 * ``score_from_stats``     - condition_block_ppl/runner_cond_block.py:279-294
+* ``diag_ell_stats`` / ``condition_terms(bound="diag_ell")`` - the diagonal-
+                             ellipsoid bound of condition_block_ball/gen_selection.py:
+                             21-87 (w, rho per block; delta = rho |q * w| / sqrt(D))
 * ``select_threshold``     - IMPL/core.py:546 (the reference's epsilon rule)
 * ``select_topk``          - no reference counterpart for blocks; the ranking
                              precedent is GEN/methods/quest.py:91-103 (GQA-mean
@@ -177,29 +180,58 @@ def score_from_stats(p: torch.Tensor, delta: torch.Tensor, b_c: torch.Tensor, b_
     return p * (first + second)
 
 
-def condition_terms(q_grouped: torch.Tensor, summ: Summaries, term1_mass_exp: bool = False) -> Dict[str, torch.Tensor]:
+def diag_ell_stats(k_all: torch.Tensor, summ: Summaries, w_dtype: Optional[torch.dtype] = None):
+    """The diagonal-ellipsoid summaries of condition_block_ball/gen_selection.py:21-73:
+    ``w = max(k_max - k_bar, k_bar - k_min)`` clamped at 1e-6 (one vector per block), optionally stored
+    in bf16 after a round-up bump of ``1 + 2^-7`` (their CONDITION_BLOCK_BALL_W_DTYPE option), and
+    ``rho = max_t |(k_t - k_bar) / w|`` computed with the stored w - in the reference's expanded form
+    ``|k|^2_w - 2 k . k_bar_w + |k_bar|^2_w``.  k_all [Hkv, L, D] is the summarised prefix.
+    Returns (w [Hkv, nb, D], rho [Hkv, nb] fp32)."""
+    k_bar = summ.k_bar.float()
+    w = torch.maximum(summ.k_max.float() - k_bar, k_bar - summ.k_min.float()).clamp_min(1e-6)
+    if w_dtype == torch.bfloat16:
+        w = (w * (1.0 + 2.0 ** -7)).to(torch.bfloat16)
+    inv_w2 = w.float().pow(-2)
+    kb, nb = _blocked(k_all.float(), summ.block_size)                  # [Hkv, nb, B, D]
+    live = torch.arange(summ.block_size).view(1, -1) < summ.counts.view(-1, 1)
+    k_norm2 = torch.einsum("hbtd,hbd->hbt", kb.pow(2), inv_w2)
+    dot = torch.einsum("hbtd,hbd->hbt", kb, k_bar * inv_w2)
+    offset = (k_bar.pow(2) * inv_w2).sum(dim=-1)
+    dist2 = (k_norm2 - 2.0 * dot + offset.unsqueeze(-1)).masked_fill(~live.unsqueeze(0), float("-inf"))
+    return w, dist2.amax(dim=-1).clamp_min(0.0).sqrt()
+
+
+def condition_terms(q_grouped: torch.Tensor, summ: Summaries, term1_mass_exp: bool = False,
+                    diag_ell=None) -> Dict[str, torch.Tensor]:
     """q_grouped [Hkv, G, D] -> per-row and per-head quantities of the score.
 
     Returns ``s`` (q.k_bar/sqrt(D)), ``delta`` (range bound), ``z`` (s + log
     count, -inf for empty blocks), ``cond`` [Hkv, G, nb] and ``score`` =
     mean over the G query rows of a kv head, [Hkv, nb].
+    ``diag_ell=(w, rho)``: the bound is ``rho |q * w| / sqrt(D)`` (condition_block_ball/
+    gen_selection.py:82-87) instead of the coordinate-range bound; everything else is the same.
     """
     q = q_grouped.float()
     hkv, g, d = q.shape
     root = d ** 0.5
     exists = (summ.counts > 0).view(1, 1, -1)
     k_bar = summ.k_bar.to(q.dtype)
-    k_hi = summ.k_max.to(q.dtype)
-    k_lo = summ.k_min.to(q.dtype)
 
     q4 = q.view(hkv, g, 1, d)
     s = (torch.einsum("gsqd,gbd->gsqb", q4, k_bar) / root)[:, :, 0]
-    qb = q4[:, :, :, None, :]
-    hi_prod = qb * k_hi[:, None, None]
-    lo_prod = qb * k_lo[:, None, None]
-    upper = (torch.maximum(hi_prod, lo_prod).sum(dim=-1) / root)[:, :, 0]
-    lower = (torch.minimum(hi_prod, lo_prod).sum(dim=-1) / root)[:, :, 0]
-    delta = torch.maximum((upper - s).abs(), (lower - s).abs()).masked_fill(~exists, 0.0)
+    if diag_ell is not None:
+        w, rho = diag_ell
+        qw = torch.sqrt(torch.einsum("gsqd,gbd->gsqb", q4.pow(2), w.float().pow(2)).clamp_min(0.0))[:, :, 0]
+        delta = (rho.float()[:, None, :] * qw / root).masked_fill(~exists, 0.0)
+    else:
+        k_hi = summ.k_max.to(q.dtype)
+        k_lo = summ.k_min.to(q.dtype)
+        qb = q4[:, :, :, None, :]
+        hi_prod = qb * k_hi[:, None, None]
+        lo_prod = qb * k_lo[:, None, None]
+        upper = (torch.maximum(hi_prod, lo_prod).sum(dim=-1) / root)[:, :, 0]
+        lower = (torch.minimum(hi_prod, lo_prod).sum(dim=-1) / root)[:, :, 0]
+        delta = torch.maximum((upper - s).abs(), (lower - s).abs()).masked_fill(~exists, 0.0)
 
     b_c = summ.v_norm_max.float()[:, None, :].expand(hkv, g, -1).masked_fill(~exists, 0.0)
     b_all = b_c.amax(dim=-1)

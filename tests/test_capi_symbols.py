@@ -50,7 +50,7 @@ def test_geometry_struct_layout_matches_the_header():
     assert ctypes.sizeof(_lib.Geom) == 12 * 4 + 2 * 8
     assert _lib.Geom.n_pool_pages.offset == 40
     assert _lib.Geom.pool_page_stride.offset == 48
-    assert ctypes.sizeof(_lib.Summaries) == 5 * ctypes.sizeof(ctypes.c_void_p)
+    assert ctypes.sizeof(_lib.Summaries) == 7 * ctypes.sizeof(ctypes.c_void_p)  # k_bar k_max k_min v_bar v_norm_max w rho
     assert ctypes.sizeof(_lib.SelectAux) == 5 * ctypes.sizeof(ctypes.c_void_p)
 
 

@@ -1,0 +1,143 @@
+"""GPU parity of the diagonal-ellipsoid bound (the reference's condition_block_ball study,
+llama/script/analysis/condition_block_ball/gen_selection.py:21-87): the summary pair (w, rho) built
+on the device against the oracle's restatement, and the selection that bounds the in-block logit
+spread with rho |q * w| / sqrt(D) against the oracle on the same stored (w, rho).
+
+Bars: w bit-exact (a subtraction, a maximum and one rounding of the same stored inputs); rho within
+1e-3 relative of the oracle (which follows the reference's expanded quadratic form in fp32) on blocks of
+more than one token and within 1e-5 of the float64 definition (the kernel uses the direct form); selected block indices identical.
+"""
+
+import pytest
+import torch
+
+from oracle import condition_block_oracle as orc
+from oracle.configs import CONFIGS, DecodeConfig, make_case, scaled
+from tests.gpu_util import logical_kv, max_blocks_of, oracle_summaries_from_gpu, rank_gap, to_device
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from interattn_b200 import ops
+    return ops
+
+
+CASES = [
+    CONFIGS["cfg1_cpu_fp32"],
+    scaled(CONFIGS["cfg2_llama8b_32k"], batch=3, max_len=2304, suffix=0),
+    scaled(CONFIGS["cfg2_llama8b_32k"], batch=2, max_len=1500, suffix=33),
+    scaled(CONFIGS["cfg5_llama70b_ragged"], batch=5, max_len=1900, suffix=3),
+    DecodeConfig("f32_d128", "float32", 2, 4, 2, 128, 16, 64, 3, (700, 129), (2, 0), seed=5),
+    DecodeConfig("bf16_d64", "bfloat16", 2, 8, 2, 64, 16, 64, 3, (777, 65), (0, 18), seed=6),
+    DecodeConfig("bf16_g16", "bfloat16", 1, 16, 1, 128, 16, 64, 5, (1111,), (4,), seed=7),
+    DecodeConfig("bf16_g1", "bfloat16", 2, 2, 2, 128, 16, 64, 2, (300, 64), (0, 0), seed=8),
+]
+
+
+@pytest.fixture(scope="module", params=CASES, ids=lambda c: c.name)
+def bundle(request):
+    ops = _ops()
+    cfg = request.param
+    case = make_case(cfg, spare_pages=3)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case), diag_ell=True)
+    torch.cuda.synchronize()
+    return cfg, case, q, kv, summ
+
+
+def test_w_and_rho(bundle):
+    ops = _ops()
+    cfg, case, q, kv, summ = bundle
+    plain = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
+    for name in ("k_bar", "k_max", "k_min", "v_bar", "v_norm_max"):  # the pair is an addition, nothing else moves
+        assert torch.equal(getattr(plain, name), getattr(summ, name)), name
+    w_dtype = torch.bfloat16 if cfg.dtype == "bfloat16" else None
+    for b in range(cfg.batch):
+        plen = int(case["prefix_lens"][b])
+        k, _ = logical_kv(case, b)
+        osum = oracle_summaries_from_gpu(summ, b, plen)
+        nb = osum.n_blocks
+        w, rho = orc.diag_ell_stats(k[:, :plen], osum, w_dtype)
+        assert torch.equal(summ.w[b, :, :nb].cpu().float(), w.float()), "w"
+        got = summ.rho[b, :, :nb].cpu()
+        many = osum.counts > 1
+        # the oracle follows the reference's expanded form |k|^2 - 2 k.k_bar + |k_bar|^2 (all over w^2) in fp32,
+        # which cancels ~3 digits on short blocks (small w, terms of 1e4); the kernel uses the direct form
+        assert torch.allclose(got[:, many], rho[:, many], rtol=1e-3, atol=1e-5), "rho"
+        # the definition itself, in float64: no key of the block lies outside the ellipsoid
+        kb, _ = orc._blocked(k[:, :plen].double(), cfg.block_size)
+        live = torch.arange(cfg.block_size).view(1, -1) < osum.counts.view(-1, 1)
+        dist = ((kb - osum.k_bar.double().unsqueeze(2)) / w.double().unsqueeze(2)).pow(2).sum(-1).sqrt()
+        dist = dist.masked_fill(~live.unsqueeze(0), 0.0).amax(-1)
+        assert torch.allclose(got.double(), dist, rtol=1e-5, atol=1e-6)
+        assert (got[:, ~many] == 0).all(), "a one-token block is its own mean"
+
+
+def test_diag_ell_selection(bundle):
+    ops = _ops()
+    cfg, case, q, kv, summ = bundle
+    idx, cnt, aux = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, want=("score", "z", "delta"),
+                                      bound="diag_ell")
+    ridx, rcnt, raux = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, want=("score", "delta"))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    idx, cnt = idx.cpu(), cnt.cpu()
+    for b in range(cfg.batch):
+        plen = int(case["prefix_lens"][b])
+        osum = oracle_summaries_from_gpu(summ, b, plen)
+        nb = osum.n_blocks
+        stored = (summ.w[b, :, :nb].cpu(), summ.rho[b, :, :nb].cpu())
+        qg = case["q"][b].reshape(cfg.n_kv_heads, cfg.group_size, cfg.head_dim).float()
+        terms = orc.condition_terms(qg, osum, diag_ell=stored)
+        ranked, _ = orc.select_topk(terms["score"], osum.counts, cfg.top_k)
+        shape = (cfg.n_kv_heads, cfg.group_size, nb)
+        assert torch.allclose(aux["delta"][b, :, :nb].cpu().reshape(shape), terms["delta"], rtol=1e-4, atol=1e-6)
+        assert torch.allclose(aux["z"][b, :, :nb].cpu().reshape(shape), terms["z"], rtol=1e-5, atol=1e-5)
+        assert torch.allclose(aux["score"][b, :, :nb].cpu(), terms["score"], rtol=2e-4, atol=1e-8)
+        for h in range(cfg.n_kv_heads):
+            n = int(cnt[b, h])
+            got = idx[b, h, :n].tolist()
+            assert got == sorted(ranked[h]), (
+                f"seq {b} head {h}: relative score gap at the cut {rank_gap(terms['score'][h], n):.3e}")
+            assert (idx[b, h, n:] == -1).all()
+    # the ellipsoid contains the block's keys and sits inside the coordinate box scaled by rho <= sqrt(D);
+    # the two bounds differ, so the deltas must
+    assert not torch.allclose(aux["delta"], raux["delta"])
+
+
+def test_diag_ell_step_uses_the_same_selection(bundle):
+    """The one-call layer step with bound="diag_ell": the same indices as the stand-alone selection and the
+    attention of exactly those blocks."""
+    ops = _ops()
+    cfg, case, q, kv, summ = bundle
+    idx, cnt, _ = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, bound="diag_ell")
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, bound="diag_ell")
+    out = step.step(q).float().cpu()
+    torch.cuda.synchronize()
+    assert torch.equal(step.sel_idx[:, :, :idx.shape[2]], idx)
+    assert torch.equal(step.sel_count, cnt)
+    assert ops.device_status() == 0
+    tol = dict(rtol=1e-5, atol=1e-5) if cfg.dtype == "float32" else dict(rtol=1e-2, atol=2e-2)
+    idx, cnt = idx.cpu(), cnt.cpu()
+    for b in range(cfg.batch):
+        plen = int(case["prefix_lens"][b])
+        k, v = logical_kv(case, b)
+        osum = oracle_summaries_from_gpu(summ, b, plen)
+        mask = torch.zeros((cfg.n_kv_heads, osum.n_blocks), dtype=torch.bool)
+        for h in range(cfg.n_kv_heads):
+            mask[h, idx[b, h, :int(cnt[b, h])].long()] = True
+        qg = case["q"][b].reshape(cfg.n_kv_heads, cfg.group_size, cfg.head_dim).float()
+        want = orc.decode_attention(qg, k, v, plen, cfg.block_size, mask, rep_mode="sparse_only")
+        got = out[b].reshape(cfg.n_kv_heads, cfg.group_size, cfg.head_dim)
+        torch.testing.assert_close(got, want, **tol)
+
+
+def test_diag_ell_needs_the_pair():
+    ops = _ops()
+    cfg = CASES[1]
+    case = make_case(cfg, spare_pages=1)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
+    with pytest.raises(ValueError):
+        ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, bound="diag_ell")

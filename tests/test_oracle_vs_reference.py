@@ -215,3 +215,40 @@ def test_step_statistics_match_reference(ref):
                                  prompt_len=prompt_len, suffix_len=suffix_len)
     got = orc.condition_stats(mask, counts, g, prompt_len, suffix_len)
     assert {k: int(v) for k, v in want.items()} == got
+
+
+@pytest.mark.parametrize("w_dtype", [None, torch.bfloat16])
+def test_diag_ell_bound_matches_reference(ref, monkeypatch, w_dtype):
+    """oracle.diag_ell_stats / condition_terms(diag_ell=...) against condition_block_ball/gen_selection.py
+    (w, rho, the delta it gives, and the epsilon masks) on a ragged bf16 prefix."""
+    _, core, _ = ref
+    sys.path.insert(0, REF_ROOT)
+    try:
+        from llama.script.analysis.condition_block_ball import gen_selection as ball
+    finally:
+        sys.path.remove(REF_ROOT)
+    if w_dtype == torch.bfloat16:
+        monkeypatch.setenv("CONDITION_BLOCK_BALL_W_DTYPE", "bfloat16")
+    else:
+        monkeypatch.delenv("CONDITION_BLOCK_BALL_W_DTYPE", raising=False)
+    cfg = scaled(CONFIGS["cfg2_llama8b_32k"], batch=2, max_len=1100, suffix=0)
+    case = make_case(cfg)
+    g = cfg.group_size
+    for b in range(cfg.batch):
+        plen = int(case["prefix_lens"][b])
+        k, v = _logical(case, b)
+        theirs = core._build_prompt_blocks(k[:, :plen], v[:, :plen], cfg.block_size)
+        summ = orc.block_summaries(k[:, :plen], v[:, :plen], cfg.block_size)
+        w, rho = orc.diag_ell_stats(k[:, :plen], summ, w_dtype)
+        w_ref, rho_ref = ball.diag_ell_stats(theirs)
+        assert torch.equal(w.float(), w_ref.float())
+        assert torch.allclose(rho, rho_ref, rtol=1e-5, atol=1e-6)
+        qg = case["q"][b].reshape(cfg.n_kv_heads, g, 1, cfg.head_dim).float()
+        terms = orc.condition_terms(qg[:, :, 0], summ, diag_ell=(w_ref, rho_ref))
+        delta_ref = ball._diag_ell_delta(qg, theirs, cfg.head_dim ** 0.5)[:, :, 0]
+        assert torch.allclose(terms["delta"], delta_ref, rtol=1e-6, atol=1e-7)
+        for quant in (0.25, 0.75):
+            eps = float(torch.quantile(terms["score"].flatten(), quant))
+            sel, z_logits, *_ = ball.select_prompt_blocks_diag_ell(qg, theirs, eps)
+            assert torch.equal(sel[:, 0, 0], orc.select_threshold(terms["score"], summ.counts, eps))
+            assert torch.equal(z_logits[:, :, 0], terms["z"])
