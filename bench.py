@@ -321,6 +321,32 @@ def kernel_times(torch, steppers, qs, K, repeats):
     return sel, att
 
 
+def kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode="sparse_only"):
+    """(kernel_us, roofline, roofline_select) of a layer step.  Two kernels: the attention kernel is the
+    dominant one and the selection kernel has its own record.  One fused kernel
+    (condition_block_select_attend_kernel): it reads the summaries and the picked pages in one launch, so its
+    algorithmic bytes are the sum and its time is the span between the events around it."""
+    peak, src = hbm_peak()
+    if fused:
+        us = sel_us + att_us  # events 0 -> 2; nothing runs between 1 and 2
+        gbs = (kv_bytes + sel_bytes) / (us * 1e-6) / 1e9
+        kernel_us = {"select_attend": us, "select": 0.0, "sparse_decode": 0.0, "finalize": 0.0}
+        roof = {"bound": "hbm", "kernel": "condition_block_select_attend_kernel", "achieved": gbs, "peak": peak,
+                "peak_source": src, "unit": "GB/s", "frac": gbs / peak,
+                "traffic": committed_traffic(workload, "select_attend"), "bytes_per_launch": kv_bytes + sel_bytes}
+        return kernel_us, roof, None
+    att_gbs, sel_gbs = kv_bytes / (att_us * 1e-6) / 1e9, sel_bytes / (sel_us * 1e-6) / 1e9
+    suffix = "" if rep_mode == "sparse_only" else f"_{rep_mode}"
+    kernel_us = {"select": sel_us, "sparse_decode": att_us, "finalize": 0.0}
+    roof = {"bound": "hbm", "kernel": "condition_block_finalize_attention_kernel", "achieved": att_gbs, "peak": peak,
+            "peak_source": src, "unit": "GB/s", "frac": att_gbs / peak,
+            "traffic": committed_traffic(workload, "sparse_decode" + suffix), "bytes_per_launch": kv_bytes}
+    roof_sel = {"bound": "hbm", "kernel": "condition_block_select_kernel", "achieved": sel_gbs, "peak": peak,
+                "unit": "GB/s", "frac": sel_gbs / peak, "bytes_per_launch": sel_bytes,
+                "traffic": committed_traffic(workload, "select")}
+    return kernel_us, roof, roof_sel
+
+
 def variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summaries, n_splits, K, R, workload,
                    bound="range"):
     """One sub-record: the layer-step in another mode / summary layout, with its own roofline."""
@@ -333,18 +359,18 @@ def variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summari
         steppers[i % n_pools].step(qs[i % n_pools])
     ms = regions.run(lambda i: steppers[i % n_pools].step(qs[i % n_pools]), K, R)
     sel_us, att_us = kernel_times(torch, steppers, qs, K, max(1, R // 5))
+    fused = ops.last_decode_fused()
     kv_bytes, sel_bytes = algorithmic_bytes(cfg, rep_mode, kbar_bf16, bound)
-    peak, src = hbm_peak()
-    att_gbs, sel_gbs = kv_bytes / (att_us * 1e-6) / 1e9, sel_bytes / (sel_us * 1e-6) / 1e9
-    return {
-        "us_per_layer": summarise(ms, K), "kernel_us": {"select": sel_us, "sparse_decode": att_us},
-        "config": {"rep_mode": rep_mode, "k_bar": "bf16" if kbar_bf16 else "f32", "bound": bound},
-        "roofline": {"bound": "hbm", "kernel": "condition_block_finalize_attention_kernel", "achieved": att_gbs,
-                     "peak": peak, "peak_source": src, "unit": "GB/s", "frac": att_gbs / peak,
-                     "bytes_per_launch": kv_bytes, "traffic": committed_traffic(workload, f"sparse_decode_{rep_mode}")},
-        "roofline_select": {"bound": "hbm", "kernel": "condition_block_select_kernel", "achieved": sel_gbs,
-                            "peak": peak, "unit": "GB/s", "frac": sel_gbs / peak, "bytes_per_launch": sel_bytes},
+    kernel_us, roof, roof_sel = kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode)
+    rec = {
+        "us_per_layer": summarise(ms, K), "kernel_us": kernel_us,
+        "config": {"rep_mode": rep_mode, "k_bar": "bf16" if kbar_bf16 else "f32", "bound": bound,
+                   "launches_per_step": 1 if fused else 2},
+        "roofline": roof,
     }
+    if roof_sel is not None:
+        rec["roofline_select"] = roof_sel
+    return rec
 
 
 def run_gpu_arm(args):
@@ -437,6 +463,7 @@ def layer_step_record(args, workload, torch, dist, regions, world, rank, local_r
     ms = regions.run(lambda i: steppers[i % n_pools].step(qs[i % n_pools]), K, R)
     # the same steps again with events between the kernels: per-kernel device times for the roofline
     sel_us, att_us = kernel_times(torch, steppers, qs, K, max(1, R // 5))
+    fused = ops.last_decode_fused()  # one launch per step (selection + attention in one kernel) or two
     status = ops.device_status()
 
     # end-to-end: host q in, host output back, every step
@@ -473,9 +500,7 @@ def layer_step_record(args, workload, torch, dist, regions, world, rank, local_r
 
     esz = 2 if cfg.dtype == "bfloat16" else 4
     kv_bytes, sel_bytes = algorithmic_bytes(cfg, args.rep_mode, args.kbar_bf16)
-    peak, peak_src = hbm_peak()
-    att_gbs = kv_bytes / (att_us * 1e-6) / 1e9
-    sel_gbs = sel_bytes / (sel_us * 1e-6) / 1e9
+    kernel_us, roof, roof_sel = kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, args.rep_mode)
     q_bytes = cfg.batch * rows * cfg.head_dim * esz
     line = {
         "metric": METRIC, "value": replicas * cfg.batch / (step_us["median"] * 1e-6), "unit": UNIT,
@@ -485,26 +510,23 @@ def layer_step_record(args, workload, torch, dist, regions, world, rank, local_r
         "config": {"workload": workload, "batch_per_gpu": cfg.batch, "n_q_heads": cfg.n_q_heads,
                    "n_kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim, "context": max(cfg.prefix_lens),
                    "page": cfg.page_size, "block": cfg.block_size, "top_k": cfg.top_k,
-                   "rep_mode": args.rep_mode, "n_splits": n_splits, "k_bar": "bf16" if args.kbar_bf16 else "f32",
+                   "rep_mode": args.rep_mode, "n_splits": 1 if fused else n_splits,
+                   "launches_per_step": 1 if fused else 2, "k_bar": "bf16" if args.kbar_bf16 else "f32",
                    "parallelism": (f"kv-head shard x{world}" if head_shard else f"batch-shard x{world}"),
                    "timing": f"median of {R} regions of {K} steps, each between synchronise + barrier, max over ranks",
                    "l2": f"{n_pools} layer pools rotated, {(kv_bytes + sel_bytes) >> 20} MiB read per step "
                          "(> 126 MB L2), no flush; cold_l2 = flushed before every step"},
         "us_per_layer": step_us["median"], "us_per_layer_stats": step_us,
-        "kernel_us": {"select": sel_us, "sparse_decode": att_us, "finalize": 0.0},
-        "roofline": {"bound": "hbm", "kernel": "condition_block_finalize_attention_kernel",
-                     "achieved": att_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                     "frac": att_gbs / peak, "traffic": committed_traffic(workload, "sparse_decode"),
-                     "bytes_per_launch": kv_bytes},
-        "roofline_select": {"bound": "hbm", "kernel": "condition_block_select_kernel", "achieved": sel_gbs,
-                            "peak": peak, "unit": "GB/s", "frac": sel_gbs / peak, "bytes_per_launch": sel_bytes,
-                            "traffic": committed_traffic(workload, "select")},
+        "kernel_us": kernel_us,
+        "roofline": roof,
+        "roofline_select": roof_sel,
         "e2e": {"value": replicas * cfg.batch / (e2e_us["median"] * 1e-6), "unit": UNIT,
                 "h2d_bytes_per_step": q_bytes, "d2h_bytes_per_step": q_bytes,
                 "us_per_layer": e2e_us["median"], "us_per_layer_stats": e2e_us,
                 "note": "KV pool and block summaries are cache state resident on the device; the step's "
                         "inputs (q) and outputs cross PCIe every step"},
-        "gpu_launches": 2 * K,   # selection + attention (finalize fused) per step, in each timed region
+        # per timed region: one fused selection-and-attention kernel per step, or selection + attention
+        "gpu_launches": (1 if fused else 2) * K,
         "clocks": clocks,
         "device_status": status,
     }

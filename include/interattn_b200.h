@@ -304,6 +304,12 @@ int ia_suggest_splits(const ia_geom* geom, int expected_blocks);
  * Every pair is cut into n_splits parts (ia_suggest_splits).  INTERATTN_B200_DECODE_GRID=flat in the
  * environment switches bf16 pools to a fixed grid of two CTAs per SM, each taking an equal share of
  * all pairs' pages whatever n_splits says (slower on B200 as measured; kept for comparison).
+ * One launch instead of two where it applies - IA_REP_SPARSE_ONLY, bf16 pools of 16-token pages with
+ * head_dim 128 and a known size (geom->n_pool_pages > 0), at most eight query rows per kv head, and a
+ * batch that gives every (sequence, kv head) one CTA of the selection kernel: that CTA then attends
+ * over the pages of the blocks it has just picked, which are still in its shared memory, and writes
+ * the output rows (condition_block_select_attend_kernel; n_splits is not used).
+ * INTERATTN_B200_FUSED=0 in the environment keeps the two launches.
  * workspace: ia_workspace_bytes() bytes, 256-byte aligned.  out [batch, rows, head_dim] in
  * geom->dtype, 16-byte aligned.  sel_idx/sel_count may be null (the selection then lives in the
  * workspace). */
@@ -313,6 +319,10 @@ int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool,
                         const ia_geom* geom, int mode, int top_k, float eps, int max_sel,
                         int rep_mode, int n_splits, void* workspace, int64_t workspace_bytes,
                         int32_t* sel_idx, int32_t* sel_count, void* out, ia_stream_t stream);
+
+/* 1 when the calling thread's last ia_decode_attention (any form) ran as the single fused launch, else 0.
+ * No reference counterpart: a reporting aid for benchmarks, which attribute time and bytes per kernel. */
+int ia_last_decode_fused(void);
 
 /* ia_decode_attention that also records four caller-created CUDA events
  * (cudaEvent_t, timing enabled) on the stream: events[0] before the selection

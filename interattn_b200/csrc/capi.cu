@@ -351,6 +351,8 @@ int ia_suggest_splits(const ia_geom* geom, int expected_blocks) {
   return best;
 }
 
+static thread_local int t_last_decode_fused = 0;
+
 static int decode_attention_impl(const void* q, const void* k_pool, const void* v_pool,
                                  const int32_t* block_table, const int32_t* prefix_lens,
                                  const int32_t* seq_lens, const ia_summaries* summaries, const ia_geom* geom,
@@ -374,6 +376,10 @@ static int decode_attention_impl(const void* q, const void* k_pool, const void* 
   int32_t* cnt = sel_count ? sel_count : w.sel_count;
   ia_select_aux aux{};
   if (rep_mode == IA_REP_HYBRID) aux.z = w.z;
+#ifdef IA_SELECT_TRACE
+  // profiling build: the selection kernel's time stamps go where IA_STEP_TRACE_PTR says (16 floats per CTA)
+  if (const char* at = getenv("IA_STEP_TRACE_PTR")) aux.delta = reinterpret_cast<float*>(strtoull(at, nullptr, 16));
+#endif
   // Argument checks of the public entry points, then two launches: the selection
   // kernel (which also clears the per-pair split counters) and the attention kernel
   // with the fused finalize - the CTA that finishes a (sequence, kv head) last merges
@@ -396,10 +402,20 @@ static int decode_attention_impl(const void* q, const void* k_pool, const void* 
     return fail(IA_ERR_BAD_ARG, "decode_attention: rep_mode %d", rep_mode);
   if (n_splits > 64) return fail(IA_ERR_BAD_ARG, "decode_attention: n_splits %d outside [1, 64]", n_splits);
   mark(0);
+  // Without representatives the selection kernel can go on to attend over what it picked - one launch;
+  // it says whether its launch shape allowed that (one CTA per (sequence, kv head), bf16, head_dim 128).
+  ia::SelectAttend attend{k_pool, v_pool, block_table, seq_lens, out, 0};
+  const bool may_fuse = rep_mode == IA_REP_SPARSE_ONLY;
   if (int s = launch_select(q, *summaries, prefix_lens, *geom, full_mode, top_k, eps, max_sel, idx, cnt, aux,
-                            w.split_counters, st))
+                            w.split_counters, st, nullptr, 0, 0, may_fuse ? &attend : nullptr))
     return s;
   mark(1);
+  t_last_decode_fused = attend.used;
+  if (attend.used) {
+    mark(2);
+    mark(3);
+    return IA_OK;
+  }
   FusedFinalize fused{out, geom->dtype, w.split_counters, w.flat_o, w.flat_lse};
   const int s = launch_sparse_decode(q, k_pool, v_pool, block_table, prefix_lens, seq_lens, idx, cnt, max_sel,
                                      summaries, w.z, *geom, rep_mode, n_splits, 0, geom->max_blocks, 1, w.o_partial,
@@ -418,6 +434,8 @@ int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool, c
                                eps, max_sel, rep_mode, n_splits, workspace, workspace_bytes, sel_idx, sel_count, out,
                                nullptr, stream);
 }
+
+int ia_last_decode_fused(void) { return t_last_decode_fused; }
 
 int ia_decode_attention_timed(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
                               const int32_t* prefix_lens, const int32_t* seq_lens, const ia_summaries* summaries,

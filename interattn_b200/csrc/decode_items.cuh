@@ -56,7 +56,8 @@ struct DecodeParams {
 
 // Profiling build (-DIA_DECODE_TRACE): thread 0 of every CTA leaves time stamps (microseconds since the
 // CTA started, from the nanosecond global timer) in a buffer whose address the environment variable
-// IA_TRACE_PTR gives - a timeline of the attention kernel's phases without a profiler.
+// IA_TRACE_PTR gives - a timeline of the attention kernel's phases without a profiler.  Slot 15 holds the
+// CTA's start (low 24 bits of the timer, ns), slot 14 the SM it ran on.
 #ifdef IA_DECODE_TRACE
 __device__ __forceinline__ unsigned long long decode_trace_now() {
   unsigned long long t;
@@ -65,7 +66,13 @@ __device__ __forceinline__ unsigned long long decode_trace_now() {
 }
 #define IA_DTRACE_BEGIN()                                                                           \
   const unsigned long long dtrace_t0 = decode_trace_now();                                           \
-  if (threadIdx.x == 0 && p.trace != nullptr) p.trace[(int64_t)blockIdx.x * 16 + 15] = (float)(dtrace_t0 & 0xffffffull)
+  if (threadIdx.x == 0 && p.trace != nullptr) {                                                      \
+    unsigned dtrace_sm;                                                                              \
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(dtrace_sm));                                           \
+    p.trace[(int64_t)blockIdx.x * 16 + 15] = (float)(dtrace_t0 & 0xffffffull);                       \
+    p.trace[(int64_t)blockIdx.x * 16 + 14] = (float)dtrace_sm;                                       \
+  }                                                                                                  \
+  do { } while (0)
 #define IA_DTRACE(i)                                                                                 \
   do {                                                                                               \
     if (threadIdx.x == 0 && p.trace != nullptr)                                                      \
@@ -325,25 +332,70 @@ __device__ __forceinline__ void finish_pair(const DecodeParams& p, int seq, int 
   } else {
     __syncthreads();
   }
-  for (int e = threadIdx.x; e < G * D; e += blockDim.x) {
-    const int g = e / D, d = e - g * D;
+  // Four output elements per thread; the parts' (lse, o) loads are independent of one another and are
+  // issued eight parts at a time, so the merge costs one or two L2 round trips, not one per part.
+  // The arithmetic (maximum over all parts first, then weights and sums in part order) is that of the
+  // stand-alone finalize kernel, value for value.
+  constexpr int kBatch = 8;
+  constexpr int VPR = D / 4;
+  const int n = p.n_splits;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int e = threadIdx.x; e < G * VPR; e += blockDim.x) {
+    const int g = e / VPR, d = (e - g * VPR) * 4;
     const int64_t row = (int64_t)seq * rows + head * G + g;
-    const float* lse = p.lse_partial + row * p.n_splits;
-    const float* o = p.o_partial + row * p.n_splits * D + d;
-    float top = -INFINITY;
-    for (int s = 0; s < p.n_splits; ++s) top = fmaxf(top, __ldcg(lse + s));
-    const float ref = top == -INFINITY ? 0.f : top;
-    float num = 0.f, den = 0.f;
-    for (int s = 0; s < p.n_splits; ++s) {
-      const float w = expf(__ldcg(lse + s) - ref);  // exp(-inf) = 0 for an empty part
-      num = fmaf(w, __ldcg(o + (int64_t)s * D), num);
-      den += w;
+    const float* lse = p.lse_partial + row * n;
+    const float* o = p.o_partial + row * n * D + d;
+    float l[kBatch];
+    float4 v[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      l[j] = j < n ? __ldcg(lse + j) : -INFINITY;
+      v[j] = j < n ? __ldcg(reinterpret_cast<const float4*>(o + (int64_t)j * D)) : zero4;
     }
-    const float v = num * (1.f / fmaxf(den, 1e-30f));  // same rounding as the stand-alone finalize kernel
-    if (p.final_dtype == IA_BF16)
-      static_cast<__nv_bfloat16*>(p.final_out)[row * D + d] = __float2bfloat16_rn(v);
-    else
-      static_cast<float*>(p.final_out)[row * D + d] = v;
+    float top = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) top = fmaxf(top, l[j]);
+    for (int s0 = kBatch; s0 < n; s0 += kBatch) {  // more than eight parts: the rest of the maximum
+      float more[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) more[j] = s0 + j < n ? __ldcg(lse + s0 + j) : -INFINITY;
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) top = fmaxf(top, more[j]);
+    }
+    const float ref = top == -INFINITY ? 0.f : top;
+    float4 num = zero4;
+    float den = 0.f;
+    for (int s0 = 0;;) {
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        if (s0 + j < n) {
+          const float w = expf(l[j] - ref);  // exp(-inf) = 0 for an empty part
+          num.x = fmaf(w, v[j].x, num.x); num.y = fmaf(w, v[j].y, num.y);
+          num.z = fmaf(w, v[j].z, num.z); num.w = fmaf(w, v[j].w, num.w);
+          den += w;
+        }
+      }
+      s0 += kBatch;
+      if (s0 >= n) break;
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        l[j] = s0 + j < n ? __ldcg(lse + s0 + j) : -INFINITY;
+        v[j] = s0 + j < n ? __ldcg(reinterpret_cast<const float4*>(o + (int64_t)(s0 + j) * D)) : zero4;
+      }
+    }
+    const float inv = 1.f / fmaxf(den, 1e-30f);  // same rounding as the stand-alone finalize kernel
+    const int64_t at = row * D + d;
+    if (p.final_dtype == IA_BF16) {
+      __nv_bfloat162 a = __floats2bfloat162_rn(num.x * inv, num.y * inv);
+      __nv_bfloat162 b = __floats2bfloat162_rn(num.z * inv, num.w * inv);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&a);
+      packed.y = *reinterpret_cast<uint32_t*>(&b);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.final_out) + at) = packed;
+    } else {
+      *reinterpret_cast<float4*>(static_cast<float*>(p.final_out) + at) =
+          make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
+    }
   }
 }
 

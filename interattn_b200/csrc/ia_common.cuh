@@ -158,10 +158,23 @@ int launch_build_summaries(const void* k_pool, const void* v_pool, const int32_t
 // split_counters (may be null): one int per (sequence, kv head), cleared by the selection
 // kernel for the attention kernel's fused finalize
 // exchange (may be null) + block range: split-KV across GPUs, this rank scores blocks [block_lo, block_hi)
+// attend (may be null): the one-kernel layer step.  Where the launch shape gives every (sequence, kv head)
+// to one CTA, that CTA goes on to attend over the pages of the blocks it has just picked (and the
+// suffix) and writes the output rows - `used` tells the caller whether it did, i.e. whether the
+// attention kernel is still to be launched.
+struct SelectAttend {
+  const void* k_pool;
+  const void* v_pool;
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  void* out;      // [batch, kv heads * group, head_dim] in the KV dtype
+  int used;       // out: 1 when the fused kernel was launched
+};
 int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_lens, const ia_geom& g,
                   int mode, int top_k, float eps, int max_sel, int32_t* sel_idx, int32_t* sel_count,
                   const ia_select_aux& aux, int* split_counters, cudaStream_t stream,
-                  const ia_select_exchange* exchange = nullptr, int block_lo = 0, int block_hi = 0);
+                  const ia_select_exchange* exchange = nullptr, int block_lo = 0, int block_hi = 0,
+                  SelectAttend* attend = nullptr);
 // Fused finalize of the attention kernel: the last CTA of a (sequence, kv head) merges the splits.
 struct FusedFinalize {
   void* out;            // [batch, rows, D]

@@ -89,9 +89,11 @@ __device__ __forceinline__ unsigned long long trace_now() {
     if (threadIdx.x == 0 && p.aux.delta != nullptr)                                                    \
       p.aux.delta[(int64_t)blockIdx.x * 16 + (i)] = (float)(trace_now() - trace_t0) * 1e-3f;           \
   } while (0)
+#define IA_TRACE_T0 trace_t0
 #else
 #define IA_TRACE_BEGIN() do { } while (0)
 #define IA_TRACE(i) do { } while (0)
+#define IA_TRACE_T0 0ull
 #endif
 
 // CTA shape: NG warp groups of four warps (one ring stage each at a time) plus one
@@ -139,6 +141,17 @@ struct SelectParams {
   ia_select_exchange xch;
   int block_lo, block_hi;
   int n_pairs;
+  // One-kernel layer step (att.on): the CTA that routed a (sequence, kv head) attends over what it picked.
+  struct Attend {
+    // the K and V pools as 4-D tensors [page, kv head, token, head_dim]; box = 128 bytes x one page of tokens
+    CUtensorMap tm_k, tm_v;
+    const int32_t* block_table;
+    const int32_t* seq_lens;
+    void* out;
+    int max_pages, n_pool_pages;
+    int ring_bytes;  // shared memory of the ring (the selection's stages), reused for the pages
+    int on;
+  } att;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -204,6 +217,27 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// one box of a 4-D tensor (c0 = element column .. c3 = outermost coordinate) global -> shared
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
+          "r"(smem_u32(dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// transpose of an 8 x 8 matrix of 16-bit elements held one row pair per thread (fragment layout)
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
 }
 
 // Running softmax normalisers of one query row: m = max z, l = sum e^{z - m},
@@ -357,9 +391,258 @@ template <int D, int G, bool MMA, int NG> struct SmemPlan {
   }
 };
 
-template <typename T, int D, int G, int NG, typename KB, bool DIAG>
-__global__ void __launch_bounds__(Shape<NG>::threads, Shape<NG>::min_ctas)
-condition_block_select_kernel(const __grid_constant__ SelectParams p) {
+// ---- the attention phase of the one-kernel layer step ---------------------------------------
+// Warp-level attention of up to eight query rows over 16-token pages with the operands swapped: the
+// page's tokens are the M side of both products, the query rows the N side (padded to 8) -
+//   S^T[token, row] = K[token, :] . Q[row, :]          (A = K tile as stored, B = Q)
+//   O^T[d, row]    += V^T[d, token] P^T[token, row]    (A = V tile through ldmatrix.trans, B = P^T)
+// so that a thread holds 32 output accumulators (head_dim 128) instead of the 64 of the row-major
+// form, and the whole phase fits the register budget of the selection kernel it is appended to.  A
+// thread's two S columns are its two query rows: the running maximum and sum of a row live in the
+// four threads of a quad column and are combined across the eight token rows with three shuffles.
+// P^T reaches the B-fragment layout through one 8 x 8 transpose (movmatrix) per eight tokens.
+template <int D, int G> struct PageAttention {
+  static constexpr int KSTEPS = D / 16, MT = D / 16;
+  static constexpr int kBox = 16 * 128;            // one TMA box: 16 token rows x 128 bytes, 128-byte swizzle
+  static constexpr int kTile = 16 * D * 2;         // the K (or V) rows of one page and kv head
+  uint32_t qb[KSTEPS][2];
+  float o[MT][4];
+  float m0, m1, l0, l1;  // query rows 2 qlane and 2 qlane + 1, log2 domain; l: this thread's share
+  int lane, quad, qlane;
+  float sc_qk;
+
+  __device__ __forceinline__ void init(int lane_, const float* q_s) {
+    lane = lane_; quad = lane_ >> 2; qlane = lane_ & 3;
+    sc_qk = kLog2e / sqrtf((float)D);
+#pragma unroll
+    for (int j = 0; j < MT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
+    m0 = -INFINITY; m1 = -INFINITY; l0 = 0.f; l1 = 0.f;
+    // B fragments of Q^T: (k = head_dim 2 qlane, +1 (+8), n = query row quad); rows past G are zero
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      const int d0 = kk * 16 + qlane * 2;
+      qb[kk][0] = quad < G ? pack_bf16(q_s[quad * D + d0], q_s[quad * D + d0 + 1]) : 0u;
+      qb[kk][1] = quad < G ? pack_bf16(q_s[quad * D + d0 + 8], q_s[quad * D + d0 + 9]) : 0u;
+    }
+  }
+
+  // One page (K tile at `stage`, V tile behind it; token rows [lo, hi) are live) into the running state.
+  __device__ __forceinline__ void consume(uint32_t stage, int lo, int hi) {
+    const uint32_t ktile = stage, vtile = stage + kTile;
+    const int mat = lane >> 3, rr = lane & 7;
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const int row = (mat & 1) * 8 + rr;  // token row of this lane's ldmatrix address
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const int ch = kk * 2 + (mat >> 1);
+        uint32_t a[4];
+        ldmatrix_x4(ktile + (ch >> 3) * kBox + row * 128 + (((ch & 7) ^ (row & 7)) << 4), a);
+        mma_bf16(s, a, qb[kk]);
+      }
+    }
+    // s[0], s[1]: token quad, rows 2 qlane, 2 qlane + 1;  s[2], s[3]: token quad + 8
+    const bool oka = quad >= lo && quad < hi, okb = quad + 8 >= lo && quad + 8 < hi;
+    s[0] = oka ? s[0] * sc_qk : -INFINITY;
+    s[1] = oka ? s[1] * sc_qk : -INFINITY;
+    s[2] = okb ? s[2] * sc_qk : -INFINITY;
+    s[3] = okb ? s[3] * sc_qk : -INFINITY;
+    float t0 = fmaxf(s[0], s[2]), t1 = fmaxf(s[1], s[3]);
+#pragma unroll
+    for (int x = 4; x < 32; x <<= 1) {
+      t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, x));
+      t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, x));
+    }
+    const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);
+    const float ref0 = n0 == -INFINITY ? 0.f : n0, ref1 = n1 == -INFINITY ? 0.f : n1;
+    const float a0 = exp2f(m0 - ref0), a1 = exp2f(m1 - ref1);
+    m0 = n0; m1 = n1;
+    const float p0 = exp2f(s[0] - ref0), p1 = exp2f(s[1] - ref1);
+    const float p2 = exp2f(s[2] - ref0), p3 = exp2f(s[3] - ref1);
+    l0 = l0 * a0 + (p0 + p2);
+    l1 = l1 * a1 + (p1 + p3);
+    uint32_t pb[2];
+    pb[0] = movmatrix_trans(pack_bf16(p0, p1));  // (tokens 2 qlane, +1; row quad)
+    pb[1] = movmatrix_trans(pack_bf16(p2, p3));  // tokens + 8
+#pragma unroll
+    for (int j = 0; j < MT; ++j) { o[j][0] *= a0; o[j][1] *= a1; o[j][2] *= a0; o[j][3] *= a1; }
+    {
+      const int row = (mat >> 1) * 8 + rr;  // token row
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        const int ch = j * 2 + (mat & 1);
+        uint32_t a[4];
+        ldmatrix_x4_trans(vtile + (ch >> 3) * kBox + row * 128 + (((ch & 7) ^ (row & 7)) << 4), a);
+        mma_bf16(o[j], a, pb);
+      }
+    }
+  }
+};
+
+// Every thread of the CTA that routed `pair` calls this after the routing: sel_list[0..count) are the
+// picked blocks, ascending.  All threads resolve the pages through the block table into page_list;
+// the CW consumer warps then take the pages round robin, each through a ring of its own carved from
+// the selection's stages (the stage count is a multiple of CW) that it fills itself with four TMA
+// boxes per page, and are merged through the idle ring at the end.  All waits are bounded.
+template <int D, int G, int CW>
+__device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int pair, int seq, int prefix_raw,
+                                                      const int* sel_list, int count, const float* q_s,
+                                                      int* page_list, int page_cap, unsigned char* ring,
+                                                      unsigned char* bar_area, unsigned long long trace_t0) {
+  (void)trace_t0;  // read by the stamps of the profiling build only
+  using PA = PageAttention<D, G>;
+  constexpr int kPage = 16;
+  constexpr int kTile = PA::kTile, kStage = 2 * kTile, kBoxes = D * 2 / 128, kBox = PA::kBox;
+  constexpr int kMaxRing = 32;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint64_t* full_b = reinterpret_cast<uint64_t*>(bar_area);
+  int nsb = min(p.att.ring_bytes / kStage, kMaxRing);
+  nsb -= nsb % CW;  // the launcher made sure that at least CW stages fit
+  const int ppb = p.block_size / kPage;
+  const int cap = p.att.max_pages * kPage;
+  const int prefix = min(prefix_raw, cap);
+  const int seq_len = min(max(p.att.seq_lens[seq], prefix), cap);
+  const int n_sel_items = count * ppb;
+  const int suf_first = prefix / kPage;
+  const int n_suf = seq_len > prefix ? (seq_len - 1) / kPage - suf_first + 1 : 0;
+  const int n_items = n_sel_items + n_suf;
+  const int head = pair - seq * p.n_kv_heads;
+
+  if (tid == 0) {
+    for (int s = 0; s < nsb; ++s) mbar_init(&full_b[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the ring was read through ldmatrix; TMA writes it next
+  __syncthreads();
+  IA_TRACE(11);  // profiling build: stamps 11 - 14 are the attention phase (11, 12 replace the late radix passes)
+
+  // item i: page i % ppb of picked block i / ppb, then the pages that hold the suffix [prefix, seq_len)
+  auto describe = [&](int i, int& lpage, int& lo, int& hi) {
+    if (i < n_sel_items) {
+      lpage = sel_list[i / ppb] * ppb + i % ppb;
+      lo = 0;
+      hi = max(min(prefix - lpage * kPage, kPage), 0);
+    } else {
+      lpage = suf_first + (i - n_sel_items);
+      lo = max(prefix - lpage * kPage, 0);
+      hi = max(min(seq_len - lpage * kPage, kPage), lo);
+    }
+  };
+  const int32_t* table = p.att.block_table + (int64_t)seq * p.att.max_pages;
+  PA w;
+  if (warp < CW) w.init(lane, q_s);
+  // Items go through in chunks of page_cap (one chunk unless the epsilon rule kept nearly every block).
+  // Item i always uses stage i % nsb, so the ring carries over from chunk to chunk.
+  for (int c0 = 0; c0 < n_items; c0 += page_cap) {
+    const int c1 = min(c0 + page_cap, n_items);
+    // every thread: the chunk's physical pages, one round trip to the block table for all of them;
+    // -1 = nothing to fetch (no live row, or an entry outside the table or the pool - reported, never read)
+    for (int i = c0 + tid; i < c1; i += blockDim.x) {
+      int lpage, lo, hi, page = -1;
+      describe(i, lpage, lo, hi);
+      if (hi > lo) {
+        if (lpage >= 0 && lpage < p.att.max_pages) page = table[lpage];
+        if (page < 0 || page >= p.att.n_pool_pages) {
+          atomicOr(&g_device_status, DEV_STATUS_BAD_INDEX);
+          page = -1;
+        }
+      }
+      page_list[i - c0] = page;
+    }
+    __syncthreads();
+    if (warp < CW) {
+      // Warp w takes the items w, w + CW, ... of the chunk; they cycle through its own nsb / CW stages.
+      // It fills those stages itself: lane 0 issues the page of item i + nsb into the stage that item
+      // i has just been consumed from - no producer warp, no "empty" barriers, and the issue cost of
+      // the TMA instructions (four per page) is spread over all consumer warps.
+      auto issue = [&](int i) {  // one lane
+        int lpage, lo, hi;
+        describe(i, lpage, lo, hi);
+        const int page = page_list[i - c0];
+        const int stage = i % nsb;
+        unsigned char* st = ring + (size_t)stage * kStage;
+        if (page >= 0 && hi > lo) {
+          mbar_arrive_expect_tx(&full_b[stage], (uint32_t)kStage);
+#pragma unroll
+          for (int j = 0; j < kBoxes; ++j) {
+            tma_load_4d(st + j * kBox, &p.att.tm_k, j * 64, 0, head, page, &full_b[stage]);
+            tma_load_4d(st + kTile + j * kBox, &p.att.tm_v, j * 64, 0, head, page, &full_b[stage]);
+          }
+        } else {
+          mbar_arrive(&full_b[stage]);  // nothing to fetch: the phase completes at once
+        }
+      };
+      const int first = c0 + (warp - c0 % CW + CW) % CW;
+      if (lane == 0)
+        for (int i = first, k = 0; k < nsb / CW && i < c1; ++k, i += CW) issue(i);
+      bool alive = true;
+      for (int i = first; i < c1; i += CW) {
+        const int stage = i % nsb, use = i / nsb;
+        if (alive && !mbar_wait(&full_b[stage], (uint32_t)(use & 1))) {
+          alive = false;
+          if (lane == 0) atomicOr(&g_device_status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
+        }
+        int lpage, lo, hi;
+        describe(i, lpage, lo, hi);
+        if (page_list[i - c0] >= 0 && hi > lo) w.consume(smem_u32(ring + (size_t)stage * kStage), lo, hi);
+        if (i == warp) IA_TRACE(13);
+        __syncwarp();  // every lane has read the stage: it may be refilled
+        if (lane == 0 && i + nsb < c1) issue(i + nsb);
+      }
+    }
+    if (c1 < n_items) __syncthreads();  // the page list is rewritten for the next chunk
+  }
+  __syncthreads();  // every page is consumed, nothing is in flight: the ring is scratch now
+  IA_TRACE(12);
+
+  // ---- merge the consumer warps: [warp][G rows][D + 4] partial outputs, then m[8], l[8] ----------
+  constexpr int kRow = D + 4;
+  constexpr int kPerWarp = 8 * kRow + 16;
+  float* mbuf = reinterpret_cast<float*>(ring);
+  if (warp < CW) {
+    w.l0 += __shfl_xor_sync(0xffffffffu, w.l0, 4);
+    w.l0 += __shfl_xor_sync(0xffffffffu, w.l0, 8);
+    w.l0 += __shfl_xor_sync(0xffffffffu, w.l0, 16);
+    w.l1 += __shfl_xor_sync(0xffffffffu, w.l1, 4);
+    w.l1 += __shfl_xor_sync(0xffffffffu, w.l1, 8);
+    w.l1 += __shfl_xor_sync(0xffffffffu, w.l1, 16);
+    float* mo = mbuf + (size_t)warp * kPerWarp;
+    const int r0 = 2 * w.qlane, r1 = r0 + 1;
+#pragma unroll
+    for (int j = 0; j < PA::MT; ++j) {
+      const int d = j * 16 + w.quad;
+      if (r0 < G) { mo[r0 * kRow + d] = w.o[j][0]; mo[r0 * kRow + d + 8] = w.o[j][2]; }
+      if (r1 < G) { mo[r1 * kRow + d] = w.o[j][1]; mo[r1 * kRow + d + 8] = w.o[j][3]; }
+    }
+    if (w.quad == 0) {
+      mo[8 * kRow + r0] = w.m0; mo[8 * kRow + 8 + r0] = w.l0;
+      mo[8 * kRow + r1] = w.m1; mo[8 * kRow + 8 + r1] = w.l1;
+    }
+  }
+  __syncthreads();
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.att.out) + (int64_t)pair * G * D;
+  for (int e = tid; e < G * D; e += blockDim.x) {
+    const int g = e / D, d = e - g * D;
+    float top = -INFINITY;
+#pragma unroll
+    for (int ww = 0; ww < CW; ++ww) top = fmaxf(top, mbuf[(size_t)ww * kPerWarp + 8 * kRow + g]);
+    float num = 0.f, den = 0.f;
+    if (top > -INFINITY) {
+#pragma unroll
+      for (int ww = 0; ww < CW; ++ww) {
+        const float* mo = mbuf + (size_t)ww * kPerWarp;
+        const float a = exp2f(mo[8 * kRow + g] - top);
+        num = fmaf(a, mo[g * kRow + d], num);
+        den = fmaf(a, mo[8 * kRow + 8 + g], den);
+      }
+    }
+    out[e] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+  }
+  IA_TRACE(14);
+}
+
+template <typename T, int D, int G, int NG, typename KB, bool DIAG, bool FUSE>
+__device__ __forceinline__ void select_body(const SelectParams& p) {
   using L = TileLayout<T, D, KB, DIAG>;
   using P = SmemPlan<D, G, kUseMma<T, G>, NG>;
   constexpr int kGroups = NG, kConsumerWarps = Shape<NG>::consumer_warps, kWarps = Shape<NG>::warps,
@@ -1155,8 +1438,13 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
 
   int32_t* out_idx = p.sel_idx + (int64_t)pair * p.max_sel;
   int n_written;
+  // one-kernel step: the picked blocks also stay in shared memory (the value norms are not needed any more)
+  int* sel_list = reinterpret_cast<int*>(vn_s);
   if (!xch_on) {
-    n_written = route(score_s, nb, [&](int slot, int b) { out_idx[slot] = b; });
+    n_written = route(score_s, nb, [&](int slot, int b) {
+      out_idx[slot] = b;
+      if constexpr (FUSE) sel_list[slot] = b;
+    });
   } else {
     // Split-KV: the k best of this GPU's blocks are candidates - (score, block index) in block order -
     // and go to every GPU; the k best of all candidates, taken in rank order (= block order, the
@@ -1203,6 +1491,29 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
     if (p.split_counters != nullptr) p.split_counters[pair] = 0;
   }
   leave();
+  if constexpr (FUSE) {
+    // The histograms are idle: their 3 KB hold the page ring's barriers and descriptors.
+    static_assert(P::hist >= 32 * 8, "the page ring's barriers live in the histogram area");
+    // (z, delta) per (row, block) are dead too: the resolved page numbers go there
+    attend_selected_pages<D, G, kConsumerWarps>(p, pair, seq, prefix, sel_list, count, q_s,
+                                                reinterpret_cast<int*>(z_s), 2 * G * nbl, stage_base,
+                                                reinterpret_cast<unsigned char*>(hist), IA_TRACE_T0);
+  }
+}
+
+template <typename T, int D, int G, int NG, typename KB, bool DIAG>
+__global__ void __launch_bounds__(Shape<NG>::threads, Shape<NG>::min_ctas)
+condition_block_select_kernel(const __grid_constant__ SelectParams p) {
+  select_body<T, D, G, NG, KB, DIAG, false>(p);
+}
+
+// The one-kernel layer step: selection, then - in the same CTA, with the picked blocks still in shared
+// memory - paged attention over them and the suffix, and the output rows.  bf16 pools, at most eight
+// query rows per kv head, one CTA per (sequence, kv head).
+template <int D, int G, int NG, typename KB>
+__global__ void __launch_bounds__(Shape<NG>::threads, Shape<NG>::min_ctas)
+condition_block_select_attend_kernel(const __grid_constant__ SelectParams p) {
+  select_body<__nv_bfloat16, D, G, NG, KB, false, true>(p);
 }
 
 // cuTensorMapEncodeTiled lives in the driver library; fetch it through the
@@ -1254,19 +1565,106 @@ static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t 
   return IA_OK;
 }
 
-template <typename T, int D, int G, int NG, typename KB, bool DIAG>
-static int launch_shaped(const SelectParams& p, int n_pairs, size_t smem, cudaStream_t stream) {
-  auto kern = condition_block_select_kernel<T, D, G, NG, KB, DIAG>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "select: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  e = launch_overlapped(kern, (unsigned)(n_pairs * p.cluster), (unsigned)Shape<NG>::threads, smem, stream, p,
-                        p.cluster);
-  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "condition_block_select_kernel: %s", cudaGetErrorString(e));
-  return check_launch("condition_block_select_kernel");
+// A bf16 KV pool as the 4-D tensor [page, kv head, token, head_dim] with its own page and head strides
+// (elements); box = 64 elements x 16 tokens of one (page, kv head), 128-byte swizzle.  Pages past
+// n_pages are out of the tensor: the TMA unit fills them with zeros instead of reading.
+struct CachedPool { const void* base; int D, heads, pages; int64_t hs, ps; CUtensorMap map; };
+static int encode_pool(CUtensorMap* tm, const void* base, int D, int heads, int pages, int64_t head_stride,
+                       int64_t page_stride) {
+  constexpr int kSlots = 16;
+  static thread_local CachedPool cache[kSlots];
+  static thread_local int next_slot = 0;
+  for (int i = 0; i < kSlots; ++i)
+    if (cache[i].base == base && cache[i].D == D && cache[i].heads == heads && cache[i].pages == pages &&
+        cache[i].hs == head_stride && cache[i].ps == page_stride && base != nullptr) {
+      *tm = cache[i].map;
+      return IA_OK;
+    }
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (enc == nullptr) return fail(IA_ERR_LAUNCH, "select: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)D, 16, (cuuint64_t)heads, (cuuint64_t)pages};
+  const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)head_stride * 2, (cuuint64_t)page_stride * 2};
+  const cuuint32_t box[4] = {64, 16, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return IA_ERR_UNSUPPORTED;  // strides the TMA unit cannot express: the caller keeps two kernels
+  cache[next_slot] = CachedPool{base, D, heads, pages, head_stride, page_stride, *tm};
+  next_slot = (next_slot + 1) % kSlots;
+  return IA_OK;
 }
 
+// What launch_select was asked to fuse; resolved into SelectParams::att once the launch shape is known.
+struct AttendRequest {
+  SelectAttend* req;
+  const ia_geom* geom;
+};
+
+template <typename Kern>
+static int launch_kernel(Kern kern, const char* name, const SelectParams& p, int n_pairs, unsigned threads, size_t smem,
+                         cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "select: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  e = launch_overlapped(kern, (unsigned)(n_pairs * p.cluster), threads, smem, stream, p, p.cluster);
+  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "%s: %s", name, cudaGetErrorString(e));
+  return check_launch(name);
+}
+
+// The fused form applies to bf16 pools with head_dim 128, at most eight query rows per kv head, the
+// range bound, one CTA per (sequence, kv head), no exchange with other GPUs, and a ring that holds at
+// least one page per consumer warp.  INTERATTN_B200_FUSED=0 keeps the two kernels.
+template <typename T, int D, int G, int NG, typename KB, bool DIAG>
+static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pairs, size_t smem, size_t ring_bytes,
+                             int resident_ctas, cudaStream_t stream, int* status) {
+  if constexpr (sizeof(T) == 2 && D == 128 && G <= 8 && !DIAG) {
+    // One wave only: with more CTAs than resident slots a CTA would hold its SM through the serial
+    // phases of the selection while the attention of other pairs waits for a slot (measured: the ragged
+    // 70B batch, 512 pairs, 293 us fused against 247 us as two kernels).
+    if (ar.req == nullptr || p.cluster != 1 || p.xch.n_ranks > 0 || n_pairs > resident_ctas) return false;
+    static const bool off = [] {
+      const char* v = getenv("INTERATTN_B200_FUSED");
+      return v != nullptr && v[0] == '0';
+    }();
+    const ia_geom& g = *ar.geom;
+    constexpr size_t kStage = 2 * 16 * D * 2;
+    if (off || g.page_size != 16 || g.block_size % 16 != 0 || g.n_pool_pages <= 0 ||
+        ring_bytes < (size_t)Shape<NG>::consumer_warps * kStage)
+      return false;
+    if (encode_pool(&p.att.tm_k, ar.req->k_pool, D, g.n_kv_heads, g.n_pool_pages, g.pool_head_stride,
+                    g.pool_page_stride) != IA_OK ||
+        encode_pool(&p.att.tm_v, ar.req->v_pool, D, g.n_kv_heads, g.n_pool_pages, g.pool_head_stride,
+                    g.pool_page_stride) != IA_OK)
+      return false;
+    p.att.block_table = ar.req->block_table;
+    p.att.seq_lens = ar.req->seq_lens;
+    p.att.out = ar.req->out;
+    p.att.max_pages = g.max_pages;
+    p.att.n_pool_pages = g.n_pool_pages;
+    p.att.ring_bytes = (int)ring_bytes;
+    p.att.on = 1;
+    *status = launch_kernel(condition_block_select_attend_kernel<D, G, NG, KB>, "condition_block_select_attend_kernel",
+                            p, n_pairs, (unsigned)Shape<NG>::threads, smem, stream);
+    ar.req->used = 1;
+    return true;
+  } else {
+    return false;
+  }
+}
+
+template <typename T, int D, int G, int NG, typename KB, bool DIAG>
+static int launch_shaped(SelectParams& p, const AttendRequest& ar, int n_pairs, size_t smem, size_t ring_bytes,
+                         int resident_ctas, cudaStream_t stream) {
+  int status = IA_OK;
+  if (try_launch_fused<T, D, G, NG, KB, DIAG>(p, ar, n_pairs, smem, ring_bytes, resident_ctas, stream, &status))
+    return status;
+  return launch_kernel(condition_block_select_kernel<T, D, G, NG, KB, DIAG>, "condition_block_select_kernel", p,
+                       n_pairs, (unsigned)Shape<NG>::threads, smem, stream);
+}
+
+
 template <typename T, int D, int G, typename KB, bool DIAG>
-static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stream) {
+static int launch_typed(const SelectParams& base, const AttendRequest& ar, int n_pairs, cudaStream_t stream) {
   using L = TileLayout<T, D, KB, DIAG>;
   using PW = SmemPlan<D, G, kUseMma<T, G>, kWideGroups>;
   using PN = SmemPlan<D, G, kUseMma<T, G>, kNarrowGroups>;
@@ -1332,7 +1730,9 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
         if (stages > my_tiles) stages = my_tiles < 2 ? 2 : my_tiles;
         if (stages > kMaxStages) stages = kMaxStages;
         p.n_stages = stages;
-        return launch_shaped<T, D, G, kNarrowGroups, KB, DIAG>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
+        // the one-kernel step turns the rest of the CTA's share of shared memory into page stages
+        const size_t ring = ar.req != nullptr ? ((budget - fixed) & ~(size_t)1023) : (size_t)stages * L::bytes;
+        return launch_shaped<T, D, G, kNarrowGroups, KB, DIAG>(p, ar, n_pairs, fixed + ring, ring, sms * ctas, stream);
       }
       break;  // the narrow shape is only ever tried with the cluster chosen above (1 unless pinned)
     }
@@ -1346,24 +1746,26 @@ static int launch_typed(const SelectParams& base, int n_pairs, cudaStream_t stre
   int stages = (int)(((size_t)max_smem - fixed) / L::bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.n_stages = stages;
-  return launch_shaped<T, D, G, kWideGroups, KB, DIAG>(p, n_pairs, fixed + (size_t)stages * L::bytes, stream);
+  const size_t ring = ar.req != nullptr ? (((size_t)max_smem - fixed) & ~(size_t)1023) : (size_t)stages * L::bytes;
+  return launch_shaped<T, D, G, kWideGroups, KB, DIAG>(p, ar, n_pairs, fixed + ring, ring, sms, stream);
 }
 
 template <typename T, int D, typename KB, bool DIAG>
-static int launch_group_bound(const SelectParams& p, int n_pairs, int group, cudaStream_t stream) {
+static int launch_group_bound(const SelectParams& p, const AttendRequest& ar, int n_pairs, int group,
+                              cudaStream_t stream) {
   switch (group) {
-    case 1: return launch_typed<T, D, 1, KB, DIAG>(p, n_pairs, stream);
-    case 2: return launch_typed<T, D, 2, KB, DIAG>(p, n_pairs, stream);
-    case 4: return launch_typed<T, D, 4, KB, DIAG>(p, n_pairs, stream);
-    case 8: return launch_typed<T, D, 8, KB, DIAG>(p, n_pairs, stream);
-    case 16: return launch_typed<T, D, 16, KB, DIAG>(p, n_pairs, stream);
+    case 1: return launch_typed<T, D, 1, KB, DIAG>(p, ar, n_pairs, stream);
+    case 2: return launch_typed<T, D, 2, KB, DIAG>(p, ar, n_pairs, stream);
+    case 4: return launch_typed<T, D, 4, KB, DIAG>(p, ar, n_pairs, stream);
+    case 8: return launch_typed<T, D, 8, KB, DIAG>(p, ar, n_pairs, stream);
+    case 16: return launch_typed<T, D, 16, KB, DIAG>(p, ar, n_pairs, stream);
     default: return fail(IA_ERR_UNSUPPORTED, "select: group_size %d not built (1, 2, 4, 8, 16)", group);
   }
 }
 template <typename T, int D, typename KB = float>
-static int launch_group(const SelectParams& p, int n_pairs, int group, cudaStream_t stream) {
-  return p.rho != nullptr ? launch_group_bound<T, D, KB, true>(p, n_pairs, group, stream)
-                          : launch_group_bound<T, D, KB, false>(p, n_pairs, group, stream);
+static int launch_group(const SelectParams& p, const AttendRequest& ar, int n_pairs, int group, cudaStream_t stream) {
+  return p.rho != nullptr ? launch_group_bound<T, D, KB, true>(p, ar, n_pairs, group, stream)
+                          : launch_group_bound<T, D, KB, false>(p, ar, n_pairs, group, stream);
 }
 
 }  // namespace
@@ -1371,8 +1773,10 @@ static int launch_group(const SelectParams& p, int n_pairs, int group, cudaStrea
 int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_lens, const ia_geom& g,
                   int mode, int top_k, float eps, int max_sel, int32_t* sel_idx, int32_t* sel_count,
                   const ia_select_aux& aux, int* split_counters, cudaStream_t stream,
-                  const ia_select_exchange* exchange, int block_lo, int block_hi) {
+                  const ia_select_exchange* exchange, int block_lo, int block_hi, SelectAttend* attend) {
   SelectParams p{};
+  if (attend != nullptr) attend->used = 0;
+  const AttendRequest ar{attend, &g};
   if (exchange != nullptr) {
     p.xch = *exchange;
     p.block_lo = block_lo;
@@ -1394,14 +1798,14 @@ int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_le
   if (n_pairs <= 0) return IA_OK;
   if (g.reserved & IA_GEOM_KBAR_BF16) {  // k_bar stored in bf16: only next to bf16 pools ("mixed" storage)
     if (g.dtype != IA_BF16) return fail(IA_ERR_UNSUPPORTED, "select: bf16 k_bar needs bf16 pools");
-    if (g.head_dim == 128) return launch_group<__nv_bfloat16, 128, __nv_bfloat16>(p, n_pairs, g.group_size, stream);
-    if (g.head_dim == 64) return launch_group<__nv_bfloat16, 64, __nv_bfloat16>(p, n_pairs, g.group_size, stream);
+    if (g.head_dim == 128) return launch_group<__nv_bfloat16, 128, __nv_bfloat16>(p, ar, n_pairs, g.group_size, stream);
+    if (g.head_dim == 64) return launch_group<__nv_bfloat16, 64, __nv_bfloat16>(p, ar, n_pairs, g.group_size, stream);
   } else if (g.dtype == IA_BF16) {
-    if (g.head_dim == 128) return launch_group<__nv_bfloat16, 128>(p, n_pairs, g.group_size, stream);
-    if (g.head_dim == 64) return launch_group<__nv_bfloat16, 64>(p, n_pairs, g.group_size, stream);
+    if (g.head_dim == 128) return launch_group<__nv_bfloat16, 128>(p, ar, n_pairs, g.group_size, stream);
+    if (g.head_dim == 64) return launch_group<__nv_bfloat16, 64>(p, ar, n_pairs, g.group_size, stream);
   } else if (g.dtype == IA_F32) {
-    if (g.head_dim == 128) return launch_group<float, 128>(p, n_pairs, g.group_size, stream);
-    if (g.head_dim == 64) return launch_group<float, 64>(p, n_pairs, g.group_size, stream);
+    if (g.head_dim == 128) return launch_group<float, 128>(p, ar, n_pairs, g.group_size, stream);
+    if (g.head_dim == 64) return launch_group<float, 64>(p, ar, n_pairs, g.group_size, stream);
   }
   return fail(IA_ERR_UNSUPPORTED, "select: head_dim %d / dtype %d not built", g.head_dim, g.dtype);
 }

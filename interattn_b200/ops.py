@@ -475,6 +475,12 @@ def decode_attention_noalloc(
     return out
 
 
+def last_decode_fused() -> bool:
+    """True when this thread's last layer step (``DecodeAttention.step`` and its variants) ran as the single
+    fused launch ``condition_block_select_attend_kernel`` rather than as selection + attention."""
+    return bool(_lib.load().ia_last_decode_fused())
+
+
 def device_status() -> int:
     """Read and clear the device status word, an OR of the ``_lib.IA_DEV_STATUS_*`` masks: a bounded
     wait inside a kernel ran out (SELECT_WAIT, GEMM_WAIT, PEER_WAIT: that result is invalid), or a

@@ -5,7 +5,7 @@ spread with rho |q * w| / sqrt(D) against the oracle on the same stored (w, rho)
 
 Bars: w bit-exact (a subtraction, a maximum and one rounding of the same stored inputs); rho within
 1e-3 relative of the oracle (which follows the reference's expanded quadratic form in fp32) on blocks of
-more than one token and within 1e-5 of the float64 definition (the kernel uses the direct form); selected block indices identical.
+at least 32 tokens and within 1e-5 of the float64 definition everywhere (the kernel uses the direct form); selected block indices identical.
 """
 
 import pytest
@@ -62,9 +62,13 @@ def test_w_and_rho(bundle):
         assert torch.equal(summ.w[b, :, :nb].cpu().float(), w.float()), "w"
         got = summ.rho[b, :, :nb].cpu()
         many = osum.counts > 1
-        # the oracle follows the reference's expanded form |k|^2 - 2 k.k_bar + |k_bar|^2 (all over w^2) in fp32,
-        # which cancels ~3 digits on short blocks (small w, terms of 1e4); the kernel uses the direct form
-        assert torch.allclose(got[:, many], rho[:, many], rtol=1e-3, atol=1e-5), "rho"
+        # The oracle follows the reference's expanded form |k|^2 - 2 k.k_bar + |k_bar|^2 (all over w^2) in
+        # fp32.  On a short tail block w is tiny, the three terms reach 1e6 and cancel: the reference's
+        # value is then noise (a seeded 2-token block gives 0 where the definition gives 11.2).  The
+        # kernel uses the direct form; it is compared with the oracle on the long blocks and held to
+        # the float64 definition on all of them.
+        long_blocks = osum.counts >= 32
+        assert torch.allclose(got[:, long_blocks], rho[:, long_blocks], rtol=1e-3, atol=1e-5), "rho"
         # the definition itself, in float64: no key of the block lies outside the ellipsoid
         kb, _ = orc._blocked(k[:, :plen].double(), cfg.block_size)
         live = torch.arange(cfg.block_size).view(1, -1) < osum.counts.view(-1, 1)

@@ -1,0 +1,160 @@
+"""GPU parity of the one-kernel layer step (``condition_block_select_attend_kernel``): the CTA that
+picked the blocks of a (sequence, kv head) attends over their pages and the suffix itself.
+
+The launch shape decides whether a step fuses (one CTA per pair); the small cases here pin that shape
+through the environment (``INTERATTN_B200_SELECT_CLUSTER=1``, wide and narrow CTAs) and assert that the
+fused kernel ran.  Bars: the selection identical to the stand-alone selection kernel; the output within the
+bf16 tolerance (2e-2 abs / 1e-2 rel) of the oracle's attention over exactly those blocks.
+"""
+
+import pytest
+import torch
+
+from oracle import condition_block_oracle as orc
+from oracle.configs import CONFIGS, DecodeConfig, make_case, scaled
+from tests.gpu_util import logical_kv, max_blocks_of, oracle_summaries_from_gpu, to_device
+
+pytestmark = pytest.mark.gpu
+TOL = dict(rtol=1e-2, atol=2e-2)
+
+
+def _ops():
+    from interattn_b200 import ops
+    return ops
+
+
+CASES = [
+    scaled(CONFIGS["cfg2_llama8b_32k"], batch=3, max_len=2304, suffix=0),
+    scaled(CONFIGS["cfg2_llama8b_32k"], batch=2, max_len=1500, suffix=33),
+    scaled(CONFIGS["cfg4_longctx_128k"], batch=2, max_len=4096, suffix=1, top_k=8),
+    scaled(CONFIGS["cfg5_llama70b_ragged"], batch=5, max_len=1900, suffix=3),
+    DecodeConfig("bf16_g1", "bfloat16", 2, 2, 2, 128, 16, 64, 2, (300, 64), (0, 0), seed=8),
+    DecodeConfig("bf16_g2_ragged", "bfloat16", 4, 4, 2, 128, 16, 64, 3, (1, 129, 1000, 0), (15, 16, 17, 40), seed=11),
+    DecodeConfig("bf16_g8_long_suffix", "bfloat16", 2, 8, 1, 128, 16, 64, 2, (520, 7), (300, 5), seed=12),
+]
+
+
+def _check_against_oracle(cfg, case, summ, out, idx, cnt):
+    out = out.float().cpu()
+    idx, cnt = idx.cpu(), cnt.cpu()
+    for b in range(cfg.batch):
+        plen = int(case["prefix_lens"][b])
+        osum = oracle_summaries_from_gpu(summ, b, plen)
+        k, v = logical_kv(case, b)
+        mask = torch.zeros((cfg.n_kv_heads, osum.n_blocks), dtype=torch.bool)
+        for h in range(cfg.n_kv_heads):
+            mask[h, idx[b, h, :int(cnt[b, h])].long()] = True
+        qg = case["q"][b].reshape(cfg.n_kv_heads, cfg.group_size, cfg.head_dim).float()
+        want = orc.decode_attention(qg, k, v, plen, cfg.block_size, mask, rep_mode="sparse_only")
+        got = out[b].reshape(cfg.n_kv_heads, cfg.group_size, cfg.head_dim)
+        torch.testing.assert_close(got, want, **TOL)
+
+
+@pytest.mark.parametrize("shape", ["wide", "narrow"])
+@pytest.mark.parametrize("cfg", CASES, ids=lambda c: c.name)
+def test_fused_step_matches_selection_and_oracle(cfg, shape, monkeypatch):
+    ops = _ops()
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    monkeypatch.setenv("INTERATTN_B200_SELECT_SHAPE", shape)
+    case = make_case(cfg, spare_pages=3)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k)
+    for _ in range(2):  # twice: the ring's barriers are initialised per launch
+        out = step.step(q).clone()
+        assert ops.last_decode_fused(), "the pinned shape must take the one-kernel form"
+    idx, cnt, _ = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.equal(step.sel_idx[:, :, :idx.shape[2]], idx) and torch.equal(step.sel_count, cnt)
+    _check_against_oracle(cfg, case, summ, out, idx, cnt)
+    # the two-kernel form on the same inputs (hybrid steps never fuse; here: the three public calls)
+    o, lse = ops.sparse_decode(q, kv, idx, cnt, block_size=cfg.block_size, max_blocks=summ.max_blocks, n_splits=2)
+    two = ops.finalize(o, lse, q.dtype)
+    torch.testing.assert_close(out.float(), two.float(), **TOL)
+
+
+def test_fused_step_with_epsilon_rule(monkeypatch):
+    ops = _ops()
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    cfg = CASES[1]
+    case = make_case(cfg, spare_pages=3)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
+    _, _, aux = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, want=("score",))
+    eps = float(aux["score"].flatten().sort().values[-40])  # keeps a few dozen blocks in total
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, eps=eps)
+    out = step.step(q).clone()
+    assert ops.last_decode_fused()
+    idx, cnt, _ = ops.select_blocks(q, summ, kv.prefix_lens, eps=eps)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.equal(step.sel_idx[:, :, :idx.shape[2]], idx) and torch.equal(step.sel_count, cnt)
+    assert int(cnt.sum()) > 0
+    _check_against_oracle(cfg, case, summ, out, idx, cnt)
+
+
+def test_fused_step_empty_prefix_and_empty_sequence(monkeypatch):
+    ops = _ops()
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    cfg = DecodeConfig("nopfx", "bfloat16", 2, 8, 2, 128, 16, 64, 4, (0, 0), (21, 0), seed=3)
+    case = make_case(cfg, spare_pages=2)
+    case["block_table"] = case["block_table"].clamp_min(0)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, 64, max_blocks=1)
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=4)
+    out = step.step(q).float().cpu()
+    assert ops.last_decode_fused() and ops.device_status() == 0
+    assert int(step.sel_count.sum()) == 0
+    k, v = logical_kv(case, 0)
+    qg = case["q"][0].reshape(2, 4, 128).float()
+    want = orc.decode_attention(qg, k, v, 0, 64, torch.zeros((2, 0), dtype=torch.bool), rep_mode="sparse_only")
+    torch.testing.assert_close(out[0].reshape(2, 4, 128), want, **TOL)
+    assert bool((out[1] == 0).all())  # nothing to attend to: zeros, not NaN
+
+
+def test_fused_step_skips_a_table_entry_outside_the_pool(monkeypatch):
+    """A block-table entry past the declared pool size: the page contributes nothing, the device status
+    word reports it, nothing outside the pool is read (the TMA unit would zero-fill it anyway)."""
+    ops = _ops()
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    cfg = CASES[0]
+    case = make_case(cfg, spare_pages=3)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
+    good = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k).step(q).clone()
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    small = ops.PagedKV(k_pool=kv.k_pool, v_pool=kv.v_pool, block_table=kv.block_table, prefix_lens=kv.prefix_lens,
+                        seq_lens=kv.seq_lens, n_pool_pages=int(kv.block_table.max()))  # the last page is "outside"
+    out = ops.DecodeAttention(small, summ, cfg.n_q_heads, top_k=cfg.top_k).step(q).clone()
+    torch.cuda.synchronize()
+    assert ops.last_decode_fused()
+    assert ops.device_status() & 8, "IA_DEV_STATUS_BAD_INDEX"  # reading the word clears it
+    assert torch.isfinite(out.float()).all() and torch.isfinite(good.float()).all()
+
+
+def test_fused_step_replays_from_a_cuda_graph(monkeypatch):
+    ops = _ops()
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    cfg = CASES[3]
+    case = make_case(cfg, spare_pages=3)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k)
+    want = step.step(q).clone()
+    assert ops.last_decode_fused()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step.step(q)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step.step(q)
+    torch.cuda.current_stream().wait_stream(side)
+    step.out.zero_()
+    graph.replay()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(step.out, want)
+    assert ops.device_status() == 0

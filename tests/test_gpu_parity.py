@@ -238,12 +238,15 @@ def test_one_call_layer_step_matches_the_three_calls(bundle):
         want = ops.finalize(o, lse, q.dtype)
         torch.cuda.synchronize()
         assert torch.equal(step.sel_idx, idx) and torch.equal(step.sel_count, cnt)
-        assert torch.equal(out, want)
+        # the single fused launch (one CTA per pair, no representatives) partitions the pages differently
+        same = torch.equal if not ops.last_decode_fused() else (
+            lambda a, b: torch.allclose(a.float(), b.float(), **TOL[cfg.dtype]))
+        assert same(out, want)
         # host-buffer entry point: pinned q in, pinned out back
         q_host = case["q"].contiguous().pin_memory()
         out_host = torch.empty_like(q_host).pin_memory()
         step.step_host(q_host, out_host)
-        assert torch.equal(out_host, want.cpu())
+        assert same(out_host, want.cpu())
 
 
 def test_equal_share_grid_matches_the_pair_grid(bundle, monkeypatch):
