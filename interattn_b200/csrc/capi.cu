@@ -402,12 +402,11 @@ static int decode_attention_impl(const void* q, const void* k_pool, const void* 
     return fail(IA_ERR_BAD_ARG, "decode_attention: rep_mode %d", rep_mode);
   if (n_splits > 64) return fail(IA_ERR_BAD_ARG, "decode_attention: n_splits %d outside [1, 64]", n_splits);
   mark(0);
-  // Without representatives the selection kernel can go on to attend over what it picked - one launch;
-  // it says whether its launch shape allowed that (one CTA per (sequence, kv head), bf16, head_dim 128).
-  ia::SelectAttend attend{k_pool, v_pool, block_table, seq_lens, out, 0};
-  const bool may_fuse = rep_mode == IA_REP_SPARSE_ONLY;
+  // The selection kernel can go on to attend over what it picked - one launch; it says whether its
+  // launch shape allowed that (the whole grid resident at once, bf16, head_dim 128, <= 8 rows per kv head).
+  ia::SelectAttend attend{k_pool, v_pool, block_table, seq_lens, out, rep_mode == IA_REP_HYBRID, 1, 0};
   if (int s = launch_select(q, *summaries, prefix_lens, *geom, full_mode, top_k, eps, max_sel, idx, cnt, aux,
-                            w.split_counters, st, nullptr, 0, 0, may_fuse ? &attend : nullptr))
+                            w.split_counters, st, nullptr, 0, 0, &attend))
     return s;
   mark(1);
   t_last_decode_fused = attend.used;

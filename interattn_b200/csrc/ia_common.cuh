@@ -168,6 +168,8 @@ struct SelectAttend {
   const int32_t* block_table;
   const int32_t* seq_lens;
   void* out;      // [batch, kv heads * group, head_dim] in the KV dtype
+  int hybrid;     // blocks that are not picked attend through their representatives (z, v_bar)
+  int z_scratch;  // aux.z only feeds the attention kernel: the fused kernel need not write it
   int used;       // out: 1 when the fused kernel was launched
 };
 int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_lens, const ia_geom& g,

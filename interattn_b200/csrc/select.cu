@@ -145,6 +145,8 @@ struct SelectParams {
   struct Attend {
     // the K and V pools as 4-D tensors [page, kv head, token, head_dim]; box = 128 bytes x one page of tokens
     CUtensorMap tm_k, tm_v;
+    CUtensorMap tm_vbar;  // hybrid: the mean values [pairs * max_blocks, head_dim], box = 128 bytes x 16 blocks
+    int hybrid;           // IA_REP_HYBRID: every block that was not picked attends through (z, v_bar)
     const int32_t* block_table;
     const int32_t* seq_lens;
     void* out;
@@ -301,6 +303,9 @@ __device__ __forceinline__ uint32_t map_to_rank(const void* p, uint32_t rank) {
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+__device__ __forceinline__ void st_cluster_s32(uint32_t addr, int v) {
+  asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 // every thread of every CTA of the cluster; orders the remote stores before it against the loads after it
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -428,7 +433,7 @@ template <int D, int G> struct PageAttention {
 
   // One page (K tile at `stage`, V tile behind it; token rows [lo, hi) are live) into the running state.
   __device__ __forceinline__ void consume(uint32_t stage, int lo, int hi) {
-    const uint32_t ktile = stage, vtile = stage + kTile;
+    const uint32_t ktile = stage;
     const int mat = lane >> 3, rr = lane & 7;
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     {
@@ -447,6 +452,28 @@ template <int D, int G> struct PageAttention {
     s[1] = oka ? s[1] * sc_qk : -INFINITY;
     s[2] = okb ? s[2] * sc_qk : -INFINITY;
     s[3] = okb ? s[3] * sc_qk : -INFINITY;
+    accumulate(s, stage + kTile);
+  }
+
+  // A tile of 16 representatives: the mean values of blocks [first, first + n) are in the V half of the
+  // stage, their logits z = s + log count (natural log, from the selection pass) in shared memory as
+  // z[row * z_stride + block]; bit t of `skip` drops block first + t (it was picked and is attended
+  // token by token).
+  __device__ __forceinline__ void consume_reps(uint32_t stage, const float* z, int z_stride, int n, uint32_t skip) {
+    const int r0 = 2 * qlane, r1 = r0 + 1;
+    const bool oka = quad < n && ((skip >> quad) & 1u) == 0u;
+    const bool okb = quad + 8 < n && ((skip >> (quad + 8)) & 1u) == 0u;
+    float s[4];
+    s[0] = oka && r0 < G ? z[r0 * z_stride + quad] * kLog2e : -INFINITY;
+    s[1] = oka && r1 < G ? z[r1 * z_stride + quad] * kLog2e : -INFINITY;
+    s[2] = okb && r0 < G ? z[r0 * z_stride + quad + 8] * kLog2e : -INFINITY;
+    s[3] = okb && r1 < G ? z[r1 * z_stride + quad + 8] * kLog2e : -INFINITY;
+    accumulate(s, stage + kTile);
+  }
+
+  // online softmax over the 16 columns of S^T held as s[] (log2 domain, -inf = masked), then O^T += V^T P^T
+  __device__ __forceinline__ void accumulate(float (&s)[4], uint32_t vtile) {
+    const int mat = lane >> 3, rr = lane & 7;
     float t0 = fmaxf(s[0], s[2]), t1 = fmaxf(s[1], s[3]);
 #pragma unroll
     for (int x = 4; x < 32; x <<= 1) {
@@ -466,18 +493,20 @@ template <int D, int G> struct PageAttention {
     pb[1] = movmatrix_trans(pack_bf16(p2, p3));  // tokens + 8
 #pragma unroll
     for (int j = 0; j < MT; ++j) { o[j][0] *= a0; o[j][1] *= a1; o[j][2] *= a0; o[j][3] *= a1; }
-    {
-      const int row = (mat >> 1) * 8 + rr;  // token row
+    const int row = (mat >> 1) * 8 + rr;  // token row
 #pragma unroll
-      for (int j = 0; j < MT; ++j) {
-        const int ch = j * 2 + (mat & 1);
-        uint32_t a[4];
-        ldmatrix_x4_trans(vtile + (ch >> 3) * kBox + row * 128 + (((ch & 7) ^ (row & 7)) << 4), a);
-        mma_bf16(o[j], a, pb);
-      }
+    for (int j = 0; j < MT; ++j) {
+      const int ch = j * 2 + (mat & 1);
+      uint32_t a[4];
+      ldmatrix_x4_trans(vtile + (ch >> 3) * kBox + row * 128 + (((ch & 7) ^ (row & 7)) << 4), a);
+      mma_bf16(o[j], a, pb);
     }
   }
 };
+
+// Warps that attend: the consumer warps of the selection; in the narrow shape the idle producer warp
+// joins them (five warps, ten page stages in the shared memory a narrow CTA has, instead of four and eight).
+template <int NG> constexpr int kAttendWarps = NG == 1 ? Shape<NG>::warps : Shape<NG>::consumer_warps;
 
 // Every thread of the CTA that routed `pair` calls this after the routing: sel_list[0..count) are the
 // picked blocks, ascending.  All threads resolve the pages through the block table into page_list;
@@ -486,7 +515,9 @@ template <int D, int G> struct PageAttention {
 // boxes per page, and are merged through the idle ring at the end.  All waits are bounded.
 template <int D, int G, int CW>
 __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int pair, int seq, int prefix_raw,
-                                                      const int* sel_list, int count, const float* q_s,
+                                                      int crank, int C, const int* sel_list, int count,
+                                                      const float* q_s, const float* z_s, int z_stride, int b_lo,
+                                                      int b_hi, uint32_t* sel_bits, int nb_cap,
                                                       int* page_list, int page_cap, unsigned char* ring,
                                                       unsigned char* bar_area, unsigned long long trace_t0) {
   (void)trace_t0;  // read by the stamps of the profiling build only
@@ -496,7 +527,10 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
   constexpr int kMaxRing = 32;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint64_t* full_b = reinterpret_cast<uint64_t*>(bar_area);
-  int nsb = min(p.att.ring_bytes / kStage, kMaxRing);
+  // A cluster keeps the end of rank 0's ring free of pages: the ranks' partial results are stored there.
+  constexpr int kShare = G * D + 2 * G;  // floats: [G][D] sums relative to top[g], then top[G], den[G]
+  const int share_bytes = C > 1 ? C * kShare * 4 : 0;
+  int nsb = min((p.att.ring_bytes - share_bytes) / kStage, kMaxRing);
   nsb -= nsb % CW;  // the launcher made sure that at least CW stages fit
   const int ppb = p.block_size / kPage;
   const int cap = p.att.max_pages * kPage;
@@ -505,19 +539,40 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
   const int n_sel_items = count * ppb;
   const int suf_first = prefix / kPage;
   const int n_suf = seq_len > prefix ? (seq_len - 1) / kPage - suf_first + 1 : 0;
-  const int n_items = n_sel_items + n_suf;
+  // a cluster of C CTAs shares the pair: rank r takes the pages r, r + C, ... (item i of this CTA is page
+  // i * C + crank of the pair) and the ranks' partial results are merged by rank 0 at the end
+  const int n_pair_items = n_sel_items + n_suf;
+  // Hybrid: the blocks this CTA scored, [b_lo, b_hi), also attend through their representatives, 16 blocks
+  // (one tile of mean values) per item; their logits are still in this CTA's shared memory.  These items
+  // come first: they need no table look-up.
+  const int n_rep = p.att.hybrid ? (max(b_hi - b_lo, 0) + 15) / 16 : 0;
+  const int n_items = n_rep + (n_pair_items - crank + C - 1) / C;
   const int head = pair - seq * p.n_kv_heads;
 
   if (tid == 0) {
     for (int s = 0; s < nsb; ++s) mbar_init(&full_b[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (n_rep > 0)
+    for (int i = tid; i < (nb_cap + 31) / 32; i += blockDim.x) sel_bits[i] = 0u;
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the ring was read through ldmatrix; TMA writes it next
   __syncthreads();
   IA_TRACE(11);  // profiling build: stamps 11 - 14 are the attention phase (11, 12 replace the late radix passes)
+  if (n_rep > 0)  // which blocks were picked: their representatives are dropped (visible past the barrier below)
+    for (int i = tid; i < count; i += blockDim.x) {
+      const int b = sel_list[i];
+      if (b >= 0 && b < nb_cap) atomicOr(&sel_bits[b >> 5], 1u << (b & 31));
+    }
 
-  // item i: page i % ppb of picked block i / ppb, then the pages that hold the suffix [prefix, seq_len)
-  auto describe = [&](int i, int& lpage, int& lo, int& hi) {
+  // item i >= n_rep: page i % ppb of picked block i / ppb, then the pages that hold the suffix [prefix, seq_len)
+  auto describe = [&](int item, int& lpage, int& lo, int& hi) {
+    if (item < n_rep) {  // representatives of blocks [b_lo + 16 item, + hi)
+      lpage = -1;
+      lo = 0;
+      hi = min(b_hi - (b_lo + item * 16), 16);
+      return;
+    }
+    const int i = (item - n_rep) * C + crank;
     if (i < n_sel_items) {
       lpage = sel_list[i / ppb] * ppb + i % ppb;
       lo = 0;
@@ -540,7 +595,9 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
     for (int i = c0 + tid; i < c1; i += blockDim.x) {
       int lpage, lo, hi, page = -1;
       describe(i, lpage, lo, hi);
-      if (hi > lo) {
+      if (i < n_rep) {
+        page = 0;  // nothing to look up
+      } else if (hi > lo) {
         if (lpage >= 0 && lpage < p.att.max_pages) page = table[lpage];
         if (page < 0 || page >= p.att.n_pool_pages) {
           atomicOr(&g_device_status, DEV_STATUS_BAD_INDEX);
@@ -561,7 +618,12 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
         const int page = page_list[i - c0];
         const int stage = i % nsb;
         unsigned char* st = ring + (size_t)stage * kStage;
-        if (page >= 0 && hi > lo) {
+        if (i < n_rep) {  // 16 rows of mean values into the V half; rows past the pair's last block are masked
+          const int y = pair * p.max_blocks + b_lo + i * 16;
+          mbar_arrive_expect_tx(&full_b[stage], (uint32_t)kTile);
+#pragma unroll
+          for (int j = 0; j < kBoxes; ++j) tma_load_2d(st + kTile + j * kBox, &p.att.tm_vbar, j * 64, y, &full_b[stage]);
+        } else if (page >= 0 && hi > lo) {
           mbar_arrive_expect_tx(&full_b[stage], (uint32_t)kStage);
 #pragma unroll
           for (int j = 0; j < kBoxes; ++j) {
@@ -584,7 +646,28 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
         }
         int lpage, lo, hi;
         describe(i, lpage, lo, hi);
-        if (page_list[i - c0] >= 0 && hi > lo) w.consume(smem_u32(ring + (size_t)stage * kStage), lo, hi);
+        if (page_list[i - c0] >= 0 && hi > lo) {
+          const uint32_t st = smem_u32(ring + (size_t)stage * kStage);
+          if (lo > 0 || hi < kPage) {
+            // A partly live tile: the dead rows of V hold whatever the pool (or the next pair's
+            // summaries) holds there, and 0 x NaN would poison the product - zero them first.
+            for (int x = lane; x < kPage * (D * 2 / 16); x += 32) {
+              const int row = x / (D * 2 / 16), ch = x % (D * 2 / 16);
+              if (row < lo || row >= hi)
+                *reinterpret_cast<uint4*>(ring + (size_t)stage * kStage + kTile + (ch >> 3) * kBox + row * 128 +
+                                          ((ch & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // before TMA refills the stage
+            __syncwarp();
+          }
+          if (i < n_rep) {
+            const int first = b_lo + i * 16;
+            const uint32_t skip = (sel_bits[first >> 5] >> (first & 31)) & 0xffffu;
+            w.consume_reps(st, z_s + (first - b_lo), z_stride, hi, skip);
+          } else {
+            w.consume(st, lo, hi);
+          }
+        }
         if (i == warp) IA_TRACE(13);
         __syncwarp();  // every lane has read the stage: it may be refilled
         if (lane == 0 && i + nsb < c1) issue(i + nsb);
@@ -621,6 +704,9 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
   }
   __syncthreads();
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.att.out) + (int64_t)pair * G * D;
+  // C > 1: this CTA's share of the pair goes into slot `crank` of the shares at the end of rank 0's ring
+  float* shares = reinterpret_cast<float*>(ring + p.att.ring_bytes - share_bytes);
+  const uint32_t my_share = C > 1 ? map_to_rank(shares + crank * kShare, 0u) : 0u;
   for (int e = tid; e < G * D; e += blockDim.x) {
     const int g = e / D, d = e - g * D;
     float top = -INFINITY;
@@ -636,7 +722,34 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
         den = fmaf(a, mo[8 * kRow + 8 + g], den);
       }
     }
-    out[e] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    if (C == 1) {
+      out[e] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else {
+      st_cluster_f32(my_share + (uint32_t)e * 4u, num);
+      if (d == 0) {
+        st_cluster_f32(my_share + (uint32_t)(G * D + g) * 4u, top);
+        st_cluster_f32(my_share + (uint32_t)(G * D + G + g) * 4u, den);
+      }
+    }
+  }
+  if (C > 1) {
+    cluster_sync_all();  // every rank's share has landed in rank 0; the other ranks are done
+    if (crank == 0) {
+      for (int e = tid; e < G * D; e += blockDim.x) {
+        const int g = e / D;
+        float top = -INFINITY;
+        for (int r = 0; r < C; ++r) top = fmaxf(top, shares[r * kShare + G * D + g]);
+        float num = 0.f, den = 0.f;
+        if (top > -INFINITY) {
+          for (int r = 0; r < C; ++r) {  // rank order: the same sum on every run
+            const float a = exp2f(shares[r * kShare + G * D + g] - top);
+            num = fmaf(a, shares[r * kShare + e], num);
+            den = fmaf(a, shares[r * kShare + G * D + G + g], den);
+          }
+        }
+        out[e] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      }
+    }
   }
   IA_TRACE(14);
 }
@@ -665,6 +778,11 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_kbar) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_kmax) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_kmin) : "memory");
+    if constexpr (FUSE) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.att.tm_k) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.att.tm_v) : "memory");
+      if (p.att.hybrid) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.att.tm_vbar) : "memory");
+    }
   }
   grid_dependency_wait();
   grid_launch_dependents();
@@ -1290,213 +1408,231 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
       }
     }
   };
-  if (crank != 0) {  // nobody reads this CTA's shared memory any more
+  // One-kernel step: the picked blocks also stay in shared memory (the value norms are not needed any more).
+  int* sel_list = reinterpret_cast<int*>(vn_s);
+  int count = 0;
+  if (crank != 0) {
     leave();
-    return;
-  }
-
-  // ---- phase 4: routing ----------------------------------------------------------------
-  // route(sc, n, emit): among the n scores sc[0..n) pick the top_k best (higher score first, lower
-  // position first among equal scores) or, in epsilon mode, every score above eps; emit(slot, j) is
-  // called once per picked position j with its output slot - slots ascend with j.  Returns how
-  // many were picked.  Every thread of the CTA calls it (it contains CTA barriers).
-  auto route = [&](const float* sc, int n, auto emit) -> int {
-    uint32_t thr_key = 0, thr_mask = 0xffffffffu;  // keys are compared on the digits resolved so far
-    int take_equal = 0;
-    const int k_eff = (p.mode == IA_SELECT_TOPK) ? min(min(p.top_k, n), p.max_sel) : 0;
-    if (k_eff > 0 && k_eff < n) {
-      // Radix select of the k_eff-th largest key, 8 bits per pass.  Three
-      // histograms rotate: pass p fills hist[p % 3] and clears hist[(p + 1) % 3]
-      // (last read two passes ago), and every warp resolves the digit for itself
-      // from the finished histogram - so a pass needs one barrier.
-      uint32_t fixed = 0, fixed_mask = 0;
-      int remaining = k_eff;
-      for (int i = tid; i < 256; i += kThreads) hist[i] = 0;
-      __syncthreads();
+    // nobody reads this CTA's shared memory any more - unless it goes on to attend its share of the pages
+    if constexpr (!FUSE) return;
+  } else {
+    // ---- phase 4: routing ----------------------------------------------------------------
+    // route(sc, n, emit): among the n scores sc[0..n) pick the top_k best (higher score first, lower
+    // position first among equal scores) or, in epsilon mode, every score above eps; emit(slot, j) is
+    // called once per picked position j with its output slot - slots ascend with j.  Returns how
+    // many were picked.  Every thread of the CTA calls it (it contains CTA barriers).
+    auto route = [&](const float* sc, int n, auto emit) -> int {
+      uint32_t thr_key = 0, thr_mask = 0xffffffffu;  // keys are compared on the digits resolved so far
+      int take_equal = 0;
+      const int k_eff = (p.mode == IA_SELECT_TOPK) ? min(min(p.top_k, n), p.max_sel) : 0;
+      if (k_eff > 0 && k_eff < n) {
+        // Radix select of the k_eff-th largest key, 8 bits per pass.  Three
+        // histograms rotate: pass p fills hist[p % 3] and clears hist[(p + 1) % 3]
+        // (last read two passes ago), and every warp resolves the digit for itself
+        // from the finished histogram - so a pass needs one barrier.
+        uint32_t fixed = 0, fixed_mask = 0;
+        int remaining = k_eff;
+        for (int i = tid; i < 256; i += kThreads) hist[i] = 0;
+        __syncthreads();
 #pragma unroll 1  // executed once per launch: keep the cold code short (it is fetched from L2)
-      for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
-        int* h = hist + (pass % 3) * 256;
-        int* h_next = hist + ((pass + 1) % 3) * 256;
-        for (int i = tid; i < 256; i += kThreads) h_next[i] = 0;
+        for (int pass = 0; pass < 4; ++pass) {
+          const int shift = 24 - 8 * pass;
+          int* h = hist + (pass % 3) * 256;
+          int* h_next = hist + ((pass + 1) % 3) * 256;
+          for (int i = tid; i < 256; i += kThreads) h_next[i] = 0;
+          for (int base = 0; base < n; base += kThreads) {
+            const int b = base + tid;
+            const uint32_t key = b < n ? order_key(sc[b]) : 0u;
+            const bool live = b < n && (key & fixed_mask) == fixed;
+            const uint32_t digit = (key >> shift) & 255u;
+            // Bin d lives at word (d & 7) * 32 + (d >> 3): the eight bins a lane scans below are then in
+            // eight different rows of 32 consecutive words, so the scan's loads are free of bank conflicts
+            // (a [256] array read as h[8 lane + i] is an 8-way conflict, paid by every warp in every pass).
+            // The leading digit (sign and high exponent bits) is shared by most keys: there the lanes of
+            // a warp that share a digit send one atomic together; the later digits are spread, and finding
+            // equal ones costs more than the few conflicts it would save.
+            if (pass == 0) {
+              const uint32_t peers = __match_any_sync(0xffffffffu, live ? digit : 0xffffffffu);
+              if (live && lane == __ffs(peers) - 1) atomicAdd(&h[(digit & 7u) * 32u + (digit >> 3)], __popc(peers));
+            } else if (live) {
+              atomicAdd(&h[(digit & 7u) * 32u + (digit >> 3)], 1);
+            }
+          }
+#ifdef IA_SELECT_TRACE_FINE
+          if (pass < 2) IA_TRACE(9 + 3 * pass);
+#endif
+          __syncthreads();
+#ifdef IA_SELECT_TRACE_FINE
+          if (pass < 2) IA_TRACE(10 + 3 * pass);
+#endif
+          // lane owns bins [8 lane, 8 lane + 8); `above` = keys in the bins of higher lanes
+          int c[8], mine = 0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { c[i] = h[i * 32 + lane]; mine += c[i]; }
+          int incl = mine;  // inclusive suffix sum over lanes
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_down_sync(0xffffffffu, incl, o);
+            if (lane + o < 32) incl += v;
+          }
+          const int above = incl - mine;
+          const bool owner = (above < remaining) && (incl >= remaining);
+          int digit = 0, left = 0, in_bin = 0;
+          if (owner) {
+            int acc = above;
+#pragma unroll
+            for (int i = 7; i >= 0; --i) {
+              if (acc + c[i] >= remaining) { digit = lane * 8 + i; in_bin = c[i]; break; }
+              acc += c[i];
+            }
+            left = remaining - acc;
+          }
+          const int src = max(__ffs(__ballot_sync(0xffffffffu, owner)) - 1, 0);  // exactly one owner lane
+          digit = __shfl_sync(0xffffffffu, digit, src);
+          remaining = __shfl_sync(0xffffffffu, left, src);
+          in_bin = __shfl_sync(0xffffffffu, in_bin, src);
+          fixed |= (uint32_t)digit << shift;
+          fixed_mask |= 255u << shift;
+#ifdef IA_SELECT_TRACE_FINE
+          if (pass < 2) IA_TRACE(11 + 3 * pass);
+#else
+          IA_TRACE(9 + pass);
+#endif
+          // every key of the threshold bin is wanted: the remaining digits cannot change the outcome
+          if (in_bin == remaining) break;
+        }
+        thr_key = fixed;
+        thr_mask = fixed_mask;
+        take_equal = remaining;
+      }
+      IA_TRACE(7);
+
+      // Ordered compaction.  Selected = key above the threshold, plus the first
+      // `take_equal` keys equal to it in index order; one block scan of the packed
+      // counts (greater: low 16 bits, equal: high 16 bits) gives every output slot.
+      int n_written = 0;
+      const bool any = (p.mode == IA_SELECT_EPS) ? (n > 0) : (k_eff > 0);
+      if (any) {
+        const bool everything = (p.mode == IA_SELECT_TOPK) && (k_eff >= n);
+        int gt_seen = 0, eq_seen = 0;
         for (int base = 0; base < n; base += kThreads) {
           const int b = base + tid;
-          const uint32_t key = b < n ? order_key(sc[b]) : 0u;
-          const bool live = b < n && (key & fixed_mask) == fixed;
-          const uint32_t digit = (key >> shift) & 255u;
-          // Bin d lives at word (d & 7) * 32 + (d >> 3): the eight bins a lane scans below are then in
-          // eight different rows of 32 consecutive words, so the scan's loads are free of bank conflicts
-          // (a [256] array read as h[8 lane + i] is an 8-way conflict, paid by every warp in every pass).
-          // The leading digit (sign and high exponent bits) is shared by most keys: there the lanes of
-          // a warp that share a digit send one atomic together; the later digits are spread, and finding
-          // equal ones costs more than the few conflicts it would save.
-          if (pass == 0) {
-            const uint32_t peers = __match_any_sync(0xffffffffu, live ? digit : 0xffffffffu);
-            if (live && lane == __ffs(peers) - 1) atomicAdd(&h[(digit & 7u) * 32u + (digit >> 3)], __popc(peers));
-          } else if (live) {
-            atomicAdd(&h[(digit & 7u) * 32u + (digit >> 3)], 1);
+          const bool in = b < n;
+          const float v = in ? sc[b] : 0.f;
+          bool gt, eq = false;
+          if (p.mode == IA_SELECT_EPS) {
+            gt = in && (v > p.eps);
+          } else if (everything) {
+            gt = in;
+          } else {
+            const uint32_t key = order_key(v) & thr_mask;
+            gt = in && key > thr_key;
+            eq = in && key == thr_key;
           }
-        }
-#ifdef IA_SELECT_TRACE_FINE
-        if (pass < 2) IA_TRACE(9 + 3 * pass);
-#endif
-        __syncthreads();
-#ifdef IA_SELECT_TRACE_FINE
-        if (pass < 2) IA_TRACE(10 + 3 * pass);
-#endif
-        // lane owns bins [8 lane, 8 lane + 8); `above` = keys in the bins of higher lanes
-        int c[8], mine = 0;
+          // exclusive scan of (gt, eq) over the block
+          const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
+          const uint32_t below = (1u << lane) - 1u;
+          // two scratch rows used alternately: the row of this iteration is not rewritten before every
+          // warp has passed the barrier of the next one, so one barrier per iteration is enough
+          int* scan_row = scan_scratch + ((base / kThreads) & 1) * 16;
+          if (lane == 0) scan_row[warp] = __popc(bg) | (__popc(be) << 16);
+          __syncthreads();
+          int packed_before = 0, packed_total = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { c[i] = h[i * 32 + lane]; mine += c[i]; }
-        int incl = mine;  // inclusive suffix sum over lanes
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int v = __shfl_down_sync(0xffffffffu, incl, o);
-          if (lane + o < 32) incl += v;
-        }
-        const int above = incl - mine;
-        const bool owner = (above < remaining) && (incl >= remaining);
-        int digit = 0, left = 0, in_bin = 0;
-        if (owner) {
-          int acc = above;
-#pragma unroll
-          for (int i = 7; i >= 0; --i) {
-            if (acc + c[i] >= remaining) { digit = lane * 8 + i; in_bin = c[i]; break; }
-            acc += c[i];
+          for (int w = 0; w < kWarps; ++w) {
+            const int c = scan_row[w];
+            if (w < warp) packed_before += c;
+            packed_total += c;
           }
-          left = remaining - acc;
+          const int gt_before = gt_seen + (packed_before & 0xffff) + __popc(bg & below);
+          const int eq_before = eq_seen + (packed_before >> 16) + __popc(be & below);
+          const bool take = gt || (eq && eq_before < take_equal);
+          const int pos = gt_before + min(eq_before, take_equal);
+          if (take && pos >= 0 && pos < p.max_sel) emit(pos, b);
+          gt_seen += packed_total & 0xffff;
+          eq_seen += packed_total >> 16;
         }
-        const int src = max(__ffs(__ballot_sync(0xffffffffu, owner)) - 1, 0);  // exactly one owner lane
-        digit = __shfl_sync(0xffffffffu, digit, src);
-        remaining = __shfl_sync(0xffffffffu, left, src);
-        in_bin = __shfl_sync(0xffffffffu, in_bin, src);
-        fixed |= (uint32_t)digit << shift;
-        fixed_mask |= 255u << shift;
-#ifdef IA_SELECT_TRACE_FINE
-        if (pass < 2) IA_TRACE(11 + 3 * pass);
-#else
-        IA_TRACE(9 + pass);
-#endif
-        // every key of the threshold bin is wanted: the remaining digits cannot change the outcome
-        if (in_bin == remaining) break;
+        n_written = gt_seen + min(eq_seen, take_equal);
       }
-      thr_key = fixed;
-      thr_mask = fixed_mask;
-      take_equal = remaining;
-    }
-    IA_TRACE(7);
+      return max(min(n_written, p.max_sel), 0);
+    };
 
-    // Ordered compaction.  Selected = key above the threshold, plus the first
-    // `take_equal` keys equal to it in index order; one block scan of the packed
-    // counts (greater: low 16 bits, equal: high 16 bits) gives every output slot.
-    int n_written = 0;
-    const bool any = (p.mode == IA_SELECT_EPS) ? (n > 0) : (k_eff > 0);
-    if (any) {
-      const bool everything = (p.mode == IA_SELECT_TOPK) && (k_eff >= n);
-      int gt_seen = 0, eq_seen = 0;
-      for (int base = 0; base < n; base += kThreads) {
-        const int b = base + tid;
-        const bool in = b < n;
-        const float v = in ? sc[b] : 0.f;
-        bool gt, eq = false;
-        if (p.mode == IA_SELECT_EPS) {
-          gt = in && (v > p.eps);
-        } else if (everything) {
-          gt = in;
-        } else {
-          const uint32_t key = order_key(v) & thr_mask;
-          gt = in && key > thr_key;
-          eq = in && key == thr_key;
+    int32_t* out_idx = p.sel_idx + (int64_t)pair * p.max_sel;
+    int n_written;
+    if (!xch_on) {
+      n_written = route(score_s, nb, [&](int slot, int b) {
+        out_idx[slot] = b;
+        if constexpr (FUSE) {
+          // the picked blocks stay on chip, in the shared memory of every CTA that will attend over them
+          if (C == 1) sel_list[slot] = b;
+          else
+            for (int r = 0; r < C; ++r) st_cluster_s32(map_to_rank(sel_list + slot, (uint32_t)r), b);
         }
-        // exclusive scan of (gt, eq) over the block
-        const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
-        const uint32_t below = (1u << lane) - 1u;
-        // two scratch rows used alternately: the row of this iteration is not rewritten before every
-        // warp has passed the barrier of the next one, so one barrier per iteration is enough
-        int* scan_row = scan_scratch + ((base / kThreads) & 1) * 16;
-        if (lane == 0) scan_row[warp] = __popc(bg) | (__popc(be) << 16);
-        __syncthreads();
-        int packed_before = 0, packed_total = 0;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-          const int c = scan_row[w];
-          if (w < warp) packed_before += c;
-          packed_total += c;
+      });
+    } else {
+      // Split-KV: the k best of this GPU's blocks are candidates - (score, block index) in block order -
+      // and go to every GPU; the k best of all candidates, taken in rank order (= block order, the
+      // ranks own ascending ranges), are the selection, identical on every GPU.
+      const int W = p.xch.n_ranks, me = p.xch.my_rank, kc = p.max_sel;
+      const int64_t slot0 = ((int64_t)xpar * p.n_pairs + pair) * W;
+      const int n_mine = route(score_s + r_lo, max(r_hi - r_lo, 0), [&](int slot, int j) {
+        const float2 c = make_float2(score_s[r_lo + j], __int_as_float(r_lo + j));
+        for (int w = 0; w < W; ++w) reinterpret_cast<float2*>(p.xch.cand[w])[(slot0 + me) * (kc + 1) + slot] = c;
+      });
+      if (tid == 0)
+        for (int w = 0; w < W; ++w)
+          reinterpret_cast<float2*>(p.xch.cand[w])[(slot0 + me) * (kc + 1) + kc] = make_float2(__int_as_float(n_mine), 0.f);
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence_system();
+        for (int w = 0; w < W; ++w) {
+          volatile int32_t* f = p.xch.flags[w] + ((int64_t)(xpar * 2 + 1) * p.n_pairs + pair) * W + me;
+          *f = xstep;
         }
-        const int gt_before = gt_seen + (packed_before & 0xffff) + __popc(bg & below);
-        const int eq_before = eq_seen + (packed_before >> 16) + __popc(be & below);
-        const bool take = gt || (eq && eq_before < take_equal);
-        const int pos = gt_before + min(eq_before, take_equal);
-        if (take && pos >= 0 && pos < p.max_sel) emit(pos, b);
-        gt_seen += packed_total & 0xffff;
-        eq_seen += packed_total >> 16;
       }
-      n_written = gt_seen + min(eq_seen, take_equal);
+      if (tid < W && !wait_flag(p.xch.flags[me] + ((int64_t)(xpar * 2 + 1) * p.n_pairs + pair) * W + tid, xstep))
+        atomicOr(&g_device_status, DEV_STATUS_PEER_WAIT_TIMEOUT);
+      __syncthreads();
+      const float2* mine = reinterpret_cast<const float2*>(p.xch.cand[me]);
+      int n_all = 0;
+      for (int w = 0; w < W; ++w) {  // rank order; every thread walks the W counts
+        const int n_w = min(max(__float_as_int(__ldcg(&mine[(slot0 + w) * (kc + 1) + kc]).x), 0), kc);
+        for (int i = tid; i < n_w; i += kThreads) {
+          const float2 c = __ldcg(&mine[(slot0 + w) * (kc + 1) + i]);
+          cand_s[n_all + i] = c.x;
+          candb_s[n_all + i] = __float_as_int(c.y);
+        }
+        n_all += n_w;
+      }
+      __syncthreads();
+      n_written = route(cand_s, n_all, [&](int slot, int j) { out_idx[slot] = candb_s[j]; });
     }
-    return max(min(n_written, p.max_sel), 0);
-  };
-
-  int32_t* out_idx = p.sel_idx + (int64_t)pair * p.max_sel;
-  int n_written;
-  // one-kernel step: the picked blocks also stay in shared memory (the value norms are not needed any more)
-  int* sel_list = reinterpret_cast<int*>(vn_s);
-  if (!xch_on) {
-    n_written = route(score_s, nb, [&](int slot, int b) {
-      out_idx[slot] = b;
-      if constexpr (FUSE) sel_list[slot] = b;
-    });
-  } else {
-    // Split-KV: the k best of this GPU's blocks are candidates - (score, block index) in block order -
-    // and go to every GPU; the k best of all candidates, taken in rank order (= block order, the
-    // ranks own ascending ranges), are the selection, identical on every GPU.
-    const int W = p.xch.n_ranks, me = p.xch.my_rank, kc = p.max_sel;
-    const int64_t slot0 = ((int64_t)xpar * p.n_pairs + pair) * W;
-    const int n_mine = route(score_s + r_lo, max(r_hi - r_lo, 0), [&](int slot, int j) {
-      const float2 c = make_float2(score_s[r_lo + j], __int_as_float(r_lo + j));
-      for (int w = 0; w < W; ++w) reinterpret_cast<float2*>(p.xch.cand[w])[(slot0 + me) * (kc + 1) + slot] = c;
-    });
-    if (tid == 0)
-      for (int w = 0; w < W; ++w)
-        reinterpret_cast<float2*>(p.xch.cand[w])[(slot0 + me) * (kc + 1) + kc] = make_float2(__int_as_float(n_mine), 0.f);
-    __syncthreads();
+    IA_TRACE(8);
+    count = n_written;
+    for (int i = count + tid; i < p.max_sel; i += kThreads) out_idx[i] = -1;
     if (tid == 0) {
-      __threadfence_system();
-      for (int w = 0; w < W; ++w) {
-        volatile int32_t* f = p.xch.flags[w] + ((int64_t)(xpar * 2 + 1) * p.n_pairs + pair) * W + me;
-        *f = xstep;
-      }
+      p.sel_count[pair] = count;
+      if (p.split_counters != nullptr) p.split_counters[pair] = 0;
     }
-    if (tid < W && !wait_flag(p.xch.flags[me] + ((int64_t)(xpar * 2 + 1) * p.n_pairs + pair) * W + tid, xstep))
-      atomicOr(&g_device_status, DEV_STATUS_PEER_WAIT_TIMEOUT);
-    __syncthreads();
-    const float2* mine = reinterpret_cast<const float2*>(p.xch.cand[me]);
-    int n_all = 0;
-    for (int w = 0; w < W; ++w) {  // rank order; every thread walks the W counts
-      const int n_w = min(max(__float_as_int(__ldcg(&mine[(slot0 + w) * (kc + 1) + kc]).x), 0), kc);
-      for (int i = tid; i < n_w; i += kThreads) {
-        const float2 c = __ldcg(&mine[(slot0 + w) * (kc + 1) + i]);
-        cand_s[n_all + i] = c.x;
-        candb_s[n_all + i] = __float_as_int(c.y);
-      }
-      n_all += n_w;
-    }
-    __syncthreads();
-    n_written = route(cand_s, n_all, [&](int slot, int j) { out_idx[slot] = candb_s[j]; });
+    leave();
   }
-  IA_TRACE(8);
-  const int count = n_written;
-  for (int i = count + tid; i < p.max_sel; i += kThreads) out_idx[i] = -1;
-  if (tid == 0) {
-    p.sel_count[pair] = count;
-    if (p.split_counters != nullptr) p.split_counters[pair] = 0;
-  }
-  leave();
   if constexpr (FUSE) {
+    if (C > 1) {
+      // The cluster shares the attention too: rank 0 has stored what it picked into every rank's shared
+      // memory (above) and adds the count; past the barrier every rank takes every C-th page.
+      int* count_slot = scan_scratch + 31;  // the compaction's scratch rows end at [28]
+      if (crank == 0 && tid == 0)
+        for (int r = 0; r < C; ++r) st_cluster_s32(map_to_rank(count_slot, (uint32_t)r), count);
+      cluster_sync_all();
+      count = *count_slot;
+    }
     // The histograms are idle: their 3 KB hold the page ring's barriers and descriptors.
     static_assert(P::hist >= 32 * 8, "the page ring's barriers live in the histogram area");
-    // (z, delta) per (row, block) are dead too: the resolved page numbers go there
-    attend_selected_pages<D, G, kConsumerWarps>(p, pair, seq, prefix, sel_list, count, q_s,
-                                                reinterpret_cast<int*>(z_s), 2 * G * nbl, stage_base,
+    // delta per (row, block) is dead too: the resolved page numbers go there; the scores' array holds the
+    // bitmap of the picked blocks (hybrid); z stays - the representatives' logits
+    attend_selected_pages<D, G, kAttendWarps<NG>>(p, pair, seq, prefix, crank, C, sel_list, count, q_s, z_s, nbl,
+                                                b_lo, b_hi, reinterpret_cast<uint32_t*>(score_s), nb_cap,
+                                                reinterpret_cast<int*>(d_s), G * nbl, stage_base,
                                                 reinterpret_cast<unsigned char*>(hist), IA_TRACE_T0);
   }
 }
@@ -1537,14 +1673,15 @@ static EncodeTiledFn tensor_map_encoder() {
 // a [rows, D] row-major matrix cut into boxes of 128 bytes x 32 rows with the 128-byte swizzle.
 // The descriptor depends only on (base, rows, D, element type); a decode loop asks for the same few
 // every step, so the last ones encoded on this thread are kept.
-struct CachedMap { const void* base; int64_t rows; int D; bool is_bf16; CUtensorMap map; };
-static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t rows, int D) {
+struct CachedMap { const void* base; int64_t rows; int D; bool is_bf16; int box_rows; CUtensorMap map; };
+static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t rows, int D,
+                       int box_rows = kTileBlocks) {
   constexpr int kSlots = 16;
   static thread_local CachedMap cache[kSlots];
   static thread_local int next_slot = 0;
   for (int i = 0; i < kSlots; ++i)
     if (cache[i].base == base && cache[i].rows == rows && cache[i].D == D && cache[i].is_bf16 == is_bf16 &&
-        base != nullptr) {
+        cache[i].box_rows == box_rows && base != nullptr) {
       *tm = cache[i].map;
       return IA_OK;
     }
@@ -1553,14 +1690,14 @@ static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t 
   const int esz = is_bf16 ? 2 : 4;
   const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)D * esz};
-  const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)kTileBlocks};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(tm, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(IA_ERR_LAUNCH, "select: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  cache[next_slot] = CachedMap{base, rows, D, is_bf16, *tm};
+  cache[next_slot] = CachedMap{base, rows, D, is_bf16, box_rows, *tm};
   next_slot = (next_slot + 1) % kSlots;
   return IA_OK;
 }
@@ -1599,6 +1736,7 @@ static int encode_pool(CUtensorMap* tm, const void* base, int D, int heads, int 
 struct AttendRequest {
   SelectAttend* req;
   const ia_geom* geom;
+  const void* vbar;
 };
 
 template <typename Kern>
@@ -1621,21 +1759,31 @@ static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pai
     // One wave only: with more CTAs than resident slots a CTA would hold its SM through the serial
     // phases of the selection while the attention of other pairs waits for a slot (measured: the ragged
     // 70B batch, 512 pairs, 293 us fused against 247 us as two kernels).
-    if (ar.req == nullptr || p.cluster != 1 || p.xch.n_ranks > 0 || n_pairs > resident_ctas) return false;
+    if (ar.req == nullptr || p.xch.n_ranks > 0 || n_pairs * p.cluster > resident_ctas) return false;
     static const bool off = [] {
       const char* v = getenv("INTERATTN_B200_FUSED");
       return v != nullptr && v[0] == '0';
     }();
     const ia_geom& g = *ar.geom;
     constexpr size_t kStage = 2 * 16 * D * 2;
+    // at the end the start of the ring holds the warps' partial results, and the end of rank 0's ring
+    // (kept free of pages) the shares of the CTAs of a cluster
+    constexpr size_t kMerge = (size_t)kAttendWarps<NG> * (8 * (D + 4) + 16) * 4;
+    const size_t shares = p.cluster > 1 ? (size_t)p.cluster * (G * D + 2 * G) * 4 : 0;
     if (off || g.page_size != 16 || g.block_size % 16 != 0 || g.n_pool_pages <= 0 ||
-        ring_bytes < (size_t)Shape<NG>::consumer_warps * kStage)
+        ring_bytes < (size_t)kAttendWarps<NG> * kStage + shares || ring_bytes < kMerge + shares)
       return false;
     if (encode_pool(&p.att.tm_k, ar.req->k_pool, D, g.n_kv_heads, g.n_pool_pages, g.pool_head_stride,
                     g.pool_page_stride) != IA_OK ||
         encode_pool(&p.att.tm_v, ar.req->v_pool, D, g.n_kv_heads, g.n_pool_pages, g.pool_head_stride,
                     g.pool_page_stride) != IA_OK)
       return false;
+    p.att.hybrid = ar.req->hybrid;
+    if (ar.req->hybrid) {
+      const int64_t rows = (int64_t)n_pairs * p.max_blocks;
+      if (ar.vbar == nullptr || encode_rows(&p.att.tm_vbar, ar.vbar, true, rows, D, 16) != IA_OK) return false;
+      if (ar.req->z_scratch) p.aux.z = nullptr;  // the logits stay in shared memory
+    }
     p.att.block_table = ar.req->block_table;
     p.att.seq_lens = ar.req->seq_lens;
     p.att.out = ar.req->out;
@@ -1776,7 +1924,7 @@ int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_le
                   const ia_select_exchange* exchange, int block_lo, int block_hi, SelectAttend* attend) {
   SelectParams p{};
   if (attend != nullptr) attend->used = 0;
-  const AttendRequest ar{attend, &g};
+  const AttendRequest ar{attend, &g, s.v_bar};
   if (exchange != nullptr) {
     p.xch = *exchange;
     p.block_lo = block_lo;

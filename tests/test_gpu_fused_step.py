@@ -1,9 +1,9 @@
 """GPU parity of the one-kernel layer step (``condition_block_select_attend_kernel``): the CTA that
 picked the blocks of a (sequence, kv head) attends over their pages and the suffix itself.
 
-The launch shape decides whether a step fuses (one CTA per pair); the small cases here pin that shape
-through the environment (``INTERATTN_B200_SELECT_CLUSTER=1``, wide and narrow CTAs) and assert that the
-fused kernel ran.  Bars: the selection identical to the stand-alone selection kernel; the output within the
+The launch shape decides whether a step fuses (the whole grid resident at once); the small cases here pin
+the shape through the environment (``INTERATTN_B200_SELECT_CLUSTER``, wide and narrow CTAs) and assert that
+the fused kernel ran.  Bars: the selection identical to the stand-alone selection kernel; the output within the
 bf16 tolerance (2e-2 abs / 1e-2 rel) of the oracle's attention over exactly those blocks.
 """
 
@@ -34,7 +34,7 @@ CASES = [
 ]
 
 
-def _check_against_oracle(cfg, case, summ, out, idx, cnt):
+def _check_against_oracle(cfg, case, summ, out, idx, cnt, rep_mode="sparse_only", z=None):
     out = out.float().cpu()
     idx, cnt = idx.cpu(), cnt.cpu()
     for b in range(cfg.batch):
@@ -45,31 +45,42 @@ def _check_against_oracle(cfg, case, summ, out, idx, cnt):
         for h in range(cfg.n_kv_heads):
             mask[h, idx[b, h, :int(cnt[b, h])].long()] = True
         qg = case["q"][b].reshape(cfg.n_kv_heads, cfg.group_size, cfg.head_dim).float()
-        want = orc.decode_attention(qg, k, v, plen, cfg.block_size, mask, rep_mode="sparse_only")
+        extra = {}
+        if rep_mode == "hybrid":
+            extra = dict(z=z[b, :, :osum.n_blocks].cpu().reshape(cfg.n_kv_heads, cfg.group_size, -1), v_bar=osum.v_bar)
+        want = orc.decode_attention(qg, k, v, plen, cfg.block_size, mask, rep_mode=rep_mode, **extra)
         got = out[b].reshape(cfg.n_kv_heads, cfg.group_size, cfg.head_dim)
         torch.testing.assert_close(got, want, **TOL)
 
 
-@pytest.mark.parametrize("shape", ["wide", "narrow"])
+@pytest.mark.parametrize("rep_mode", ["sparse_only", "hybrid"])
+@pytest.mark.parametrize("shape,cluster", [("wide", 1), ("narrow", 1), ("wide", 2), ("wide", 4), ("narrow", 2)])
 @pytest.mark.parametrize("cfg", CASES, ids=lambda c: c.name)
-def test_fused_step_matches_selection_and_oracle(cfg, shape, monkeypatch):
+def test_fused_step_matches_selection_and_oracle(cfg, shape, cluster, rep_mode, monkeypatch):
+    """cluster > 1: the CTAs that share a (sequence, kv head) also share its pages and rank 0 merges them.
+    hybrid: every block that was not picked attends through its representative, straight from the logits the
+    selection left in shared memory."""
     ops = _ops()
-    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    resident = torch.cuda.get_device_properties(0).multi_processor_count * (2 if shape == "narrow" else 1)
+    if cfg.batch * cfg.n_kv_heads * cluster > resident:
+        pytest.skip("more CTAs than resident slots: this batch keeps the two kernels")
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", str(cluster))
     monkeypatch.setenv("INTERATTN_B200_SELECT_SHAPE", shape)
     case = make_case(cfg, spare_pages=3)
     q, kv = to_device(case)
     summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
-    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k)
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode)
     for _ in range(2):  # twice: the ring's barriers are initialised per launch
         out = step.step(q).clone()
         assert ops.last_decode_fused(), "the pinned shape must take the one-kernel form"
-    idx, cnt, _ = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k)
+    idx, cnt, aux = ops.select_blocks(q, summ, kv.prefix_lens, top_k=cfg.top_k, want=("z",))
     torch.cuda.synchronize()
     assert ops.device_status() == 0
     assert torch.equal(step.sel_idx[:, :, :idx.shape[2]], idx) and torch.equal(step.sel_count, cnt)
-    _check_against_oracle(cfg, case, summ, out, idx, cnt)
-    # the two-kernel form on the same inputs (hybrid steps never fuse; here: the three public calls)
-    o, lse = ops.sparse_decode(q, kv, idx, cnt, block_size=cfg.block_size, max_blocks=summ.max_blocks, n_splits=2)
+    _check_against_oracle(cfg, case, summ, out, idx, cnt, rep_mode, aux["z"])
+    # the two-kernel form on the same inputs, through the three public calls (they never fuse)
+    o, lse = ops.sparse_decode(q, kv, idx, cnt, block_size=cfg.block_size, max_blocks=summ.max_blocks, n_splits=2,
+                               rep_mode=rep_mode, summ=summ, z=aux["z"])
     two = ops.finalize(o, lse, q.dtype)
     torch.testing.assert_close(out.float(), two.float(), **TOL)
 
@@ -132,6 +143,32 @@ def test_fused_step_skips_a_table_entry_outside_the_pool(monkeypatch):
     assert ops.last_decode_fused()
     assert ops.device_status() & 8, "IA_DEV_STATUS_BAD_INDEX"  # reading the word clears it
     assert torch.isfinite(out.float()).all() and torch.isfinite(good.float()).all()
+
+
+@pytest.mark.parametrize("rep_mode", ["sparse_only", "hybrid"])
+def test_fused_step_ignores_what_lies_in_dead_rows(rep_mode, monkeypatch):
+    """Token slots past a sequence's end (inside its last page) and summary rows past its last block hold
+    NaN: the kernel masks their logits and must also keep them out of the P.V product (0 x NaN)."""
+    ops = _ops()
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    cfg = DecodeConfig("dead_rows", "bfloat16", 2, 8, 2, 128, 16, 64, 3, (1000, 333), (5, 20), seed=21)
+    case = make_case(cfg, spare_pages=2)
+    q, kv = to_device(case)
+    nb = max_blocks_of(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=nb + 3)
+    clean = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode).step(q).clone()
+    assert ops.last_decode_fused()
+    for b in range(cfg.batch):
+        slen, plen = int(case["seq_lens"][b]), int(case["prefix_lens"][b])
+        page = int(case["block_table"][b, (slen - 1) // 16])
+        kv.k_pool[page, :, slen % 16:] = float("nan")
+        kv.v_pool[page, :, slen % 16:] = float("nan")
+        n_blocks = (plen + 63) // 64
+        summ.v_bar[b, :, n_blocks:] = float("nan")
+    out = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode).step(q).clone()
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, clean)
 
 
 def test_fused_step_replays_from_a_cuda_graph(monkeypatch):
