@@ -304,11 +304,13 @@ int ia_suggest_splits(const ia_geom* geom, int expected_blocks);
  * Every pair is cut into n_splits parts (ia_suggest_splits).  INTERATTN_B200_DECODE_GRID=flat in the
  * environment switches bf16 pools to a fixed grid of two CTAs per SM, each taking an equal share of
  * all pairs' pages whatever n_splits says (slower on B200 as measured; kept for comparison).
- * One launch instead of two where it applies - IA_REP_SPARSE_ONLY, bf16 pools of 16-token pages with
- * head_dim 128 and a known size (geom->n_pool_pages > 0), at most eight query rows per kv head, and a
- * batch that gives every (sequence, kv head) one CTA of the selection kernel: that CTA then attends
- * over the pages of the blocks it has just picked, which are still in its shared memory, and writes
- * the output rows (condition_block_select_attend_kernel; n_splits is not used).
+ * One launch instead of two where it applies - bf16 pools of 16-token pages with head_dim 128 and a
+ * known size (geom->n_pool_pages > 0), at most eight query rows per kv head, the range bound, and a
+ * batch whose selection grid is resident at once ((sequence, kv head) pairs x cluster size <= SMs x
+ * CTAs per SM): the CTA (or cluster) that picked a pair's blocks then attends over their pages, which
+ * it still has in shared memory - in hybrid mode also over the representatives, whose logits never
+ * leave shared memory - and writes the output rows (condition_block_select_attend_kernel; n_splits
+ * is not used).
  * INTERATTN_B200_FUSED=0 in the environment keeps the two launches.
  * workspace: ia_workspace_bytes() bytes, 256-byte aligned.  out [batch, rows, head_dim] in
  * geom->dtype, 16-byte aligned.  sel_idx/sel_count may be null (the selection then lives in the
