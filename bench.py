@@ -348,8 +348,18 @@ def kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mod
 
 
 def variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summaries, n_splits, K, R, workload,
-                   bound="range"):
-    """One sub-record: the layer-step in another mode / summary layout, with its own roofline."""
+                   bound="range", fused=True):
+    """One sub-record: the layer-step in another mode / summary layout / launch form, with its own roofline."""
+    from interattn_b200 import ops
+    before = ops.set_fused_step(fused)
+    try:
+        return _variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summaries, n_splits, K, R,
+                               workload, bound)
+    finally:
+        ops.set_fused_step(before)
+
+
+def _variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summaries, n_splits, K, R, workload, bound):
     from interattn_b200 import ops
     steppers = [ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k, rep_mode=rep_mode, n_splits=n_splits,
                                     bound=bound)
@@ -536,6 +546,11 @@ def layer_step_record(args, workload, torch, dist, regions, world, rank, local_r
         # the reference's own mode (representatives of the unselected blocks) and the bf16 k_bar layout
         Rv = max(5, R // 2)
         summ_f32 = [s for _, s in layers]
+        if fused:
+            # the same step as selection kernel + attention kernel: what the one-kernel form is measured against,
+            # and the per-kernel rooflines of the form that runs where the fused one does not apply
+            line["two_kernel"] = variant_record(torch, regions, cfg, layers, qs, args.rep_mode, args.kbar_bf16,
+                                                summ_f32, args.n_splits or None, K, Rv, workload, fused=False)
         if args.rep_mode != "hybrid":
             line["hybrid"] = variant_record(torch, regions, cfg, layers, qs, "hybrid", args.kbar_bf16, summ_f32,
                                             n_splits, K, Rv, workload)
@@ -576,7 +591,9 @@ def llama_decode_line(steps):
         g = torch.Generator(device="cuda").manual_seed(0)
         ids = torch.randint(0, model.config.vocab_size, (32, 8192), generator=g, device="cuda")
         _, st = ld.generate_batched(model, ids, int(steps), cuda_graph=True, fused_step=True)
+        from interattn_b200 import ops
         return {"metric": "llama3_8b_decode_tokens_per_s", "value": st["tokens_per_s"], "unit": "tok/s",
+                "attention_launches_per_layer": 1 if ops.last_decode_fused() else 2,
                 "ms_per_decode_step": 1e3 * st["decode_s"] / max(st["decode_steps_timed"], 1),
                 "decode_steps_timed": st["decode_steps_timed"], "prefill_s": st["prefill_s"],
                 "config": {"layers": 32, "batch": 32, "prompt": 8192, "new_tokens": int(steps), "block": 64,

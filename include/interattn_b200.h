@@ -326,6 +326,11 @@ int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool,
  * No reference counterpart: a reporting aid for benchmarks, which attribute time and bytes per kernel. */
 int ia_last_decode_fused(void);
 
+/* Process-wide switch of the one-kernel form (1 = allowed where it applies, the default unless
+ * INTERATTN_B200_FUSED=0 is in the environment; 0 = always two launches).  Returns the previous setting.
+ * No reference counterpart: for A/B measurements and for profiling the two kernels separately. */
+int ia_set_fused_step(int enabled);
+
 /* ia_decode_attention that also records four caller-created CUDA events
  * (cudaEvent_t, timing enabled) on the stream: events[0] before the selection
  * kernel, [1] between selection and attention, [2] and [3] after the

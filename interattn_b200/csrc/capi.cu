@@ -1,6 +1,7 @@
 // extern "C" surface of libinterattn_b200.so: argument checks, status
 // plumbing and the one-call layer-step.  Declarations and the reference
 // interfaces they replace: include/interattn_b200.h.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -129,6 +130,21 @@ static Workspace carve(const ia_geom& g, int max_sel, int n_splits, int rep_mode
 }  // namespace ia
 
 using namespace ia;
+
+// -1: not set by the caller, the environment decides (INTERATTN_B200_FUSED=0 turns the one-kernel step off)
+static std::atomic<int> g_fused_step{-1};
+
+namespace ia {
+bool fused_step_enabled() {
+  const int v = g_fused_step.load(std::memory_order_relaxed);
+  if (v >= 0) return v != 0;
+  static const bool env_on = [] {
+    const char* e = getenv("INTERATTN_B200_FUSED");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return env_on;
+}
+}  // namespace ia
 
 extern "C" {
 
@@ -435,6 +451,12 @@ int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool, c
 }
 
 int ia_last_decode_fused(void) { return t_last_decode_fused; }
+
+int ia_set_fused_step(int enabled) {
+  const int before = ia::fused_step_enabled() ? 1 : 0;
+  g_fused_step.store(enabled ? 1 : 0, std::memory_order_relaxed);
+  return before;
+}
 
 int ia_decode_attention_timed(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
                               const int32_t* prefix_lens, const int32_t* seq_lens, const ia_summaries* summaries,

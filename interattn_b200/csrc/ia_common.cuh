@@ -121,6 +121,8 @@ __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 bool overlapped_launch_enabled();
+// the one-kernel layer step may be used (INTERATTN_B200_FUSED, ia_set_fused_step)
+bool fused_step_enabled();
 template <typename Kern, typename Params>
 inline cudaError_t launch_overlapped(Kern kern, unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
                                      const Params& params, int cluster = 1) {

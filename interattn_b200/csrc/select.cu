@@ -147,6 +147,7 @@ struct SelectParams {
     CUtensorMap tm_k, tm_v;
     CUtensorMap tm_vbar;  // hybrid: the mean values [pairs * max_blocks, head_dim], box = 128 bytes x 16 blocks
     int hybrid;           // IA_REP_HYBRID: every block that was not picked attends through (z, v_bar)
+    int heads_outer;      // the pools' tensor maps are [kv head, page, token, head_dim] (head stride > page stride)
     const int32_t* block_table;
     const int32_t* seq_lens;
     void* out;
@@ -624,11 +625,12 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
 #pragma unroll
           for (int j = 0; j < kBoxes; ++j) tma_load_2d(st + kTile + j * kBox, &p.att.tm_vbar, j * 64, y, &full_b[stage]);
         } else if (page >= 0 && hi > lo) {
+          const int c_inner = p.att.heads_outer ? page : head, c_outer = p.att.heads_outer ? head : page;
           mbar_arrive_expect_tx(&full_b[stage], (uint32_t)kStage);
 #pragma unroll
           for (int j = 0; j < kBoxes; ++j) {
-            tma_load_4d(st + j * kBox, &p.att.tm_k, j * 64, 0, head, page, &full_b[stage]);
-            tma_load_4d(st + kTile + j * kBox, &p.att.tm_v, j * 64, 0, head, page, &full_b[stage]);
+            tma_load_4d(st + j * kBox, &p.att.tm_k, j * 64, 0, c_inner, c_outer, &full_b[stage]);
+            tma_load_4d(st + kTile + j * kBox, &p.att.tm_v, j * 64, 0, c_inner, c_outer, &full_b[stage]);
           }
         } else {
           mbar_arrive(&full_b[stage]);  // nothing to fetch: the phase completes at once
@@ -1704,10 +1706,13 @@ static int encode_rows(CUtensorMap* tm, const void* base, bool is_bf16, int64_t 
 
 // A bf16 KV pool as the 4-D tensor [page, kv head, token, head_dim] with its own page and head strides
 // (elements); box = 64 elements x 16 tokens of one (page, kv head), 128-byte swizzle.  Pages past
-// n_pages are out of the tensor: the TMA unit fills them with zeros instead of reading.
+// n_pages are out of the tensor: the TMA unit fills them with zeros instead of reading.  The two outer
+// dimensions are ordered by stride (a cache laid out [batch, kv head, token, head_dim] and addressed in
+// place as pages has the larger stride on the head): *heads_outer tells the kernel which coordinate is which.
 struct CachedPool { const void* base; int D, heads, pages; int64_t hs, ps; CUtensorMap map; };
 static int encode_pool(CUtensorMap* tm, const void* base, int D, int heads, int pages, int64_t head_stride,
-                       int64_t page_stride) {
+                       int64_t page_stride, int* heads_outer) {
+  *heads_outer = head_stride > page_stride;
   constexpr int kSlots = 16;
   static thread_local CachedPool cache[kSlots];
   static thread_local int next_slot = 0;
@@ -1719,8 +1724,12 @@ static int encode_pool(CUtensorMap* tm, const void* base, int D, int heads, int 
     }
   EncodeTiledFn enc = tensor_map_encoder();
   if (enc == nullptr) return fail(IA_ERR_LAUNCH, "select: cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint64_t dims[4] = {(cuuint64_t)D, 16, (cuuint64_t)heads, (cuuint64_t)pages};
-  const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)head_stride * 2, (cuuint64_t)page_stride * 2};
+  cuuint64_t dims[4] = {(cuuint64_t)D, 16, (cuuint64_t)heads, (cuuint64_t)pages};
+  cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)head_stride * 2, (cuuint64_t)page_stride * 2};
+  if (*heads_outer) {
+    dims[2] = (cuuint64_t)pages; dims[3] = (cuuint64_t)heads;
+    strides[1] = (cuuint64_t)page_stride * 2; strides[2] = (cuuint64_t)head_stride * 2;
+  }
   const cuuint32_t box[4] = {64, 16, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
@@ -1760,10 +1769,7 @@ static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pai
     // phases of the selection while the attention of other pairs waits for a slot (measured: the ragged
     // 70B batch, 512 pairs, 293 us fused against 247 us as two kernels).
     if (ar.req == nullptr || p.xch.n_ranks > 0 || n_pairs * p.cluster > resident_ctas) return false;
-    static const bool off = [] {
-      const char* v = getenv("INTERATTN_B200_FUSED");
-      return v != nullptr && v[0] == '0';
-    }();
+    const bool off = !fused_step_enabled();
     const ia_geom& g = *ar.geom;
     constexpr size_t kStage = 2 * 16 * D * 2;
     // at the end the start of the ring holds the warps' partial results, and the end of rank 0's ring
@@ -1774,9 +1780,9 @@ static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pai
         ring_bytes < (size_t)kAttendWarps<NG> * kStage + shares || ring_bytes < kMerge + shares)
       return false;
     if (encode_pool(&p.att.tm_k, ar.req->k_pool, D, g.n_kv_heads, g.n_pool_pages, g.pool_head_stride,
-                    g.pool_page_stride) != IA_OK ||
+                    g.pool_page_stride, &p.att.heads_outer) != IA_OK ||
         encode_pool(&p.att.tm_v, ar.req->v_pool, D, g.n_kv_heads, g.n_pool_pages, g.pool_head_stride,
-                    g.pool_page_stride) != IA_OK)
+                    g.pool_page_stride, &p.att.heads_outer) != IA_OK)
       return false;
     p.att.hybrid = ar.req->hybrid;
     if (ar.req->hybrid) {

@@ -481,6 +481,12 @@ def last_decode_fused() -> bool:
     return bool(_lib.load().ia_last_decode_fused())
 
 
+def set_fused_step(enabled: bool) -> bool:
+    """Allow (default) or forbid the one-kernel form of the layer step, process-wide; returns the previous
+    setting.  For A/B measurements: the two-kernel form is what runs anyway where the fused one does not apply."""
+    return bool(_lib.load().ia_set_fused_step(1 if enabled else 0))
+
+
 def device_status() -> int:
     """Read and clear the device status word, an OR of the ``_lib.IA_DEV_STATUS_*`` masks: a bounded
     wait inside a kernel ran out (SELECT_WAIT, GEMM_WAIT, PEER_WAIT: that result is invalid), or a

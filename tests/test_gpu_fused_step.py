@@ -85,6 +85,29 @@ def test_fused_step_matches_selection_and_oracle(cfg, shape, cluster, rep_mode, 
     torch.testing.assert_close(out.float(), two.float(), **TOL)
 
 
+def test_switch_between_the_one_kernel_and_the_two_kernel_form(monkeypatch):
+    ops = _ops()
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    cfg = CASES[0]
+    case = make_case(cfg, spare_pages=3)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k)
+    one = step.step(q).clone()
+    assert ops.last_decode_fused()
+    before = ops.set_fused_step(False)
+    try:
+        two = step.step(q).clone()
+        assert not ops.last_decode_fused()
+    finally:
+        assert ops.set_fused_step(before) is False
+    again = step.step(q).clone()
+    torch.cuda.synchronize()
+    assert ops.last_decode_fused() and ops.device_status() == 0
+    assert torch.equal(one, again)
+    torch.testing.assert_close(one.float(), two.float(), **TOL)
+
+
 def test_fused_step_with_epsilon_rule(monkeypatch):
     ops = _ops()
     monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
@@ -169,6 +192,34 @@ def test_fused_step_ignores_what_lies_in_dead_rows(rep_mode, monkeypatch):
     torch.cuda.synchronize()
     assert torch.isfinite(out.float()).all()
     assert torch.equal(out, clean)
+
+
+def test_fused_step_over_a_static_cache_addressed_in_place(monkeypatch):
+    """A [batch, kv head, token, head_dim] cache viewed as pages (head stride > page stride): the pools' tensor
+    maps put the head outermost; same output as the two-kernel form over the same view."""
+    ops = _ops()
+    from interattn_b200.llama_decode import cache_as_pool
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    b, hkv, t, d, g = 3, 2, 1024, 128, 4
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    key = torch.randn((b, hkv, t, d), device="cuda", generator=gen).to(torch.bfloat16)
+    value = torch.randn((b, hkv, t, d), device="cuda", generator=gen).to(torch.bfloat16)
+    k_pool, v_pool, table = cache_as_pool(key, value)
+    prefix = torch.tensor([900, 640, 77], dtype=torch.int32, device="cuda")
+    seq = prefix + torch.tensor([5, 100, 16], dtype=torch.int32, device="cuda")
+    kv = ops.PagedKV(k_pool, v_pool, table, prefix, seq)
+    summ = ops.build_summaries(kv, 64, max_blocks=15)
+    q = torch.randn((b, hkv * g, d), device="cuda", generator=gen).to(torch.bfloat16)
+    step = ops.DecodeAttention(kv, summ, hkv * g, top_k=4)
+    out = step.step(q).clone()
+    assert ops.last_decode_fused(), "the strided view must be expressible as a tensor map"
+    idx, cnt, _ = ops.select_blocks(q, summ, prefix, top_k=4)
+    assert torch.equal(step.sel_idx[:, :, :idx.shape[2]], idx) and torch.equal(step.sel_count, cnt)
+    o, lse = ops.sparse_decode(q, kv, idx, cnt, block_size=64, max_blocks=15, n_splits=2)
+    two = ops.finalize(o, lse, q.dtype)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    torch.testing.assert_close(out.float(), two.float(), **TOL)
 
 
 def test_fused_step_replays_from_a_cuda_graph(monkeypatch):
