@@ -134,6 +134,7 @@ struct SelectParams {
   int* split_counters;  // may be null
   ia_select_aux aux;
   int n_stages, nb_cap;
+  int longest_first;  // CTAs take the sequences in order of descending prefix length (grids of several waves)
   int cluster;     // CTAs per (sequence, kv head): a thread-block cluster splits the blocks
   int nb_loc_cap;  // row stride of the per-CTA (row, block) arrays
   // Split-KV across GPUs: this rank scores the blocks [block_lo, block_hi) only and exchanges the row
@@ -767,9 +768,8 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int C = p.cluster;
-  const int pair = blockIdx.x / C;  // (sequence, kv head)
+  int pair = blockIdx.x / C;  // (sequence, kv head); re-mapped below when the grid runs in several waves
   const int crank = blockIdx.x - pair * C;  // rank inside the cluster that shares this pair
-  const int seq = pair / p.n_kv_heads;
   // Launched with programmatic dependent launch: nothing in global memory may be read
   // before the predecessor on the stream has completed (it may have produced the
   // lengths or the query, and the attention kernel of the previous step may still be
@@ -789,6 +789,27 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
   grid_dependency_wait();
   grid_launch_dependents();
   IA_TRACE(0);
+  if (p.longest_first) {
+    // More CTAs than the GPU holds at once: the hardware hands out CTAs in index order, so the CTAs take
+    // the sequences longest first - a long sequence that starts in the last wave would run alone at the
+    // end.  Every CTA ranks the batch by prefix length for itself (ties by index): a few hundred
+    // cached loads per thread.
+    int& seq_of_rank = reinterpret_cast<int*>(smem_raw + P::bars + P::hist)[30];  // a free word of the scan scratch
+    const int n_seq = p.n_pairs / p.n_kv_heads;
+    const int want = pair / p.n_kv_heads, head = pair - want * p.n_kv_heads;
+    for (int t = tid; t < n_seq; t += kThreads) {
+      const int len = p.prefix_lens[t];
+      int rank = 0;
+      for (int j = 0; j < n_seq; ++j) {
+        const int lj = p.prefix_lens[j];
+        rank += (lj > len || (lj == len && j < t)) ? 1 : 0;
+      }
+      if (rank == want) seq_of_rank = t;
+    }
+    __syncthreads();
+    pair = seq_of_rank * p.n_kv_heads + head;
+  }
+  const int seq = pair / p.n_kv_heads;
   const int prefix = p.prefix_lens[seq];
   const int nb = min((prefix + p.block_size - 1) / p.block_size, p.max_blocks);
   const int nb_cap = p.nb_cap;
@@ -1812,6 +1833,11 @@ static int launch_shaped(SelectParams& p, const AttendRequest& ar, int n_pairs, 
   int status = IA_OK;
   if (try_launch_fused<T, D, G, NG, KB, DIAG>(p, ar, n_pairs, smem, ring_bytes, resident_ctas, stream, &status))
     return status;
+  static const bool in_order = [] {
+    const char* v = getenv("INTERATTN_B200_SELECT_ORDER");
+    return v != nullptr && strcmp(v, "index") == 0;
+  }();
+  p.longest_first = !in_order && n_pairs * p.cluster > resident_ctas && n_pairs / p.n_kv_heads <= 4096;
   return launch_kernel(condition_block_select_kernel<T, D, G, NG, KB, DIAG>, "condition_block_select_kernel", p,
                        n_pairs, (unsigned)Shape<NG>::threads, smem, stream);
 }

@@ -54,7 +54,7 @@ def _check_against_oracle(cfg, case, summ, out, idx, cnt, rep_mode="sparse_only"
 
 
 @pytest.mark.parametrize("rep_mode", ["sparse_only", "hybrid"])
-@pytest.mark.parametrize("shape,cluster", [("wide", 1), ("narrow", 1), ("wide", 2), ("wide", 4), ("narrow", 2)])
+@pytest.mark.parametrize("shape,cluster", [("wide", 1), ("narrow", 1), ("wide", 2), ("wide", 4), ("wide", 8), ("narrow", 2)])
 @pytest.mark.parametrize("cfg", CASES, ids=lambda c: c.name)
 def test_fused_step_matches_selection_and_oracle(cfg, shape, cluster, rep_mode, monkeypatch):
     """cluster > 1: the CTAs that share a (sequence, kv head) also share its pages and rank 0 merges them.
