@@ -1669,10 +1669,10 @@ condition_block_select_kernel(const __grid_constant__ SelectParams p) {
 // The one-kernel layer step: selection, then - in the same CTA, with the picked blocks still in shared
 // memory - paged attention over them and the suffix, and the output rows.  bf16 pools, at most eight
 // query rows per kv head, one CTA per (sequence, kv head).
-template <int D, int G, int NG, typename KB>
+template <int D, int G, int NG, typename KB, bool DIAG>
 __global__ void __launch_bounds__(Shape<NG>::threads, Shape<NG>::min_ctas)
 condition_block_select_attend_kernel(const __grid_constant__ SelectParams p) {
-  select_body<__nv_bfloat16, D, G, NG, KB, false, true>(p);
+  select_body<__nv_bfloat16, D, G, NG, KB, DIAG, true>(p);
 }
 
 // cuTensorMapEncodeTiled lives in the driver library; fetch it through the
@@ -1779,17 +1779,22 @@ static int launch_kernel(Kern kern, const char* name, const SelectParams& p, int
   return check_launch(name);
 }
 
-// The fused form applies to bf16 pools with head_dim 128, at most eight query rows per kv head, the
-// range bound, one CTA per (sequence, kv head), no exchange with other GPUs, and a ring that holds at
-// least one page per consumer warp.  INTERATTN_B200_FUSED=0 keeps the two kernels.
+// The fused form applies to bf16 pools with head_dim 128, at most eight query rows per kv head, a
+// grid that is resident at once, no exchange with other GPUs, and a ring that holds at least one page
+// per attending warp.  INTERATTN_B200_FUSED=0 / ia_set_fused_step(0) keep the two kernels;
+// INTERATTN_B200_FUSED_WAVES=any lifts the single-wave rule (an experiment switch: measured slower).
 template <typename T, int D, int G, int NG, typename KB, bool DIAG>
 static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pairs, size_t smem, size_t ring_bytes,
                              int resident_ctas, cudaStream_t stream, int* status) {
-  if constexpr (sizeof(T) == 2 && D == 128 && G <= 8 && !DIAG) {
+  if constexpr (sizeof(T) == 2 && D == 128 && G <= 8) {
     // One wave only: with more CTAs than resident slots a CTA would hold its SM through the serial
     // phases of the selection while the attention of other pairs waits for a slot (measured: the ragged
-    // 70B batch, 512 pairs, 293 us fused against 247 us as two kernels).
-    if (ar.req == nullptr || p.xch.n_ranks > 0 || n_pairs * p.cluster > resident_ctas) return false;
+    // 70B batch, 512 pairs, 255 us fused against 240 us as two kernels).
+    static const bool any_waves = [] {
+      const char* v = getenv("INTERATTN_B200_FUSED_WAVES");
+      return v != nullptr && strcmp(v, "any") == 0;
+    }();
+    if (ar.req == nullptr || p.xch.n_ranks > 0 || (n_pairs * p.cluster > resident_ctas && !any_waves)) return false;
     const bool off = !fused_step_enabled();
     const ia_geom& g = *ar.geom;
     constexpr size_t kStage = 2 * 16 * D * 2;
@@ -1818,7 +1823,7 @@ static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pai
     p.att.n_pool_pages = g.n_pool_pages;
     p.att.ring_bytes = (int)ring_bytes;
     p.att.on = 1;
-    *status = launch_kernel(condition_block_select_attend_kernel<D, G, NG, KB>, "condition_block_select_attend_kernel",
+    *status = launch_kernel(condition_block_select_attend_kernel<D, G, NG, KB, DIAG>, "condition_block_select_attend_kernel",
                             p, n_pairs, (unsigned)Shape<NG>::threads, smem, stream);
     ar.req->used = 1;
     return true;
@@ -1831,13 +1836,13 @@ template <typename T, int D, int G, int NG, typename KB, bool DIAG>
 static int launch_shaped(SelectParams& p, const AttendRequest& ar, int n_pairs, size_t smem, size_t ring_bytes,
                          int resident_ctas, cudaStream_t stream) {
   int status = IA_OK;
-  if (try_launch_fused<T, D, G, NG, KB, DIAG>(p, ar, n_pairs, smem, ring_bytes, resident_ctas, stream, &status))
-    return status;
   static const bool in_order = [] {
     const char* v = getenv("INTERATTN_B200_SELECT_ORDER");
     return v != nullptr && strcmp(v, "index") == 0;
   }();
   p.longest_first = !in_order && n_pairs * p.cluster > resident_ctas && n_pairs / p.n_kv_heads <= 4096;
+  if (try_launch_fused<T, D, G, NG, KB, DIAG>(p, ar, n_pairs, smem, ring_bytes, resident_ctas, stream, &status))
+    return status;
   return launch_kernel(condition_block_select_kernel<T, D, G, NG, KB, DIAG>, "condition_block_select_kernel", p,
                        n_pairs, (unsigned)Shape<NG>::threads, smem, stream);
 }
