@@ -99,7 +99,7 @@ typedef struct ia_geom {
 #define IA_GEOM_KBAR_BF16 1
 /* ia_geom.reserved flag: the selection bounds |q . (k - k_bar)| with the diagonal-ellipsoid summaries
  * (ia_summaries.w, .rho) instead of the coordinate range (k_max, k_min) - the "diag_ell" bound of the
- * reference's condition_block_ball study (condition_block_ball/gen_selection.py:21-87, verdict in
+ * reference's condition_block_ball study (condition_block_ball/gen_selection.py:21-87, conclusions in
  * condition_block_ball/README.md:228-241): w = max(k_max - k_bar, k_bar - k_min) clamped at 1e-6,
  * rho = max_t |(k_t - k_bar) / w|, delta = rho |q * w| / sqrt(D).  Two vectors and a scalar per block
  * instead of three vectors; k_max / k_min are then not read by ia_select (and may be null there). */
