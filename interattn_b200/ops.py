@@ -388,20 +388,29 @@ class DecodeAttention:
         self.sel_count = torch.empty((b, kv.n_kv_heads), device=dev, dtype=torch.int32)
         self.out = torch.empty((b, rows, kv.head_dim), device=dev, dtype=kv.k_pool.dtype)
         self.q_dev = torch.empty((b, rows, kv.head_dim), device=dev, dtype=kv.k_pool.dtype)
+        # The step is called once per layer per token: everything that does not change from call to call is
+        # turned into ctypes objects here, once.  The tensors of ``kv`` and ``summ`` are therefore bound at
+        # construction - update them in place (lengths, table entries), do not replace them.
+        self._dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
+        self._shape, self._dtype = tuple(self.out.shape), self.out.dtype
+        self._kv_args = (_ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),
+                         _ptr(kv.seq_lens), ctypes.byref(self.c_summ), ctypes.byref(self.geom), self.mode,
+                         self.top_k, self.eps, self.max_sel, _REP[self.rep_mode], self.n_splits, self._ws_ptr(),
+                         self.ws_bytes)
+        self._out_args = (_ptr(self.sel_idx), _ptr(self.sel_count), _ptr(self.out))
+        self._q_dev_ptr, self._out_ptr = _ptr(self.q_dev), _ptr(self.out)
 
     def _ws_ptr(self):
         return ctypes.c_void_p(self.workspace.data_ptr() + self._ws_off)
 
+    def _stream(self):
+        return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(self._dev_index))
+
     def step(self, q: torch.Tensor) -> torch.Tensor:
-        _need_cuda(q)
-        if q.shape != self.out.shape or q.dtype != self.out.dtype or not q.is_contiguous():
-            raise ValueError(f"q must be a contiguous {tuple(self.out.shape)} {self.out.dtype} tensor")
-        kv = self.kv
-        check(self.lib.ia_decode_attention(
-            _ptr(q), _ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),
-            _ptr(kv.seq_lens), ctypes.byref(self.c_summ), ctypes.byref(self.geom), self.mode, self.top_k,
-            self.eps, self.max_sel, _REP[self.rep_mode], self.n_splits, self._ws_ptr(), self.ws_bytes,
-            _ptr(self.sel_idx), _ptr(self.sel_count), _ptr(self.out), _stream()))
+        if not q.is_cuda or q.shape != self._shape or q.dtype != self._dtype or not q.is_contiguous():
+            raise ValueError(f"q must be a contiguous CUDA {self._shape} {self._dtype} tensor")
+        check(self.lib.ia_decode_attention(ctypes.c_void_p(q.data_ptr()), *self._kv_args, *self._out_args,
+                                           self._stream()))
         return self.out
 
     def step_timed(self, q: torch.Tensor, events: Sequence[torch.cuda.Event]) -> torch.Tensor:
@@ -424,16 +433,13 @@ class DecodeAttention:
     def step_host(self, q_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
         if q_host.is_cuda or out_host.is_cuda:
             raise ValueError("step_host takes host tensors (pinned for full speed)")
-        if q_host.shape != self.out.shape or q_host.dtype != self.out.dtype or not q_host.is_contiguous():
-            raise ValueError(f"q_host must be a contiguous {tuple(self.out.shape)} {self.out.dtype} tensor")
-        if out_host.shape != self.out.shape or out_host.dtype != self.out.dtype or not out_host.is_contiguous():
+        if q_host.shape != self._shape or q_host.dtype != self._dtype or not q_host.is_contiguous():
+            raise ValueError(f"q_host must be a contiguous {self._shape} {self._dtype} tensor")
+        if out_host.shape != self._shape or out_host.dtype != self._dtype or not out_host.is_contiguous():
             raise ValueError("out_host must match q_host")
-        kv = self.kv
         check(self.lib.ia_decode_attention_host(
-            _ptr(q_host), _ptr(self.q_dev), _ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table),
-            _ptr(kv.prefix_lens), _ptr(kv.seq_lens), ctypes.byref(self.c_summ), ctypes.byref(self.geom),
-            self.mode, self.top_k, self.eps, self.max_sel, _REP[self.rep_mode], self.n_splits, self._ws_ptr(),
-            self.ws_bytes, _ptr(self.out), _ptr(out_host), _stream()))
+            ctypes.c_void_p(q_host.data_ptr()), self._q_dev_ptr, *self._kv_args, self._out_ptr,
+            ctypes.c_void_p(out_host.data_ptr()), self._stream()))
         return out_host
 
 
