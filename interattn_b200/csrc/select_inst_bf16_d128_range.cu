@@ -1,0 +1,8 @@
+// Instantiations of the selection kernels (select_kernel.cuh): bf16, d128, range.
+#include "select_kernel.cuh"
+
+namespace ia {
+int launch_select_bf16_d128_range(const SelectParams& p, const AttendRequest& ar, int n_pairs, int group, cudaStream_t stream) {
+  return launch_group_bound<__nv_bfloat16, 128, float, false>(p, ar, n_pairs, group, stream);
+}
+}  // namespace ia
