@@ -128,6 +128,28 @@ def test_fused_step_with_epsilon_rule(monkeypatch):
     _check_against_oracle(cfg, case, summ, out, idx, cnt)
 
 
+@pytest.mark.parametrize("cluster", [1, 2])
+def test_fused_step_with_more_pages_than_the_page_list_holds(cluster, monkeypatch):
+    """One query row per kv head and an epsilon below every score: all blocks are kept, four pages each -
+    more items than the shared-memory page list (rows x blocks entries) holds, so the attention phase
+    resolves and streams them in several chunks while the ring carries over."""
+    ops = _ops()
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", str(cluster))
+    cfg = DecodeConfig("g1_keep_all", "bfloat16", 2, 2, 2, 128, 16, 64, 2, (64 * 37 + 5, 64 * 12), (9, 0), seed=31)
+    case = make_case(cfg, spare_pages=3)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, eps=-1.0)
+    out = step.step(q).clone()
+    assert ops.last_decode_fused()
+    idx, cnt, _ = ops.select_blocks(q, summ, kv.prefix_lens, eps=-1.0)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert cnt.cpu().tolist() == [[38, 38], [12, 12]], "every block of every sequence"
+    assert torch.equal(step.sel_idx[:, :, :idx.shape[2]], idx) and torch.equal(step.sel_count, cnt)
+    _check_against_oracle(cfg, case, summ, out, idx, cnt)
+
+
 def test_fused_step_empty_prefix_and_empty_sequence(monkeypatch):
     ops = _ops()
     monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
