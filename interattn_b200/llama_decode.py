@@ -27,6 +27,7 @@ from __future__ import annotations
 import argparse
 import contextlib
 import json
+import os
 import time
 from typing import Optional
 
@@ -211,6 +212,7 @@ def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, blo
         tokens[:, i:i + 1] = tok_buf
 
     n_decode = max_new_tokens - 1
+    nvtx_steps = os.environ.get("INTERATTN_B200_NVTX", "") == "1"
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.no_grad(), _attn_impl(model, "eager"), _decode_patches(decoder):
         done = 0
@@ -242,7 +244,11 @@ def generate_batched(model, input_ids: torch.Tensor, max_new_tokens: int, *, blo
                 graph.replay()
             else:
                 decoder.set_position(prompt_len + done)
+                if nvtx_steps:  # a named range per eager step, for a profiler's range filter
+                    torch.cuda.nvtx.range_push(f"decode_step_{timed}")
                 one_step()
+                if nvtx_steps:
+                    torch.cuda.nvtx.range_pop()
                 pos_buf.add_(1)
             done += 1
             timed += 1
