@@ -31,6 +31,9 @@ CASES = [
     DecodeConfig("bf16_g1", "bfloat16", 2, 2, 2, 128, 16, 64, 2, (300, 64), (0, 0), seed=8),
     DecodeConfig("bf16_g2_ragged", "bfloat16", 4, 4, 2, 128, 16, 64, 3, (1, 129, 1000, 0), (15, 16, 17, 40), seed=11),
     DecodeConfig("bf16_g8_long_suffix", "bfloat16", 2, 8, 1, 128, 16, 64, 2, (520, 7), (300, 5), seed=12),
+    # blocks of two and of eight pages
+    DecodeConfig("bf16_block32", "bfloat16", 2, 8, 2, 128, 16, 32, 5, (1000, 333), (3, 40), seed=13),
+    DecodeConfig("bf16_block128", "bfloat16", 2, 8, 2, 128, 16, 128, 3, (2000, 129), (17, 0), seed=14),
 ]
 
 
