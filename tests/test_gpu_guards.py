@@ -126,3 +126,29 @@ def test_index_list_out_of_order_is_reported():
     got = _run(ops, q, kv, shuffled, cnt, nb, block_range=(0, nb), with_suffix=True)
     assert ops.device_status() & _lib.IA_DEV_STATUS_BAD_INDEX
     assert bool(torch.isfinite(got).all())
+
+
+def test_summaries_skip_a_table_entry_outside_the_declared_pool():
+    """The summary kernel fetches whole (page, kv head) runs with bulk copies: a block-table entry past the
+    declared pool is reported and its sixteen tokens are left out of the block's summary - never fetched."""
+    from interattn_b200 import _lib, ops
+    case = make_case(CFG)
+    q, kv = to_device(case)
+    nb = max_blocks_of(case)
+    clean = ops.build_summaries(kv, CFG.block_size, max_blocks=nb)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    # declare one page less than exist: the highest page id of the table is now "outside"
+    top = int(kv.block_table.max())
+    small = replace(kv, n_pool_pages=top)
+    got = ops.build_summaries(small, CFG.block_size, max_blocks=nb)
+    torch.cuda.synchronize()
+    assert ops.device_status() & _lib.IA_DEV_STATUS_BAD_INDEX
+    where = (kv.block_table == top).nonzero()[0]
+    seq, blk = int(where[0]), int(where[1]) // (CFG.block_size // 16)
+    same = torch.ones(clean.k_bar.shape[:3], dtype=torch.bool, device=clean.k_bar.device)
+    same[seq, :, blk] = False
+    assert torch.equal(got.k_bar[same], clean.k_bar[same]) and torch.equal(got.k_max[same], clean.k_max[same])
+    assert torch.isfinite(got.k_bar.float()).all()
+    if blk * CFG.block_size < int(kv.prefix_lens[seq]):  # the block lies in the summarised prefix: 48 tokens are left
+        assert not torch.equal(got.k_bar[seq, :, blk], clean.k_bar[seq, :, blk])
