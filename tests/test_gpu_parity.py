@@ -535,3 +535,37 @@ def test_argument_errors_are_value_errors():
         ops.sparse_decode(q, kv, idx, cnt, block_size=64, max_blocks=2, rep_mode="hybrid")   # no z / summaries
     with pytest.raises(ValueError):
         ops.sparse_decode(q, kv, idx, cnt, block_size=64, max_blocks=2, n_splits=0)
+
+
+@pytest.mark.parametrize("dtype,head_dim", [("bfloat16", 128), ("bfloat16", 64), ("float32", 128), ("float32", 64)])
+def test_streaming_and_direct_summary_kernels_agree(dtype, head_dim, monkeypatch):
+    """The two forms of the summary kernel (bulk-copy rings / plain loads) do the same arithmetic in the same
+    order per coordinate: means, bounds and mean values are identical bit for bit; the largest value norm only
+    differs in how the 32 lanes' partial sums are added (a few ulp).  Ragged lengths, an incremental update
+    included."""
+    ops = _ops()
+    cfg = DecodeConfig("summ_forms", dtype, 5, 8, 2, head_dim, 16, 64, 3, (1, 1000, 64, 2049, 0), (0, 3, 0, 0, 5), seed=17)
+    case = make_case(cfg, spare_pages=2)
+    case["block_table"] = case["block_table"].clamp_min(0)
+    q, kv = to_device(case)
+    nb = max_blocks_of(case)
+    built = {}
+    for form in ("stream", "direct"):
+        monkeypatch.setenv("INTERATTN_B200_SUMMARIES", form)
+        full = ops.build_summaries(kv, cfg.block_size, max_blocks=nb + 2)
+        part = ops.build_summaries(kv, cfg.block_size, max_blocks=nb + 2)
+        for name in ("k_bar", "k_max", "k_min", "v_bar", "v_norm_max"):
+            getattr(part, name).fill_(7.0)  # blocks below first_blocks must keep what they hold
+        first = torch.tensor([0, 9, 1, 30, 0], dtype=torch.int32, device=q.device)
+        ops.build_summaries(kv, cfg.block_size, max_blocks=nb + 2, out=part, first_blocks=first)
+        built[form] = (full, part)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    for which in (0, 1):
+        a, b = built["stream"][which], built["direct"][which]
+        for name in ("k_bar", "k_max", "k_min", "v_bar"):
+            assert torch.equal(getattr(a, name), getattr(b, name)), name
+        assert torch.allclose(a.v_norm_max, b.v_norm_max, rtol=1e-6, atol=0)
+    full, part = built["stream"]
+    assert bool((part.k_max[1, :, :9] == 7.0).all()) and torch.equal(part.k_max[1, :, 9:16], full.k_max[1, :, 9:16])
+    assert bool((part.k_max[3, :, :30] == 7.0).all()) and torch.equal(part.k_max[3, :, 30:33], full.k_max[3, :, 30:33])
