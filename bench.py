@@ -321,7 +321,7 @@ def kernel_times(torch, steppers, qs, K, repeats):
     return sel, att
 
 
-def kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode="sparse_only"):
+def kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode="sparse_only", phases=None):
     """(kernel_us, roofline, roofline_select) of a layer step.  Two kernels: the attention kernel is the
     dominant one and the selection kernel has its own record.  One fused kernel
     (condition_block_select_attend_kernel): it reads the summaries and the picked pages in one launch, so its
@@ -334,6 +334,17 @@ def kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mod
         roof = {"bound": "hbm", "kernel": "condition_block_select_attend_kernel", "achieved": gbs, "peak": peak,
                 "peak_source": src, "unit": "GB/s", "frac": gbs / peak,
                 "traffic": committed_traffic(workload, "select_attend"), "bytes_per_launch": kv_bytes + sel_bytes}
+        if phases is not None and phases[0] > 0 and phases[1] > 0:
+            # the kernel's own clock (time stamps of its first CTA): the latency-bound selection in front and the
+            # streaming attention phase behind it, each with the bytes it moves
+            s_us, a_us = phases
+            roof["phases"] = {
+                "selection": {"us": s_us, "bytes": sel_bytes, "achieved": sel_bytes / (s_us * 1e-6) / 1e9,
+                              "frac": sel_bytes / (s_us * 1e-6) / 1e9 / peak},
+                "attention": {"us": a_us, "bytes": kv_bytes, "achieved": kv_bytes / (a_us * 1e-6) / 1e9,
+                              "frac": kv_bytes / (a_us * 1e-6) / 1e9 / peak},
+                "clock": "nanosecond global timer, first CTA of the last launch; the event-timed duration above "
+                         "also holds launch and drain"}
         return kernel_us, roof, None
     att_gbs, sel_gbs = kv_bytes / (att_us * 1e-6) / 1e9, sel_bytes / (sel_us * 1e-6) / 1e9
     suffix = "" if rep_mode == "sparse_only" else f"_{rep_mode}"
@@ -370,8 +381,9 @@ def _variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summar
     ms = regions.run(lambda i: steppers[i % n_pools].step(qs[i % n_pools]), K, R)
     sel_us, att_us = kernel_times(torch, steppers, qs, K, max(1, R // 5))
     fused = ops.last_decode_fused()
+    phases = ops.last_step_phases() if fused else None
     kv_bytes, sel_bytes = algorithmic_bytes(cfg, rep_mode, kbar_bf16, bound)
-    kernel_us, roof, roof_sel = kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode)
+    kernel_us, roof, roof_sel = kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode, phases)
     rec = {
         "us_per_layer": summarise(ms, K), "kernel_us": kernel_us,
         "config": {"rep_mode": rep_mode, "k_bar": "bf16" if kbar_bf16 else "f32", "bound": bound,
@@ -474,6 +486,7 @@ def layer_step_record(args, workload, torch, dist, regions, world, rank, local_r
     # the same steps again with events between the kernels: per-kernel device times for the roofline
     sel_us, att_us = kernel_times(torch, steppers, qs, K, max(1, R // 5))
     fused = ops.last_decode_fused()  # one launch per step (selection + attention in one kernel) or two
+    phases = ops.last_step_phases() if fused else None
     status = ops.device_status()
 
     # end-to-end: host q in, host output back, every step
@@ -510,7 +523,8 @@ def layer_step_record(args, workload, torch, dist, regions, world, rank, local_r
 
     esz = 2 if cfg.dtype == "bfloat16" else 4
     kv_bytes, sel_bytes = algorithmic_bytes(cfg, args.rep_mode, args.kbar_bf16)
-    kernel_us, roof, roof_sel = kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, args.rep_mode)
+    kernel_us, roof, roof_sel = kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, args.rep_mode,
+                                               phases)
     q_bytes = cfg.batch * rows * cfg.head_dim * esz
     line = {
         "metric": METRIC, "value": replicas * cfg.batch / (step_us["median"] * 1e-6), "unit": UNIT,

@@ -326,6 +326,12 @@ int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool,
  * No reference counterpart: a reporting aid for benchmarks, which attribute time and bytes per kernel. */
 int ia_last_decode_fused(void);
 
+/* How the last completed one-kernel step on the current device split its time, in microseconds, as seen by
+ * its first CTA: from kernel entry to the end of the routing (selection_us) and from there to the written
+ * output rows (attention_us).  Reads device memory with a synchronous copy: call it where the host waits
+ * anyway.  No reference counterpart: benchmarks report the two phases of the fused kernel separately. */
+int ia_last_step_phases(double* selection_us, double* attention_us);
+
 /* Process-wide switch of the one-kernel form (1 = allowed where it applies, the default unless
  * INTERATTN_B200_FUSED=0 is in the environment; 0 = always two launches).  Returns the previous setting.
  * No reference counterpart: for A/B measurements and for profiling the two kernels separately. */

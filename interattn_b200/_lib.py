@@ -65,6 +65,7 @@ SIGNATURES = {
     "ia_abi_version": (c_int, []),
     "ia_last_decode_fused": (c_int, []),
     "ia_set_fused_step": (c_int, [c_int]),
+    "ia_last_step_phases": (c_int, [POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
     "ia_last_error_string": (c_char_p, []),
     "ia_read_device_status": (c_int, [POINTER(c_int)]),
     "ia_build_summaries": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Geom), POINTER(Summaries), c_void_p]),

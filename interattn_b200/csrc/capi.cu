@@ -452,6 +452,11 @@ int ia_decode_attention(const void* q, const void* k_pool, const void* v_pool, c
 
 int ia_last_decode_fused(void) { return t_last_decode_fused; }
 
+int ia_last_step_phases(double* selection_us, double* attention_us) {
+  if (!selection_us || !attention_us) return fail(IA_ERR_BAD_ARG, "last_step_phases: null argument");
+  return read_step_phases(selection_us, attention_us);
+}
+
 int ia_set_fused_step(int enabled) {
   const int before = ia::fused_step_enabled() ? 1 : 0;
   g_fused_step.store(enabled ? 1 : 0, std::memory_order_relaxed);

@@ -29,6 +29,7 @@ enum : int {
 };
 int* device_status_address();  // device address of the status word on the current device
 int read_and_clear_device_status(int* out);  // defined next to the kernel that owns the word
+int read_step_phases(double* selection_us, double* attention_us);  // of the last one-kernel step's first CTA
 
 // ---- dtype traits ---------------------------------------------------------------
 template <typename T> struct DType;

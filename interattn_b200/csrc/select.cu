@@ -28,6 +28,32 @@ int* device_status_address() {
   return cached[dev];
 }
 
+// Time stamps of the one-kernel step's first CTA (nanosecond global timer): kernel entry, start of the
+// attention phase, end.  A reporting aid: benchmarks split the fused kernel's time into its two phases.
+__device__ unsigned long long g_step_stamps[4] = {0, 0, 0, 0};
+
+unsigned long long* step_stamps_address() {
+  constexpr int kMaxDevices = 64;
+  static unsigned long long* cached[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_step_stamps) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<unsigned long long*>(ptr);
+  }
+  return cached[dev];
+}
+
+int read_step_phases(double* selection_us, double* attention_us) {
+  unsigned long long v[4] = {0, 0, 0, 0};
+  const cudaError_t e = cudaMemcpyFromSymbol(v, g_step_stamps, sizeof(v));
+  if (e != cudaSuccess) return fail(IA_ERR_LAUNCH, "step phases: %s", cudaGetErrorString(e));
+  *selection_us = v[1] >= v[0] ? (double)(v[1] - v[0]) * 1e-3 : 0.0;
+  *attention_us = v[2] >= v[1] ? (double)(v[2] - v[1]) * 1e-3 : 0.0;
+  return IA_OK;
+}
+
 int read_and_clear_device_status(int* out) {
   int v = 0, zero = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int));
@@ -52,6 +78,7 @@ int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_le
   p.n_pairs = g.batch * g.n_kv_heads;
   p.status = device_status_address();
   if (p.status == nullptr) return IA_ERR_LAUNCH;
+  p.stamps = step_stamps_address();
   p.q = q; p.k_bar = s.k_bar; p.k_max = s.k_max; p.k_min = s.k_min; p.v_norm_max = s.v_norm_max;
   if (g.reserved & IA_GEOM_DIAG_ELL) {  // the diagonal-ellipsoid bound: w takes the place of k_max, k_min is not read
     p.k_max = s.w;

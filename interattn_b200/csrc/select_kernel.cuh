@@ -68,6 +68,7 @@ struct SelectParams {
   int block_lo, block_hi;
   int n_pairs;
   int* status;  // the device status word (bounded waits that ran out, indices out of range)
+  unsigned long long* stamps;  // may be null: the first CTA of the one-kernel step leaves three time stamps
   // One-kernel layer step (att.on): the CTA that routed a (sequence, kv head) attends over what it picked.
   struct Attend {
     // the K and V pools as 4-D tensors [page, kv head, token, head_dim]; box = 128 bytes x one page of tokens
@@ -146,6 +147,11 @@ constexpr int kMaxStages = 8;
 constexpr uint32_t kWaitPolls = 1u << 20;  // bounded mbarrier wait, then give up
 
 
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -777,6 +783,9 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
   grid_dependency_wait();
   grid_launch_dependents();
   IA_TRACE(0);
+  if constexpr (FUSE) {
+    if (blockIdx.x == 0 && tid == 0 && p.stamps != nullptr) p.stamps[0] = global_timer_ns();
+  }
   if (p.longest_first) {
     // More CTAs than the GPU holds at once: the hardware hands out CTAs in index order, so the CTAs take
     // the sequences longest first - a long sequence that starts in the last wave would run alone at the
@@ -1639,12 +1648,14 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
     }
     // The histograms are idle: their 3 KB hold the page ring's barriers and descriptors.
     static_assert(P::hist >= 32 * 8, "the page ring's barriers live in the histogram area");
+    if (blockIdx.x == 0 && tid == 0 && p.stamps != nullptr) p.stamps[1] = global_timer_ns();
     // delta per (row, block) is dead too: the resolved page numbers go there; the scores' array holds the
     // bitmap of the picked blocks (hybrid); z stays - the representatives' logits
     attend_selected_pages<D, G, kAttendWarps<NG>>(p, pair, seq, prefix, crank, C, sel_list, count, q_s, z_s, nbl,
                                                 b_lo, b_hi, reinterpret_cast<uint32_t*>(score_s), nb_cap,
                                                 reinterpret_cast<int*>(d_s), G * nbl, stage_base,
                                                 reinterpret_cast<unsigned char*>(hist), IA_TRACE_T0);
+    if (blockIdx.x == 0 && tid == 0 && p.stamps != nullptr) p.stamps[2] = global_timer_ns();
   }
 }
 

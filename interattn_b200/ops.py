@@ -487,6 +487,14 @@ def last_decode_fused() -> bool:
     return bool(_lib.load().ia_last_decode_fused())
 
 
+def last_step_phases() -> Tuple[float, float]:
+    """(selection_us, attention_us) of the last completed one-kernel step on the current device, as seen by
+    the kernel's first CTA.  Synchronises (a device-to-host copy)."""
+    sel, att = ctypes.c_double(0.0), ctypes.c_double(0.0)
+    check(_lib.load().ia_last_step_phases(ctypes.byref(sel), ctypes.byref(att)))
+    return float(sel.value), float(att.value)
+
+
 def set_fused_step(enabled: bool) -> bool:
     """Allow (default) or forbid the one-kernel form of the layer step, process-wide; returns the previous
     setting.  For A/B measurements: the two-kernel form is what runs anyway where the fused one does not apply."""

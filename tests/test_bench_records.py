@@ -48,3 +48,11 @@ def test_kernel_records(bench, fused):
         assert kernel_us == {"select": 30.0, "sparse_decode": 50.0, "finalize": 0.0}
     # the traffic figures come from the committed ncu summaries
     assert roof["traffic"] is not None and roof["traffic"] >= roof["bytes_per_launch"]
+
+
+def test_fused_record_splits_into_phases(bench):
+    _, roof, _ = bench.kernel_records(True, 30.0, 50.0, 268435456, 67371008, "cfg2_llama8b_32k", phases=(22.0, 45.0))
+    ph = roof["phases"]
+    assert abs(ph["attention"]["achieved"] - 268435456 / 45e-6 / 1e9) < 1e-6
+    assert abs(ph["selection"]["frac"] - 67371008 / 22e-6 / 1e9 / roof["peak"]) < 1e-12
+    assert ph["attention"]["bytes"] + ph["selection"]["bytes"] == roof["bytes_per_launch"]

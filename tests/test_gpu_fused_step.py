@@ -271,3 +271,25 @@ def test_fused_step_replays_from_a_cuda_graph(monkeypatch):
     torch.cuda.synchronize()
     assert torch.equal(step.out, want)
     assert ops.device_status() == 0
+
+
+def test_phase_stamps_of_the_last_fused_step(monkeypatch):
+    """The first CTA of the one-kernel step leaves three time stamps; the two phases are positive and add up to
+    less than the step's duration between events."""
+    ops = _ops()
+    monkeypatch.setenv("INTERATTN_B200_SELECT_CLUSTER", "1")
+    cfg = CASES[0]
+    case = make_case(cfg, spare_pages=3)
+    q, kv = to_device(case)
+    summ = ops.build_summaries(kv, cfg.block_size, max_blocks=max_blocks_of(case))
+    step = ops.DecodeAttention(kv, summ, cfg.n_q_heads, top_k=cfg.top_k)
+    step.step(q)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    step.step(q)
+    b.record()
+    torch.cuda.synchronize()
+    assert ops.last_decode_fused()
+    sel_us, att_us = ops.last_step_phases()
+    assert 0.5 < sel_us < 1000.0 and 0.5 < att_us < 1000.0
+    assert sel_us + att_us <= a.elapsed_time(b) * 1e3 + 1.0
