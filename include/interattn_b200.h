@@ -83,7 +83,7 @@ typedef struct ia_geom {
   int32_t max_pages;    /* row length of block_table */
   int32_t max_blocks;   /* blocks per (sequence, kv head) in the summary arrays */
   int32_t dtype;        /* ia_dtype of q, pools, k_max/k_min/v_bar */
-  int32_t reserved;     /* flags: IA_GEOM_KBAR_BF16, else 0 */
+  int32_t reserved;     /* flags: IA_GEOM_KBAR_BF16 | IA_GEOM_DIAG_ELL | IA_GEOM_PACKED_BOUNDS, else 0 */
   int32_t n_pool_pages; /* physical pages in k_pool / v_pool; block-table entries are checked against
                            it before they are used.  0: unknown, entries are trusted. */
   int32_t reserved2;    /* 0 */
@@ -104,6 +104,13 @@ typedef struct ia_geom {
  * rho = max_t |(k_t - k_bar) / w|, delta = rho |q * w| / sqrt(D).  Two vectors and a scalar per block
  * instead of three vectors; k_max / k_min are then not read by ia_select (and may be null there). */
 #define IA_GEOM_DIAG_ELL 2
+/* ia_geom.reserved flag: the coordinate range is stored packed, as the reference does with
+ * CONDITION_BLOCK_TMA_BOUNDS=1 (IMPL/core.py:490-499: torch.stack((k_max, k_min), dim=-1).flatten(2)):
+ * ia_summaries.k_max points to one array [batch, kv heads, max_blocks, 2 * head_dim] in the KV dtype whose
+ * element 2 d is k_max[d] and element 2 d + 1 is k_min[d]; ia_summaries.k_min is not read.  ia_build_summaries
+ * writes that layout, ia_select / ia_decode_attention read it (same bytes per block as the two arrays).
+ * Not together with IA_GEOM_DIAG_ELL. */
+#define IA_GEOM_PACKED_BOUNDS 4
 
 /* Block summaries, "mixed" storage of the reference (IMPL/core.py:411-446):
  * means accumulated in fp32, k_bar kept in fp32, the rest in the KV dtype

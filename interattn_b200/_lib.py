@@ -24,6 +24,7 @@ IA_SELECT_TOPK, IA_SELECT_EPS = 0, 1
 IA_SELECT_TERM1_MASS_EXP = 0x100   # OR-ed into the mode
 IA_GEOM_KBAR_BF16 = 1              # ia_geom.reserved flag: k_bar stored in bf16
 IA_GEOM_DIAG_ELL = 2               # ia_geom.reserved flag: the selection uses the (w, rho) bound
+IA_GEOM_PACKED_BOUNDS = 4          # ia_geom.reserved flag: k_max holds (k_max[d], k_min[d]) pairs, k_min is unused
 IA_REP_SPARSE_ONLY, IA_REP_HYBRID = 0, 1
 ABI_VERSION = 3
 # masks of the device status word (ia_read_device_status)

@@ -23,7 +23,8 @@ OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "libinterattn_b200.so")
 SOURCES = ["capi.cu", "summaries.cu", "select.cu", "select_inst_bf16_d128_range.cu", "select_inst_bf16_d128_diag.cu",
            "select_inst_bf16_d64.cu", "select_inst_f32_d128.cu", "select_inst_f32_d64.cu",
-           "select_inst_kbar16_d128.cu", "select_inst_kbar16_d64.cu", "sparse_decode.cu", "sparse_decode_mma.cu",
+           "select_inst_kbar16_d128.cu", "select_inst_kbar16_d64.cu", "select_inst_bf16_d128_packed.cu",
+           "select_inst_bf16_d64_packed.cu", "select_inst_f32_packed.cu", "select_inst_kbar16_packed.cu", "sparse_decode.cu", "sparse_decode_mma.cu",
            "finalize.cu", "llama_step.cu", "skinny_gemm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -65,8 +65,10 @@ int check_geom(const ia_geom* g) {
   const int64_t esz = g->dtype == IA_BF16 ? 2 : 4;
   if ((g->pool_head_stride * esz) % 16 != 0 || (g->pool_page_stride * esz) % 16 != 0)
     return fail(IA_ERR_BAD_ARG, "geom: pool strides must be multiples of 16 bytes");
-  if (g->reserved & ~(IA_GEOM_KBAR_BF16 | IA_GEOM_DIAG_ELL))
+  if (g->reserved & ~(IA_GEOM_KBAR_BF16 | IA_GEOM_DIAG_ELL | IA_GEOM_PACKED_BOUNDS))
     return fail(IA_ERR_BAD_ARG, "geom: unknown flag bits in reserved (%d)", g->reserved);
+  if ((g->reserved & IA_GEOM_DIAG_ELL) && (g->reserved & IA_GEOM_PACKED_BOUNDS))
+    return fail(IA_ERR_BAD_ARG, "geom: the packed range layout and the diag_ell bound exclude one another");
   if (g->n_pool_pages < 0 || g->reserved2 != 0)
     return fail(IA_ERR_BAD_ARG, "geom: n_pool_pages %d (0 = unknown), reserved2 %d (must be 0)", g->n_pool_pages,
                 g->reserved2);
@@ -78,8 +80,12 @@ int check_geom(const ia_geom* g) {
 static int check_summaries(const ia_summaries* s, const ia_geom* g = nullptr, bool building = false) {
   if (s == nullptr) return fail(IA_ERR_BAD_ARG, "summaries is null");
   const bool diag = g != nullptr && (g->reserved & IA_GEOM_DIAG_ELL) != 0;
+  const bool packed = g != nullptr && (g->reserved & IA_GEOM_PACKED_BOUNDS) != 0;  // k_max holds both, k_min unused
   if (!s->k_bar || !s->v_bar || !s->v_norm_max) return fail(IA_ERR_BAD_ARG, "summaries: null member");
-  if ((!diag || building) && (!s->k_max || !s->k_min)) return fail(IA_ERR_BAD_ARG, "summaries: null k_max / k_min");
+  if ((!diag || building) && (!s->k_max || (!packed && !s->k_min)))
+    return fail(IA_ERR_BAD_ARG, "summaries: null k_max / k_min");
+  if (packed && building && (s->w || s->rho))
+    return fail(IA_ERR_BAD_ARG, "summaries: the packed range layout does not carry the diagonal-ellipsoid pair");
   if ((diag || s->w || s->rho) && (!s->w || !s->rho))
     return fail(IA_ERR_BAD_ARG, "summaries: the diagonal-ellipsoid bound needs both w and rho");
   if (!aligned16(s->k_bar) || !aligned16(s->k_max) || !aligned16(s->k_min) || !aligned16(s->v_bar) || !aligned16(s->w))

@@ -92,6 +92,19 @@ int launch_select(const void* q, const ia_summaries& s, const int32_t* prefix_le
   p.sel_idx = sel_idx; p.sel_count = sel_count; p.aux = aux; p.split_counters = split_counters;
   const int n_pairs = g.batch * g.n_kv_heads;
   if (n_pairs <= 0) return IA_OK;
+  if (g.reserved & IA_GEOM_PACKED_BOUNDS) {  // k_max holds the (k_max, k_min) pairs; k_min is not read
+    p.k_min = p.k_max;
+    if (g.head_dim != 128 && g.head_dim != 64)
+      return fail(IA_ERR_UNSUPPORTED, "select: head_dim %d / dtype %d not built", g.head_dim, g.dtype);
+    if (g.reserved & IA_GEOM_KBAR_BF16) {
+      if (g.dtype != IA_BF16) return fail(IA_ERR_UNSUPPORTED, "select: bf16 k_bar needs bf16 pools");
+      return launch_select_kbar16_packed(p, ar, n_pairs, g.group_size, g.head_dim, stream);
+    }
+    if (g.dtype == IA_BF16)
+      return g.head_dim == 128 ? launch_select_bf16_d128_packed(p, ar, n_pairs, g.group_size, stream)
+                               : launch_select_bf16_d64_packed(p, ar, n_pairs, g.group_size, stream);
+    return launch_select_f32_packed(p, ar, n_pairs, g.group_size, g.head_dim, stream);
+  }
   if (g.reserved & IA_GEOM_KBAR_BF16) {  // k_bar stored in bf16: only next to bf16 pools ("mixed" storage)
     if (g.dtype != IA_BF16) return fail(IA_ERR_UNSUPPORTED, "select: bf16 k_bar needs bf16 pools");
     if (g.head_dim == 128) return launch_select_kbar16_d128(p, ar, n_pairs, g.group_size, stream);

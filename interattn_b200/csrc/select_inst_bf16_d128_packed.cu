@@ -1,0 +1,9 @@
+// Instantiations of the selection kernels (select_kernel.cuh): bf16, d128, packed range.
+#include "select_kernel.cuh"
+
+namespace ia {
+int launch_select_bf16_d128_packed(const SelectParams& p, const AttendRequest& ar, int n_pairs, int group,
+                                   cudaStream_t stream) {
+  return launch_group_packed<__nv_bfloat16, 128>(p, ar, n_pairs, group, stream);
+}
+}  // namespace ia

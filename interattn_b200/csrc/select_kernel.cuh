@@ -100,6 +100,11 @@ int launch_select_f32_d128(const SelectParams&, const AttendRequest&, int n_pair
 int launch_select_f32_d64(const SelectParams&, const AttendRequest&, int n_pairs, int group, cudaStream_t);
 int launch_select_kbar16_d128(const SelectParams&, const AttendRequest&, int n_pairs, int group, cudaStream_t);
 int launch_select_kbar16_d64(const SelectParams&, const AttendRequest&, int n_pairs, int group, cudaStream_t);
+// the same with the coordinate range in the packed layout (IA_GEOM_PACKED_BOUNDS)
+int launch_select_bf16_d128_packed(const SelectParams&, const AttendRequest&, int n_pairs, int group, cudaStream_t);
+int launch_select_bf16_d64_packed(const SelectParams&, const AttendRequest&, int n_pairs, int group, cudaStream_t);
+int launch_select_f32_packed(const SelectParams&, const AttendRequest&, int n_pairs, int group, int head_dim, cudaStream_t);
+int launch_select_kbar16_packed(const SelectParams&, const AttendRequest&, int n_pairs, int group, int head_dim, cudaStream_t);
 
 namespace {
 
@@ -751,8 +756,11 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
   IA_TRACE(14);
 }
 
-template <typename T, int D, int G, int NG, typename KB, bool DIAG, bool FUSE>
+template <typename T, int D, int G, int NG, typename KB, int BOUND, bool FUSE>
 __device__ __forceinline__ void select_body(const SelectParams& p) {
+  // BOUND: 0 = coordinate range from two arrays, 1 = diagonal ellipsoid (w, rho), 2 = coordinate range from the
+  // packed array of (k_max[d], k_min[d]) pairs (same stage layout as 0: the pairs fill the two bound vectors' space)
+  constexpr bool DIAG = BOUND == 1, PACKED = BOUND == 2;
   using L = TileLayout<T, D, KB, DIAG>;
   using P = SmemPlan<D, G, kUseMma<T, G>, NG>;
   constexpr int kGroups = NG, kConsumerWarps = Shape<NG>::consumer_warps, kWarps = Shape<NG>::warps,
@@ -870,12 +878,18 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
 #pragma unroll
     for (int j = 0; j < L::kbar_boxes; ++j)
       tma_load_2d(st + j * L::box_bytes, &p.tm_kbar, j * L::kbar_box_cols, y, &full_bar[stage]);
+    if constexpr (PACKED) {  // rows of 2 D elements: twice the boxes of one vector, into the two vectors' space
 #pragma unroll
-    for (int j = 0; j < L::bnd_boxes; ++j) {
-      tma_load_2d(st + L::kbar_bytes + j * L::box_bytes, &p.tm_kmax, j * L::bnd_box_cols, y, &full_bar[stage]);
-      if constexpr (!DIAG)
-        tma_load_2d(st + L::kbar_bytes + L::bnd_bytes + j * L::box_bytes, &p.tm_kmin, j * L::bnd_box_cols, y,
-                    &full_bar[stage]);
+      for (int j = 0; j < 2 * L::bnd_boxes; ++j)
+        tma_load_2d(st + L::kbar_bytes + j * L::box_bytes, &p.tm_kmax, j * L::bnd_box_cols, y, &full_bar[stage]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < L::bnd_boxes; ++j) {
+        tma_load_2d(st + L::kbar_bytes + j * L::box_bytes, &p.tm_kmax, j * L::bnd_box_cols, y, &full_bar[stage]);
+        if constexpr (!DIAG)
+          tma_load_2d(st + L::kbar_bytes + L::bnd_bytes + j * L::box_bytes, &p.tm_kmin, j * L::bnd_box_cols, y,
+                      &full_bar[stage]);
+      }
     }
   };
   // The producer lane owns the barriers: it initialises them and fills the ring's first uses while
@@ -1045,8 +1059,28 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
           mma_bf16(cd, a, bm[kk]);
         }
       }
+      if constexpr (PACKED) {
+        // Rows of (k_max[d], k_min[d]) pairs: a k-step of 16 packed elements is eight coordinates, and
+        //   sum_d max(q k_max, q k_min) = row . (q+_0, q-_0, q+_1, q-_1, ...),
+        //   sum_d min(q k_max, q k_min) = row . (q-_0, q+_0, q-_1, q+_1, ...):
+        // two contractions of length 2 D with the query's signed parts interleaved - the B fragments are
+        // put together from the query row in shared memory at every step, the accumulators are xp and np_.
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
+        for (int kk = 0; kk < D / 8; ++kk) {
+          const int byte = (kk * 16 + (lm >> 1) * 8) * 2;
+          const uint32_t off = (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4);
+          uint32_t a[4];
+          ldmatrix_x4(st + L::kbar_bytes + off, a);
+          const float x0 = n < G ? q_s[n * D + kk * 8 + kq] : 0.f;      // fragment k = 2 kq, 2 kq + 1: coordinate kq
+          const float x1 = n < G ? q_s[n * D + kk * 8 + kq + 4] : 0.f;  // k + 8: coordinate kq + 4
+          const uint32_t bu[2] = {pack_bf16(fmaxf(x0, 0.f), fminf(x0, 0.f)), pack_bf16(fmaxf(x1, 0.f), fminf(x1, 0.f))};
+          const uint32_t bl[2] = {pack_bf16(fminf(x0, 0.f), fmaxf(x0, 0.f)), pack_bf16(fminf(x1, 0.f), fmaxf(x1, 0.f))};
+          mma_bf16(xp, a, bu);
+          mma_bf16(np_, a, bl);
+        }
+      }
+#pragma unroll
+      for (int kk = 0; kk < (PACKED ? 0 : D / 16); ++kk) {
         const int byte = (kk * 16 + (lm >> 1) * 8) * 2;
         const uint32_t off = (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4);
         uint32_t a[4];
@@ -1186,7 +1220,22 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
         } else {
           load8(swz<__nv_bfloat16>(kbar_v, lane, e0), kb);
         }
-        if constexpr (sizeof(T) == 2) {
+        if constexpr (PACKED) {
+          // sixteen packed elements = the (k_max, k_min) pairs of the eight coordinates e0 .. e0 + 7
+          float both[16];
+          if constexpr (sizeof(T) == 2) {
+            float a8[8], b8[8];
+            load8(swz<T>(kmax_v, lane, 2 * e0), a8);
+            load8(swz<T>(kmax_v, lane, 2 * e0 + 8), b8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { both[i] = a8[i]; both[8 + i] = b8[i]; }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) load4(swz<float>(kmax_v, lane, 2 * e0 + 4 * i), both + 4 * i);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { hi[i] = both[2 * i]; lo[i] = both[2 * i + 1]; }
+        } else if constexpr (sizeof(T) == 2) {
           load8(swz<T>(kmax_v, lane, e0), hi);
           if constexpr (!DIAG) load8(swz<T>(kmin_v, lane, e0), lo);
         } else {
@@ -1659,19 +1708,19 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
   }
 }
 
-template <typename T, int D, int G, int NG, typename KB, bool DIAG>
+template <typename T, int D, int G, int NG, typename KB, int BOUND>
 __global__ void __launch_bounds__(Shape<NG>::threads, Shape<NG>::min_ctas)
 condition_block_select_kernel(const __grid_constant__ SelectParams p) {
-  select_body<T, D, G, NG, KB, DIAG, false>(p);
+  select_body<T, D, G, NG, KB, BOUND, false>(p);
 }
 
 // The one-kernel layer step: selection, then - in the same CTA, with the picked blocks still in shared
 // memory - paged attention over them and the suffix, and the output rows.  bf16 pools, at most eight
 // query rows per kv head, one CTA per (sequence, kv head).
-template <int D, int G, int NG, typename KB, bool DIAG>
+template <int D, int G, int NG, typename KB, int BOUND>
 __global__ void __launch_bounds__(Shape<NG>::threads, Shape<NG>::min_ctas)
 condition_block_select_attend_kernel(const __grid_constant__ SelectParams p) {
-  select_body<__nv_bfloat16, D, G, NG, KB, DIAG, true>(p);
+  select_body<__nv_bfloat16, D, G, NG, KB, BOUND, true>(p);
 }
 
 // cuTensorMapEncodeTiled lives in the driver library; fetch it through the
@@ -1776,7 +1825,7 @@ static int launch_kernel(Kern kern, const char* name, const SelectParams& p, int
 // grid that is resident at once, no exchange with other GPUs, and a ring that holds at least one page
 // per attending warp.  INTERATTN_B200_FUSED=0 / ia_set_fused_step(0) keep the two kernels;
 // INTERATTN_B200_FUSED_WAVES=any lifts the single-wave rule (an experiment switch: measured slower).
-template <typename T, int D, int G, int NG, typename KB, bool DIAG>
+template <typename T, int D, int G, int NG, typename KB, int BOUND>
 static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pairs, size_t smem, size_t ring_bytes,
                              int resident_ctas, cudaStream_t stream, int* status) {
   if constexpr (sizeof(T) == 2 && D == 128 && G <= 8) {
@@ -1816,7 +1865,7 @@ static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pai
     p.att.n_pool_pages = g.n_pool_pages;
     p.att.ring_bytes = (int)ring_bytes;
     p.att.on = 1;
-    *status = launch_kernel(condition_block_select_attend_kernel<D, G, NG, KB, DIAG>, "condition_block_select_attend_kernel",
+    *status = launch_kernel(condition_block_select_attend_kernel<D, G, NG, KB, BOUND>, "condition_block_select_attend_kernel",
                             p, n_pairs, (unsigned)Shape<NG>::threads, smem, stream);
     ar.req->used = 1;
     return true;
@@ -1825,7 +1874,7 @@ static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pai
   }
 }
 
-template <typename T, int D, int G, int NG, typename KB, bool DIAG>
+template <typename T, int D, int G, int NG, typename KB, int BOUND>
 static int launch_shaped(SelectParams& p, const AttendRequest& ar, int n_pairs, size_t smem, size_t ring_bytes,
                          int resident_ctas, cudaStream_t stream) {
   int status = IA_OK;
@@ -1834,15 +1883,16 @@ static int launch_shaped(SelectParams& p, const AttendRequest& ar, int n_pairs, 
     return v != nullptr && strcmp(v, "index") == 0;
   }();
   p.longest_first = !in_order && n_pairs * p.cluster > resident_ctas && n_pairs / p.n_kv_heads <= 4096;
-  if (try_launch_fused<T, D, G, NG, KB, DIAG>(p, ar, n_pairs, smem, ring_bytes, resident_ctas, stream, &status))
+  if (try_launch_fused<T, D, G, NG, KB, BOUND>(p, ar, n_pairs, smem, ring_bytes, resident_ctas, stream, &status))
     return status;
-  return launch_kernel(condition_block_select_kernel<T, D, G, NG, KB, DIAG>, "condition_block_select_kernel", p,
+  return launch_kernel(condition_block_select_kernel<T, D, G, NG, KB, BOUND>, "condition_block_select_kernel", p,
                        n_pairs, (unsigned)Shape<NG>::threads, smem, stream);
 }
 
 
-template <typename T, int D, int G, typename KB, bool DIAG>
+template <typename T, int D, int G, typename KB, int BOUND>
 static int launch_typed(const SelectParams& base, const AttendRequest& ar, int n_pairs, cudaStream_t stream) {
+  constexpr bool DIAG = BOUND == 1, PACKED = BOUND == 2;
   using L = TileLayout<T, D, KB, DIAG>;
   using PW = SmemPlan<D, G, kUseMma<T, G>, kWideGroups>;
   using PN = SmemPlan<D, G, kUseMma<T, G>, kNarrowGroups>;
@@ -1876,8 +1926,10 @@ static int launch_typed(const SelectParams& base, const AttendRequest& ar, int n
   const int64_t rows = (int64_t)n_pairs * p.max_blocks;
   if (rows > 0x7fffffff) return fail(IA_ERR_UNSUPPORTED, "select: %lld summary rows exceed the TMA coordinate range", (long long)rows);
   if (int s = encode_rows(&p.tm_kbar, p.k_bar, sizeof(KB) == 2, rows, D)) return s;
-  if (int s = encode_rows(&p.tm_kmax, p.k_max, sizeof(T) == 2, rows, D)) return s;  // diag_ell: k_max is w
-  if (int s = encode_rows(&p.tm_kmin, DIAG ? p.k_max : p.k_min, sizeof(T) == 2, rows, D)) return s;
+  // diag_ell: k_max is w; packed range: k_max is the array of (k_max, k_min) pairs, rows of 2 D elements
+  if (int s = encode_rows(&p.tm_kmax, p.k_max, sizeof(T) == 2, rows, PACKED ? 2 * D : D)) return s;
+  if constexpr (DIAG || PACKED) p.tm_kmin = p.tm_kmax;  // not read
+  else if (int s = encode_rows(&p.tm_kmin, p.k_min, sizeof(T) == 2, rows, D)) return s;
 
   // Narrow shape: more pairs than SMs and room for two or three CTAs per SM (each CTA pays 1 KB of
   // reserved shared memory) with a ring of at least two stages.  A cluster of narrow CTAs per pair
@@ -1910,7 +1962,7 @@ static int launch_typed(const SelectParams& base, const AttendRequest& ar, int n
         p.n_stages = stages;
         // the one-kernel step turns the rest of the CTA's share of shared memory into page stages
         const size_t ring = ar.req != nullptr ? ((budget - fixed) & ~(size_t)1023) : (size_t)stages * L::bytes;
-        return launch_shaped<T, D, G, kNarrowGroups, KB, DIAG>(p, ar, n_pairs, fixed + ring, ring, sms * ctas, stream);
+        return launch_shaped<T, D, G, kNarrowGroups, KB, BOUND>(p, ar, n_pairs, fixed + ring, ring, sms * ctas, stream);
       }
       break;  // the narrow shape is only ever tried with the cluster chosen above (1 unless pinned)
     }
@@ -1925,25 +1977,30 @@ static int launch_typed(const SelectParams& base, const AttendRequest& ar, int n
   if (stages > kMaxStages) stages = kMaxStages;
   p.n_stages = stages;
   const size_t ring = ar.req != nullptr ? (((size_t)max_smem - fixed) & ~(size_t)1023) : (size_t)stages * L::bytes;
-  return launch_shaped<T, D, G, kWideGroups, KB, DIAG>(p, ar, n_pairs, fixed + ring, ring, sms, stream);
+  return launch_shaped<T, D, G, kWideGroups, KB, BOUND>(p, ar, n_pairs, fixed + ring, ring, sms, stream);
 }
 
-template <typename T, int D, typename KB, bool DIAG>
+template <typename T, int D, typename KB, int BOUND>
 static int launch_group_bound(const SelectParams& p, const AttendRequest& ar, int n_pairs, int group,
                               cudaStream_t stream) {
   switch (group) {
-    case 1: return launch_typed<T, D, 1, KB, DIAG>(p, ar, n_pairs, stream);
-    case 2: return launch_typed<T, D, 2, KB, DIAG>(p, ar, n_pairs, stream);
-    case 4: return launch_typed<T, D, 4, KB, DIAG>(p, ar, n_pairs, stream);
-    case 8: return launch_typed<T, D, 8, KB, DIAG>(p, ar, n_pairs, stream);
-    case 16: return launch_typed<T, D, 16, KB, DIAG>(p, ar, n_pairs, stream);
+    case 1: return launch_typed<T, D, 1, KB, BOUND>(p, ar, n_pairs, stream);
+    case 2: return launch_typed<T, D, 2, KB, BOUND>(p, ar, n_pairs, stream);
+    case 4: return launch_typed<T, D, 4, KB, BOUND>(p, ar, n_pairs, stream);
+    case 8: return launch_typed<T, D, 8, KB, BOUND>(p, ar, n_pairs, stream);
+    case 16: return launch_typed<T, D, 16, KB, BOUND>(p, ar, n_pairs, stream);
     default: return fail(IA_ERR_UNSUPPORTED, "select: group_size %d not built (1, 2, 4, 8, 16)", group);
   }
 }
 template <typename T, int D, typename KB = float>
+static int launch_group_packed(const SelectParams& p, const AttendRequest& ar, int n_pairs, int group,
+                               cudaStream_t stream) {
+  return launch_group_bound<T, D, KB, 2>(p, ar, n_pairs, group, stream);
+}
+template <typename T, int D, typename KB = float>
 static int launch_group(const SelectParams& p, const AttendRequest& ar, int n_pairs, int group, cudaStream_t stream) {
-  return p.rho != nullptr ? launch_group_bound<T, D, KB, true>(p, ar, n_pairs, group, stream)
-                          : launch_group_bound<T, D, KB, false>(p, ar, n_pairs, group, stream);
+  return p.rho != nullptr ? launch_group_bound<T, D, KB, 1>(p, ar, n_pairs, group, stream)
+                          : launch_group_bound<T, D, KB, 0>(p, ar, n_pairs, group, stream);
 }
 
 }  // namespace

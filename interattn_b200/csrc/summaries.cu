@@ -18,6 +18,29 @@
 
 namespace ia {
 
+// k_max / k_min of a lane's VEC coordinates: two arrays, or - IA_GEOM_PACKED_BOUNDS - one array of
+// (k_max[d], k_min[d]) pairs (the reference's packed k_bounds, IMPL/core.py:490-499)
+template <typename T, int VEC>
+__device__ __forceinline__ void store_bounds(const ia_geom& g, const ia_summaries& out, int64_t row,
+                                             const float (&kmax)[VEC], const float (&kmin)[VEC]) {
+  if (g.reserved & IA_GEOM_PACKED_BOUNDS) {
+    float both[2 * VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) { both[2 * i] = kmax[i]; both[2 * i + 1] = kmin[i]; }
+    T* dst = reinterpret_cast<T*>(out.k_max) + 2 * row;
+    if constexpr (VEC == 4) {
+      float lo[4] = {both[0], both[1], both[2], both[3]}, hi[4] = {both[4], both[5], both[6], both[7]};
+      store_vec<4>(dst, lo);
+      store_vec<4>(dst + 4, hi);
+    } else {
+      store_vec<2 * VEC>(dst, both);
+    }
+  } else {
+    store_vec<VEC>(reinterpret_cast<T*>(out.k_max) + row, kmax);
+    store_vec<VEC>(reinterpret_cast<T*>(out.k_min) + row, kmin);
+  }
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(128)
 condition_block_build_summaries_direct_kernel(const T* __restrict__ k_pool, const T* __restrict__ v_pool,
@@ -87,8 +110,7 @@ condition_block_build_summaries_direct_kernel(const T* __restrict__ k_pool, cons
   else
     store_vec<VEC>(out.k_bar + row, kb);
   store_vec<VEC>(reinterpret_cast<T*>(out.v_bar) + row, vb);
-  store_vec<VEC>(reinterpret_cast<T*>(out.k_max) + row, kmax);
-  store_vec<VEC>(reinterpret_cast<T*>(out.k_min) + row, kmin);
+  store_bounds<T, VEC>(g, out, row, kmax, kmin);
   if (lane == 0) out.v_norm_max[unit] = sqrtf(vn2max);
   if (out.w == nullptr || out.rho == nullptr) return;
 
@@ -360,8 +382,7 @@ condition_block_build_summaries_kernel(const T* __restrict__ k_pool, const T* __
     else
       store_vec<VEC>(out.k_bar + row, kb);
     store_vec<VEC>(reinterpret_cast<T*>(out.v_bar) + row, vb);
-    store_vec<VEC>(reinterpret_cast<T*>(out.k_max) + row, kmax);
-    store_vec<VEC>(reinterpret_cast<T*>(out.k_min) + row, kmin);
+    store_bounds<T, VEC>(g, out, row, kmax, kmin);
     vn2max = warp_max(vn2max);
     if (lane == 0) out.v_norm_max[unit] = sqrtf(vn2max);
     if (out.w == nullptr || out.rho == nullptr) continue;

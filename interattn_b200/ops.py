@@ -51,6 +51,10 @@ def _geom_flags(summ, bound: str = "range") -> int:
     if bound not in ("range", "diag_ell"):
         raise ValueError("bound must be 'range' or 'diag_ell'")
     flags = _lib.IA_GEOM_KBAR_BF16 if summ is not None and summ.k_bar.dtype == torch.bfloat16 else 0
+    if summ is not None and summ.k_bounds is not None:
+        if bound == "diag_ell":
+            raise ValueError("summaries with the packed range layout do not carry the diag_ell pair")
+        flags |= _lib.IA_GEOM_PACKED_BOUNDS
     if bound == "diag_ell":
         if summ is None or summ.w is None or summ.rho is None:
             raise ValueError("the diag_ell bound needs summaries built with diag_ell=True (w and rho)")
@@ -127,12 +131,18 @@ class BlockSummaries:
     # optional diagonal-ellipsoid pair (the reference's condition_block_ball "diag_ell" bound):
     w: Optional[torch.Tensor] = None     # [B, Hkv, nb, D] KV dtype, max_t |k_t - k_bar| (rounded up in bf16)
     rho: Optional[torch.Tensor] = None   # [B, Hkv, nb] f32, max_t |(k_t - k_bar) / w|
+    # optional packed range (the reference's CONDITION_BLOCK_TMA_BOUNDS layout, IMPL/core.py:490-499):
+    # [B, Hkv, nb, 2 D] with (k_max[d], k_min[d]) pairs; k_max / k_min are then strided views into it
+    k_bounds: Optional[torch.Tensor] = None
 
     @property
     def max_blocks(self) -> int:
         return int(self.k_bar.shape[2])
 
     def c_struct(self) -> Summaries:
+        if self.k_bounds is not None:  # the kernels read the packed array through the k_max member; k_min is unused
+            return Summaries(self.k_bar.data_ptr(), self.k_bounds.data_ptr(), None, self.v_bar.data_ptr(),
+                             self.v_norm_max.data_ptr(), None, None)
         return Summaries(self.k_bar.data_ptr(), self.k_max.data_ptr(), self.k_min.data_ptr(),
                          self.v_bar.data_ptr(), self.v_norm_max.data_ptr(),
                          None if self.w is None else self.w.data_ptr(),
@@ -140,14 +150,20 @@ class BlockSummaries:
 
     @staticmethod
     def empty(batch: int, n_kv_heads: int, max_blocks: int, head_dim: int, dtype: torch.dtype, device,
-              block_size: int, k_bar_dtype: torch.dtype = torch.float32, diag_ell: bool = False) -> "BlockSummaries":
+              block_size: int, k_bar_dtype: torch.dtype = torch.float32, diag_ell: bool = False,
+              packed_bounds: bool = False) -> "BlockSummaries":
         shape = (batch, n_kv_heads, max_blocks, head_dim)
         if k_bar_dtype not in (torch.float32, torch.bfloat16) or (k_bar_dtype != torch.float32 and dtype != torch.bfloat16):
             raise ValueError("k_bar is float32, or bfloat16 next to bfloat16 pools")
+        if packed_bounds and diag_ell:
+            raise ValueError("the packed range layout and the diag_ell pair exclude one another")
+        k_bounds = torch.zeros(shape[:3] + (2 * head_dim,), device=device, dtype=dtype) if packed_bounds else None
+        pairs = k_bounds.view(*shape, 2) if packed_bounds else None
         return BlockSummaries(
             k_bar=torch.zeros(shape, device=device, dtype=k_bar_dtype),
-            k_max=torch.zeros(shape, device=device, dtype=dtype),
-            k_min=torch.zeros(shape, device=device, dtype=dtype),
+            k_max=pairs[..., 0] if packed_bounds else torch.zeros(shape, device=device, dtype=dtype),
+            k_min=pairs[..., 1] if packed_bounds else torch.zeros(shape, device=device, dtype=dtype),
+            k_bounds=k_bounds,
             v_bar=torch.zeros(shape, device=device, dtype=dtype),
             v_norm_max=torch.zeros(shape[:3], device=device, dtype=torch.float32),
             block_size=int(block_size),
@@ -158,8 +174,12 @@ class BlockSummaries:
 def build_summaries(kv: PagedKV, block_size: int, max_blocks: Optional[int] = None,
                     out: Optional[BlockSummaries] = None,
                     first_blocks: Optional[torch.Tensor] = None,
-                    k_bar_dtype: torch.dtype = torch.float32, diag_ell: bool = False) -> BlockSummaries:
+                    k_bar_dtype: torch.dtype = torch.float32, diag_ell: bool = False,
+                    packed_bounds: bool = False) -> BlockSummaries:
     """Block summaries of every sequence's prefix (reference: ``_build_prompt_blocks``).
+    ``packed_bounds=True`` stores the coordinate range as the reference does with
+    ``CONDITION_BLOCK_TMA_BOUNDS=1`` (``IMPL/core.py:490-499``): one array ``k_bounds`` of ``(k_max[d], k_min[d])``
+    pairs, ``k_max`` / ``k_min`` being strided views into it; the selection reads that layout directly.
     ``diag_ell=True`` also keeps the diagonal-ellipsoid pair ``w, rho`` (the reference's
     ``condition_block_ball`` bound; ``select_blocks(..., bound="diag_ell")`` then reads two vectors and a
     scalar per block instead of three vectors).
@@ -185,7 +205,7 @@ def build_summaries(kv: PagedKV, block_size: int, max_blocks: Optional[int] = No
             1, (int(kv.block_table.shape[1]) * kv.page_size + block_size - 1) // block_size)
     if out is None:
         out = BlockSummaries.empty(kv.batch, kv.n_kv_heads, max_blocks, kv.head_dim, kv.k_pool.dtype,
-                                   kv.k_pool.device, block_size, k_bar_dtype, diag_ell)
+                                   kv.k_pool.device, block_size, k_bar_dtype, diag_ell, packed_bounds)
     g = kv.geom(1, block_size, max_blocks, out)
     s = out.c_struct()
     check(lib.ia_build_summaries(_ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.block_table), _ptr(kv.prefix_lens),

@@ -132,7 +132,10 @@ def _build_prompt_blocks(k_all: torch.Tensor, v_all: torch.Tensor, block_size: i
         raise ValueError(f"CONDITION_BLOCK_K_BAR_DTYPE must be float32 or bfloat16, got {k_bar_name!r}.")
     if k_bar_name != "float32" and k_all.dtype != torch.bfloat16:
         raise ValueError("CONDITION_BLOCK_K_BAR_DTYPE=bfloat16 needs bfloat16 keys and values.")
-    summ = ops.BlockSummaries.empty(1, hkv, nb, d, k_all.dtype, dev, block_size, getattr(torch, k_bar_name))
+    # the reference's switch for the packed coordinate range (core.py:490-499)
+    packed = os.environ.get("CONDITION_BLOCK_TMA_BOUNDS") == "1"
+    summ = ops.BlockSummaries.empty(1, hkv, nb, d, k_all.dtype, dev, block_size, getattr(torch, k_bar_name),
+                                    packed_bounds=packed)
     g = geometry.geom(k_all, 1, block_size, nb, summ)
     s = summ.c_struct()
     check(lib.ia_build_summaries(ctypes.c_void_p(k_all.data_ptr()), ctypes.c_void_p(v_all.data_ptr()),
@@ -166,6 +169,10 @@ def _build_prompt_blocks(k_all: torch.Tensor, v_all: torch.Tensor, block_size: i
         "block_valid_counts": counts,
         "_b200": _PrefixHandle(k_all, v_all, block_size, summ, geometry),
     }
+    if packed:  # as the reference: the packed array, and k_max / k_min as views into it (no duplicate storage)
+        prefix["k_bounds"] = summ.k_bounds[0, :, :n_real]
+        pairs = prefix["k_bounds"].view(hkv, n_real, d, 2)
+        prefix["k_max"], prefix["k_min"] = pairs[..., 0], pairs[..., 1]
     return prefix
 
 

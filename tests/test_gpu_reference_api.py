@@ -115,6 +115,37 @@ def test_select_and_stats_shims():
         api._select_prompt_blocks(q.to(DEV), {"k_bar": None}, 0.1)
 
 
+def test_packed_bounds_switch_of_the_reference(monkeypatch):
+    """CONDITION_BLOCK_TMA_BOUNDS=1 (IMPL/core.py:490-499): the prefix carries ``k_bounds`` = stack((k_max, k_min),
+    -1).flatten(2) and k_max / k_min become views into it; selection and the fused decode give what they give
+    from two arrays."""
+    api = _api()
+    hkv, g, d, block, length = 4, 4, 128, 64, 1500
+    k, v = _cache(hkv, length + 8, d, torch.bfloat16, 2)
+    kd, vd = k.to(DEV), v.to(DEV)
+    q = torch.randn((hkv, g, 1, d), generator=torch.Generator().manual_seed(3)).bfloat16().to(DEV)
+    monkeypatch.setenv("CONDITION_BLOCK_MIXED_SUMMARIES", "1")
+    plain = api._build_prompt_blocks(kd[:, :length], vd[:, :length], block)
+    monkeypatch.setenv("CONDITION_BLOCK_TMA_BOUNDS", "1")
+    packed = api._build_prompt_blocks(kd[:, :length], vd[:, :length], block)
+    assert "k_bounds" in packed and "k_bounds" not in plain
+    want = torch.stack((plain["k_max"], plain["k_min"]), dim=-1).flatten(2)
+    assert torch.equal(packed["k_bounds"], want)
+    assert torch.equal(packed["k_max"], plain["k_max"]) and torch.equal(packed["k_min"], plain["k_min"])
+    assert packed["k_max"].data_ptr() == packed["k_bounds"].data_ptr()  # views, no duplicate storage
+    eps = 1e-3
+    sel_p = api._select_prompt_blocks(q, packed, eps)[0]
+    sel = api._select_prompt_blocks(q, plain, eps)[0]
+    assert torch.equal(sel_p, sel)
+    n_suffix = torch.tensor(5, device=DEV, dtype=torch.int32)
+    outs = [api._condition_block_decode_output_fused_triton(
+        q_grouped=q, prompt_prefix=prefix, k_suffix=kd[:, length:], v_suffix=vd[:, length:], suffix_len_dev=n_suffix,
+        eps=eps, page_size=block, store_selected=True, output_dtype=torch.bfloat16, workspace={})
+        for prefix in (packed, plain)]
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
 SANITY = [(4096, 1, 0.0), (4099, 33, 0.0), (4096, 1, 1e6), (4099, 33, 1e6)]
 
 
