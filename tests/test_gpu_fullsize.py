@@ -146,3 +146,30 @@ def test_full_size_properties_and_sampled_parity(name, cfg, sample, n_summary_ch
             want = orc.decode_attention(qg, k_all, v_all, plen, cfg.block_size, mask, rep_mode=rep_mode,
                                         z=terms["z"], v_bar=osum.v_bar)
             torch.testing.assert_close(got[b].cpu().reshape(want.shape), want, rtol=1e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("name", ["cfg2_llama8b_32k", "cfg3_layer_llama8b_8k", "cfg4_longctx_128k"])
+@pytest.mark.parametrize("rep_mode", ["sparse_only", "hybrid"])
+def test_full_size_one_kernel_step_repeats_bit_for_bit(name, rep_mode):
+    """The one-kernel step at full size (wide, narrow and cluster shapes), sixty launches back to back and a second
+    pool in between: every warp owns fixed pages and merges happen in a fixed order, so any difference between two
+    launches on the same inputs would be a race (a stage refilled while it is read, a barrier phase out of step)."""
+    from interattn_b200 import ops
+    cfg = CONFIGS[name]
+    q, kv = _device_case(cfg)
+    q2, kv2 = _device_case(cfg, seed=1)
+    nb = max((n + cfg.block_size - 1) // cfg.block_size for n in cfg.prefix_lens)
+    steps = [ops.DecodeAttention(c, ops.build_summaries(c, cfg.block_size, max_blocks=nb), cfg.n_q_heads,
+                                 top_k=cfg.top_k, rep_mode=rep_mode) for c in (kv, kv2)]
+    first = steps[0].step(q).clone()
+    idx = steps[0].sel_idx.clone()
+    assert ops.last_decode_fused(), "these workloads take the one-kernel form"
+    same = torch.ones((), dtype=torch.bool, device=q.device)
+    for i in range(60):
+        if i % 3 == 2:
+            steps[1].step(q2)  # other pages through the same shared memory and L2
+        out = steps[0].step(q)
+        same &= (out == first).all() & (steps[0].sel_idx == idx).all()
+    torch.cuda.synchronize()
+    assert bool(same)
+    assert ops.device_status() == 0
