@@ -381,7 +381,7 @@ __device__ __forceinline__ const E* swz(const unsigned char* vec_base, int row, 
 // Fixed shared-memory carve-up (bytes), shared by the kernel and the launcher.
 template <int D, int G, bool MMA, int NG> struct SmemPlan {
   static constexpr int kWarps = Shape<NG>::warps, kConsumerWarps = Shape<NG>::consumer_warps;
-  static constexpr size_t bars = 2 * kMaxStages * 8;
+  static constexpr size_t bars = 4 * kMaxStages * 8;  // full / empty of the ring, and of the second pass's ring
   static constexpr size_t hist = 3 * 256 * 4;
   static constexpr size_t scan = 32 * 4;
   static constexpr size_t red = (size_t)kWarps * 16 * 3 * 4 + (size_t)kWarps * 4 + 12;  // [warp][row][m,l,d] + b_max per warp
@@ -756,8 +756,14 @@ __device__ __forceinline__ void attend_selected_pages(const SelectParams& p, int
   IA_TRACE(14);
 }
 
-template <typename T, int D, int G, int NG, typename KB, int BOUND, bool FUSE>
+template <typename T, int D, int G, int NG, typename KB, int BOUND, bool FUSE, bool TWOPASS = false>
 __device__ __forceinline__ void select_body(const SelectParams& p) {
+  // TWOPASS: no per-(row, block) state.  The first pass over the summaries only forms the row normalisers;
+  // a second pass over the same tiles (out of L2) scores every block again and turns it into its condition
+  // score at once.  The CTA then needs a few KB per thousand blocks instead of 8 G bytes per block, so that
+  // long sequences with eight query rows per kv head still fit two narrow CTAs per SM.
+  static_assert(!TWOPASS || (kUseMma<T, G> && BOUND == 0 && !FUSE && NG == kNarrowGroups),
+                "the two-pass form is built for the narrow tensor-core shape and the range bound");
   // BOUND: 0 = coordinate range from two arrays, 1 = diagonal ellipsoid (w, rho), 2 = coordinate range from the
   // packed array of (k_max[d], k_min[d]) pairs (same stage layout as 0: the pairs fill the two bound vectors' space)
   constexpr bool DIAG = BOUND == 1, PACKED = BOUND == 2;
@@ -845,7 +851,9 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
   // ---- shared memory carve-up -------------------------------------------------
   unsigned char* sp = smem_raw;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(sp);
-  uint64_t* empty_bar = full_bar + kMaxStages;         sp += P::bars;
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* full_bar2 = empty_bar + kMaxStages;        // second pass (TWOPASS)
+  uint64_t* empty_bar2 = full_bar2 + kMaxStages;       sp += P::bars;
   int* hist = reinterpret_cast<int*>(sp);              sp += P::hist;   // three rotating 256-bin histograms
   int* scan_scratch = reinterpret_cast<int*>(sp);      sp += P::scan;
   float* red_s = reinterpret_cast<float*>(sp);                          // [kWarps][16][3] row normalisers
@@ -861,16 +869,16 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
   float* score_s = vn_s + nb_cap;                                       // [nb_cap]
   float* rho_s = score_s + nb_cap;                                      // [nb_cap] (diag_ell bound only)
   float* z_s = rho_s + nb_cap;                                          // [G][nbl]: z = s + log count (own blocks)
-  float* d_s = z_s + (size_t)G * nbl;                                   // [G][nbl]: delta (range bound)
+  float* d_s = z_s + (TWOPASS ? 0 : (size_t)G * nbl);                   // [G][nbl]: delta (range bound)
   // split-KV: the ranks' top-k candidates, gathered: [n_ranks * max_sel] scores and block indices
-  float* cand_s = d_s + (size_t)G * nbl;
+  float* cand_s = d_s + (TWOPASS ? 0 : (size_t)G * nbl);
   int* candb_s = reinterpret_cast<int*>(cand_s + (xch_on ? p.xch.n_ranks * p.max_sel : 0));
   unsigned char* stage_base = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(candb_s + (xch_on ? p.xch.n_ranks * p.max_sel : 0)) + 1023) & ~uintptr_t(1023));
 
   const int64_t sum_row0 = (int64_t)pair * p.max_blocks;  // first summary row of this pair
   // one ring stage: the TMA box copies of 32 blocks' summaries, completing on the stage's barrier
-  auto issue_tile = [&](int lt) {
+  auto issue_tile_on = [&](int lt, uint64_t* full_bar) {
     const int stage = lt % n_stages;
     unsigned char* st = stage_base + (size_t)stage * L::bytes;
     const int y = (int)sum_row0 + (t_lo + lt) * kTileBlocks;  // rows past the array are zero-filled by the TMA unit
@@ -892,6 +900,7 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
       }
     }
   };
+  auto issue_tile = [&](int lt) { issue_tile_on(lt, full_bar); };
   // The producer lane owns the barriers: it initialises them and fills the ring's first uses while
   // the other warps still fetch the query and the value norms - the summaries are on their way
   // before the CTA's set-up barrier.  The consumers touch the barriers only after that barrier.
@@ -905,6 +914,10 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
       for (int s = 0; s < n_stages; ++s) {
         mbar_init(&full_bar[s], 1);
         mbar_init(&empty_bar[s], kUseMma<T, G> ? 2 : kGroupWarps);
+        if constexpr (TWOPASS) {
+          mbar_init(&full_bar2[s], 1);
+          mbar_init(&empty_bar2[s], 2);
+        }
       }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       for (int lt = 0; lt < n_primed; ++lt) issue_tile(lt);
@@ -1129,8 +1142,10 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
           float ch, a_term, th;
           delta_terms(delta, p.mass_exp, ch, a_term, th);
           norm_absorb(acc, z, ch);
-          z_s[g * nbl + b - b_lo] = z;
-          d_s[g * nbl + b - b_lo] = delta;  // the score phase recomputes cosh - 1 and tanh from it
+          if constexpr (!TWOPASS) {
+            z_s[g * nbl + b - b_lo] = z;
+            d_s[g * nbl + b - b_lo] = delta;  // the score phase recomputes cosh - 1 and tanh from it
+          }
           const int64_t o = ((int64_t)pair * G + g) * p.max_blocks + b;
           if (p.aux.s != nullptr) p.aux.s[o] = s;
           if (p.aux.z != nullptr) p.aux.z[o] = z;
@@ -1445,7 +1460,182 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
   // cond = softmax(z) (2 b_all (cosh d - 1) / denom + 2 b_c tanh(d / 2))   (IMPL/core.py:535-544)
   // Each CTA scores its own blocks and delivers the scores to rank 0 of the cluster,
   // which routes for the whole (sequence, kv head).
-  {
+  if constexpr (TWOPASS) {
+    // Second pass (C == 1, no exchange): the tiles come through the ring once more - out of L2, this CTA has
+    // just streamed them - on a second pair of barriers; s, delta and z are formed again, value for value,
+    // and go straight into the block's score.  The four lanes of a quad hold the rows of a block; the
+    // terms are gathered and added in row order, which is the order of the one-pass form.
+    if (warp == kConsumerWarps) {
+      const int n_first = min(n_stages, n_my_tiles);
+      if (lane == 0)
+        for (int lt = 0; lt < n_first; ++lt) issue_tile_on(lt, full_bar2);
+      __syncwarp();
+      bool alive = true;
+      for (int lt = n_first; lt < n_my_tiles; ++lt) {
+        const int stage = lt % n_stages, use = lt / n_stages;
+        if (alive && !mbar_wait(&empty_bar2[stage], (uint32_t)((use - 1) & 1))) {
+          alive = false;
+          if (lane == 0) atomicOr(p.status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
+        }
+        if (lane == 0) issue_tile_on(lt, full_bar2);
+        __syncwarp();
+      }
+    } else {
+      const int mh = warp & 1, slot = warp >> 1;
+      const int n = lane >> 2, kq = lane & 3;
+      uint32_t bq[D / 8][2], bp[D / 16][2], bm[D / 16][2];
+#pragma unroll
+      for (int kk = 0; kk < D / 8; ++kk) {
+        bq[kk][0] = n < G ? __float_as_uint(q_s[n * D + kk * 8 + kq]) : 0u;
+        bq[kk][1] = n < G ? __float_as_uint(q_s[n * D + kk * 8 + kq + 4]) : 0u;
+      }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float x0 = n < G ? q_s[n * D + kk * 16 + h * 8 + kq * 2] : 0.f;
+          const float x1 = n < G ? q_s[n * D + kk * 16 + h * 8 + kq * 2 + 1] : 0.f;
+          bp[kk][h] = pack_bf16(fmaxf(x0, 0.f), fmaxf(x1, 0.f));
+          bm[kk][h] = pack_bf16(fminf(x0, 0.f), fminf(x1, 0.f));
+        }
+      }
+      const int lm = lane >> 3, lr = lane & 7;
+      const int arow = mh * 16 + (lm & 1) * 8 + lr;
+      const uint32_t row_off = (uint32_t)(arow * 128);
+      const uint32_t row_xor = (uint32_t)(arow & 7);
+      const unsigned quad_base = (unsigned)(lane & ~3);
+      bool alive = true;
+      for (int lt = slot; slot < n_slots && lt < n_my_tiles; lt += n_slots) {
+        const int t = t_lo + lt;
+        const int stage = lt % n_stages, use = lt / n_stages;
+        if (alive && !mbar_wait(&full_bar2[stage], (uint32_t)(use & 1))) {
+          alive = false;
+          if (lane == 0) atomicOr(p.status, DEV_STATUS_SELECT_WAIT_TIMEOUT);
+        }
+        const uint32_t st = smem_u32(stage_base + (size_t)stage * L::bytes);
+        float cd[4] = {0.f, 0.f, 0.f, 0.f};
+        float xp[4] = {0.f, 0.f, 0.f, 0.f}, xm[4] = {0.f, 0.f, 0.f, 0.f};
+        float np_[4] = {0.f, 0.f, 0.f, 0.f}, nm[4] = {0.f, 0.f, 0.f, 0.f};
+        if constexpr (sizeof(KB) == 4) {
+#pragma unroll
+          for (int kk = 0; kk < D / 8; ++kk) {
+            const int byte = (kk * 8 + (lm >> 1) * 4) * 4;
+            uint32_t a[4], hi[4], md[4], lo[4];
+            ldmatrix_x4(st + (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4), a);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              hi[i] = a[i] & 0xffffe000u;
+              const float r1 = __uint_as_float(a[i]) - __uint_as_float(hi[i]);
+              md[i] = __float_as_uint(r1) & 0xffffe000u;
+              lo[i] = __float_as_uint(r1 - __uint_as_float(md[i]));
+            }
+            mma_tf32(cd, hi, bq[kk]);
+            mma_tf32(cd, md, bq[kk]);
+            mma_tf32(cd, lo, bq[kk]);
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const int byte = (kk * 16 + (lm >> 1) * 8) * 2;
+            uint32_t a[4];
+            ldmatrix_x4(st + (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4), a);
+            mma_bf16(cd, a, bp[kk]);
+            mma_bf16(cd, a, bm[kk]);
+          }
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const int byte = (kk * 16 + (lm >> 1) * 8) * 2;
+          const uint32_t off = (byte >> 7) * L::box_bytes + row_off + ((((byte >> 4) & 7) ^ row_xor) << 4);
+          uint32_t a[4];
+          ldmatrix_x4(st + L::kbar_bytes + off, a);
+          mma_bf16(xp, a, bp[kk]);
+          mma_bf16(xm, a, bm[kk]);
+          ldmatrix_x4(st + L::kbar_bytes + L::bnd_bytes + off, a);
+          mma_bf16(np_, a, bp[kk]);
+          mma_bf16(nm, a, bm[kk]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar2[stage]);
+        // one (row, block) entry -> its term of the block's score (0 where there is no such row or block)
+        auto term = [&](int g, int b, float dotv, float up, float lw) -> float2 {
+          if (g >= G || b >= nb) return make_float2(0.f, 0.f);
+          const int count = min(p.block_size, prefix - b * p.block_size);
+          const float s = dotv / root;
+          const float upper = up / root, lower = lw / root;
+          const float delta = fmaxf(fabsf(upper - s), fabsf(lower - s));
+          const float z = (count == p.block_size ? log_full : logf((float)count)) + s;
+          const float pm = expf(z - norm_s[g]) * norm_s[16 + g];
+          float ch, a_term, th;
+          delta_terms(delta, p.mass_exp, ch, a_term, th);
+          const float two_bc = 2.f * vn_s[b];
+          return make_float2(pm, fmaf(norm_s[32 + g], a_term, two_bc * th));  // the row adds pm * (...) to the score
+        };
+        const int b0 = t * kTileBlocks + mh * 16 + n;
+        if constexpr (G <= 4) {
+          // as in the first pass: lane kq finishes rows 2 (kq & 1) + {0, 1} of block b0 + 8 (kq >> 1)
+          float2 tv[2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const float d2 = __shfl_xor_sync(0xffffffffu, cd[2 + j], 2);
+            const float u2 = __shfl_xor_sync(0xffffffffu, xp[2 + j] + nm[2 + j], 2);
+            const float l2 = __shfl_xor_sync(0xffffffffu, np_[2 + j] + xm[2 + j], 2);
+            const float dv = kq < 2 ? cd[j] : d2;
+            const float up = kq < 2 ? xp[j] + nm[j] : u2;
+            const float lw = kq < 2 ? np_[j] + xm[j] : l2;
+            tv[j] = term((kq & 1) * 2 + j, b0 + (kq >> 1) * 8, dv, up, lw);
+          }
+          // rows 0, 1 sit in lane 2 h, rows 2, 3 in lane 2 h + 1 of the quad (h = block half)
+          const unsigned src = quad_base + (unsigned)(kq & 2);
+          float sum = 0.f;
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const float pm = __shfl_sync(0xffffffffu, tv[j].x, src + r), f = __shfl_sync(0xffffffffu, tv[j].y, src + r);
+              if (2 * r + j < G) sum = fmaf(pm, f, sum);
+            }
+          }
+          const int b = b0 + (kq >> 1) * 8;
+          if ((kq & 1) == 0 && b < nb) {
+            const float sc = sum / (float)G;
+            score_s[b] = sc;
+            if (p.aux.score != nullptr) p.aux.score[(int64_t)pair * p.max_blocks + b] = sc;
+          }
+        } else {
+          // lane kq holds rows 2 kq, 2 kq + 1 of the blocks b0 and b0 + 8
+          float2 tv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            tv[e] = term(kq * 2 + (e & 1), b0 + (e >> 1) * 8, cd[e], xp[e] + nm[e], np_[e] + xm[e]);
+          float sum[2] = {0.f, 0.f};
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const float pm = __shfl_sync(0xffffffffu, tv[2 * h + j].x, quad_base + r);
+                const float f = __shfl_sync(0xffffffffu, tv[2 * h + j].y, quad_base + r);
+                if (2 * r + j < G) sum[h] = fmaf(pm, f, sum[h]);
+              }
+            }
+          }
+          if (kq == 0) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int b = b0 + h * 8;
+              if (b < nb) {
+                const float sc = sum[h] / (float)G;
+                score_s[b] = sc;
+                if (p.aux.score != nullptr) p.aux.score[(int64_t)pair * p.max_blocks + b] = sc;
+              }
+            }
+          }
+        }
+      }
+    }
+  } else {
     const uint32_t score_r0 = map_to_rank(score_s, 0u);
     for (int b = b_lo + tid; b < b_hi; b += kThreads) {
       const float two_bc = 2.f * vn_s[b];
@@ -1455,7 +1645,7 @@ __device__ __forceinline__ void select_body(const SelectParams& p) {
         const float pm = expf(z_s[g * nbl + b - b_lo] - norm_s[g]) * norm_s[16 + g];
         float ch, a_term, th;
         delta_terms(d_s[g * nbl + b - b_lo], p.mass_exp, ch, a_term, th);
-        sum += pm * fmaf(norm_s[32 + g], a_term, two_bc * th);
+        sum = fmaf(pm, fmaf(norm_s[32 + g], a_term, two_bc * th), sum);  // written out: the two-pass form adds the same way
       }
       const float sc = sum / (float)G;
       if (C == 1) score_s[b] = sc;
@@ -1723,6 +1913,16 @@ condition_block_select_attend_kernel(const __grid_constant__ SelectParams p) {
   select_body<__nv_bfloat16, D, G, NG, KB, BOUND, true>(p);
 }
 
+// The selection without per-(row, block) state (see TWOPASS in select_body): narrow CTAs for sequences whose
+// (z, delta) arrays would not leave room for two CTAs per SM.  bf16 pools, at most eight query rows per kv
+// head, the range bound from two arrays.
+template <int D, int G, typename KB>
+__global__ void __launch_bounds__(Shape<kNarrowGroups>::threads, 2)
+condition_block_select_twopass_kernel(const __grid_constant__ SelectParams p) {
+  select_body<__nv_bfloat16, D, G, kNarrowGroups, KB, 0, false, true>(p);
+}
+
+
 // cuTensorMapEncodeTiled lives in the driver library; fetch it through the
 // runtime so that the shared library links against cudart only.
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1874,15 +2074,19 @@ static bool try_launch_fused(SelectParams& p, const AttendRequest& ar, int n_pai
   }
 }
 
-template <typename T, int D, int G, int NG, typename KB, int BOUND>
-static int launch_shaped(SelectParams& p, const AttendRequest& ar, int n_pairs, size_t smem, size_t ring_bytes,
-                         int resident_ctas, cudaStream_t stream) {
-  int status = IA_OK;
+static bool select_in_index_order() {
   static const bool in_order = [] {
     const char* v = getenv("INTERATTN_B200_SELECT_ORDER");
     return v != nullptr && strcmp(v, "index") == 0;
   }();
-  p.longest_first = !in_order && n_pairs * p.cluster > resident_ctas && n_pairs / p.n_kv_heads <= 4096;
+  return in_order;
+}
+
+template <typename T, int D, int G, int NG, typename KB, int BOUND>
+static int launch_shaped(SelectParams& p, const AttendRequest& ar, int n_pairs, size_t smem, size_t ring_bytes,
+                         int resident_ctas, cudaStream_t stream) {
+  int status = IA_OK;
+  p.longest_first = !select_in_index_order() && n_pairs * p.cluster > resident_ctas && n_pairs / p.n_kv_heads <= 4096;
   if (try_launch_fused<T, D, G, NG, KB, BOUND>(p, ar, n_pairs, smem, ring_bytes, resident_ctas, stream, &status))
     return status;
   return launch_kernel(condition_block_select_kernel<T, D, G, NG, KB, BOUND>, "condition_block_select_kernel", p,
@@ -1940,13 +2144,15 @@ static int launch_typed(const SelectParams& base, const AttendRequest& ar, int n
   // INTERATTN_B200_SELECT_SHAPE=wide|narrow (+ INTERATTN_B200_SELECT_CLUSTER) pin the choice where it fits.
   const char* shape = getenv("INTERATTN_B200_SELECT_SHAPE");
   const bool want_narrow = shape != nullptr ? strcmp(shape, "narrow") == 0 : n_pairs > sms;
+  const char* tp = getenv("INTERATTN_B200_SELECT_TWOPASS");
+  const int twopass = tp == nullptr ? 0 : atoi(tp);  // 1: the two-pass form wherever the narrow shape is wanted
   if (xch_on && (want_narrow || n_pairs * cluster > sms))
     // the CTAs of a split-KV selection wait for their peers on the other GPUs: all of them must be
     // resident at once (one wide CTA per SM), or a CTA could wait for one that is not scheduled yet
     return fail(IA_ERR_UNSUPPORTED, "select (split-KV): %d (sequence, kv head) pairs x cluster %d exceed the %d SMs",
                 n_pairs, cluster, sms);
   if (want_narrow) {
-    for (int c = cluster; c <= 8; c *= 2) {
+    for (int c = cluster; c <= 8 && twopass != 1; c *= 2) {
       p.cluster = c;
       p.nb_loc_cap = (max_tiles / c + 1) * kTileBlocks;
       const size_t fixed = PN::fixed + PN::per_blocks(p.nb_cap, p.nb_loc_cap) + 1024;
@@ -1965,6 +2171,30 @@ static int launch_typed(const SelectParams& base, const AttendRequest& ar, int n
         return launch_shaped<T, D, G, kNarrowGroups, KB, BOUND>(p, ar, n_pairs, fixed + ring, ring, sms * ctas, stream);
       }
       break;  // the narrow shape is only ever tried with the cluster chosen above (1 unless pinned)
+    }
+    // The two-pass form keeps no (z, delta) arrays and so fits two narrow CTAs per SM where the one-pass
+    // narrow shape does not (long sequences, eight query rows per kv head).  Measured on the ragged 70B
+    // batch it loses to the wide shape all the same (135.8 against 113.5 us: four consumer warps and a
+    // two-stage ring per CTA, every summary through the tensor cores twice), so it is taken on request
+    // only: INTERATTN_B200_SELECT_TWOPASS=1 (also where the one-pass narrow shape fits - A/B runs, tests).
+    if constexpr (kUseMma<T, G> && BOUND == 0 && sizeof(T) == 2) {
+      if (twopass == 1 && cluster == 1 && !xch_on) {
+        p.cluster = 1;
+        p.nb_loc_cap = (max_tiles + 1) * kTileBlocks;
+        const size_t fixed = PN::fixed + (size_t)p.nb_cap * 4 * 3 + 1024;
+        const int ctas = 2;
+        const size_t budget = (size_t)sm_smem / ctas - 1024;
+        if (budget >= fixed + 2 * (size_t)L::bytes) {
+          int stages = (int)((budget - fixed) / L::bytes);
+          if (stages > max_tiles) stages = max_tiles < 2 ? 2 : max_tiles;
+          if (stages > kMaxStages) stages = kMaxStages;
+          p.n_stages = stages;
+          p.longest_first = !select_in_index_order() && n_pairs > sms * ctas && n_pairs / p.n_kv_heads <= 4096;
+          return launch_kernel(condition_block_select_twopass_kernel<D, G, KB>, "condition_block_select_twopass_kernel",
+                               p, n_pairs, (unsigned)Shape<kNarrowGroups>::threads, fixed + (size_t)stages * L::bytes,
+                               stream);
+        }
+      }
     }
     p.cluster = cluster;  // no narrow form fits: the wide shape with the cluster chosen above
     p.nb_loc_cap = (max_tiles / cluster + 1) * kTileBlocks;
