@@ -26,11 +26,16 @@ One JSON line on rank 0:
              whole job, inputs resident in HBM (one C-ABI call per step)
   e2e        the same through the host-buffer entry point: pinned q -> device,
              the step, output -> pinned host, every step
-  roofline   the paged sparse-attention kernel: K/V bytes of the selected
-             tokens / its CUDA-event duration, against the measured HBM peak
-  hybrid, kbar_bf16   the same step in the reference's own mode (unselected
-             blocks attended through their representatives) and with the
-             block key means stored in bf16, each with its own roofline
+  roofline   the one-kernel step (selection, then paged sparse attention, in
+             one launch): block summaries read + K/V bytes of the selected
+             tokens / its CUDA-event duration, against the measured HBM peak;
+             `phases` splits that launch at the first CTA's time stamps
+  two_kernel the same step as two launches (selection, attention), each with
+             its own duration and roofline
+  hybrid, kbar_bf16, diag_ell   the same step in the reference's own mode
+             (unselected blocks attended through their representatives), with
+             the block key means stored in bf16, and with the diagonal-ellipsoid
+             bound in place of the coordinate range, each with its own roofline
   cpu_baseline  the CPU port of the reference's PyTorch path timed on this
              box's host cores on a bounded sample: its sparse (gather the
              selected tokens) and dense (score every token, then mask) legs
