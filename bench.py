@@ -28,8 +28,10 @@ One JSON line on rank 0:
              the step, output -> pinned host, every step
   roofline   the one-kernel step (selection, then paged sparse attention, in
              one launch): block summaries read + K/V bytes of the selected
-             tokens / its CUDA-event duration, against the measured HBM peak;
-             `phases` splits that launch at the first CTA's time stamps
+             tokens / its average launch duration over the timed regions
+             (which hold nothing but its launches), against the measured HBM
+             peak; `isolated_us` = events around single launches; `phases`
+             splits a launch at the first CTA's time stamps
   two_kernel the same step as two launches (selection, attention), each with
              its own duration and roofline
   hybrid, kbar_bf16, diag_ell   the same step in the reference's own mode
@@ -326,19 +328,29 @@ def kernel_times(torch, steppers, qs, K, repeats):
     return sel, att
 
 
-def kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode="sparse_only", phases=None):
+def kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode="sparse_only", phases=None,
+                   region_us=None):
     """(kernel_us, roofline, roofline_select) of a layer step.  Two kernels: the attention kernel is the
     dominant one and the selection kernel has its own record.  One fused kernel
     (condition_block_select_attend_kernel): it reads the summaries and the picked pages in one launch, so its
-    algorithmic bytes are the sum and its time is the span between the events around it."""
+    algorithmic bytes are the sum.  Its timed regions hold nothing but its launches, so its average launch
+    duration over the timed region is ``region_us`` (region / launches; programmatic launch lets a launch's
+    prologue overlap its predecessor's drain); the span between events around single launches, where nothing
+    overlaps, is kept beside it as ``isolated_us``."""
     peak, src = hbm_peak()
     if fused:
-        us = sel_us + att_us  # events 0 -> 2; nothing runs between 1 and 2
+        isolated = sel_us + att_us  # events 0 -> 2; nothing runs between 1 and 2
+        us = region_us if region_us else isolated
         gbs = (kv_bytes + sel_bytes) / (us * 1e-6) / 1e9
-        kernel_us = {"select_attend": us, "select": 0.0, "sparse_decode": 0.0, "finalize": 0.0}
+        kernel_us = {"select_attend": isolated, "select": 0.0, "sparse_decode": 0.0, "finalize": 0.0}
         roof = {"bound": "hbm", "kernel": "condition_block_select_attend_kernel", "achieved": gbs, "peak": peak,
                 "peak_source": src, "unit": "GB/s", "frac": gbs / peak,
-                "traffic": committed_traffic(workload, "select_attend"), "bytes_per_launch": kv_bytes + sel_bytes}
+                "traffic": committed_traffic(workload, "select_attend"), "bytes_per_launch": kv_bytes + sel_bytes,
+                "duration_us": us, "isolated_us": isolated,
+                "isolated_frac": (kv_bytes + sel_bytes) / (isolated * 1e-6) / 1e9 / peak,
+                "timing": ("duration = timed region / launches (the regions hold this kernel only); "
+                           "isolated = CUDA events around single launches" if region_us else
+                           "CUDA events around single launches")}
         if phases is not None and phases[0] > 0 and phases[1] > 0:
             # the kernel's own clock (time stamps of its first CTA): the latency-bound selection in front and the
             # streaming attention phase behind it, each with the bytes it moves
@@ -388,9 +400,11 @@ def _variant_record(torch, regions, cfg, layers, qs, rep_mode, kbar_bf16, summar
     fused = ops.last_decode_fused()
     phases = ops.last_step_phases() if fused else None
     kv_bytes, sel_bytes = algorithmic_bytes(cfg, rep_mode, kbar_bf16, bound)
-    kernel_us, roof, roof_sel = kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode, phases)
+    per_step = summarise(ms, K)
+    kernel_us, roof, roof_sel = kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, rep_mode, phases,
+                                               per_step["median"])
     rec = {
-        "us_per_layer": summarise(ms, K), "kernel_us": kernel_us,
+        "us_per_layer": per_step, "kernel_us": kernel_us,
         "config": {"rep_mode": rep_mode, "k_bar": "bf16" if kbar_bf16 else "f32", "bound": bound,
                    "launches_per_step": 1 if fused else 2},
         "roofline": roof,
@@ -529,7 +543,7 @@ def layer_step_record(args, workload, torch, dist, regions, world, rank, local_r
     esz = 2 if cfg.dtype == "bfloat16" else 4
     kv_bytes, sel_bytes = algorithmic_bytes(cfg, args.rep_mode, args.kbar_bf16)
     kernel_us, roof, roof_sel = kernel_records(fused, sel_us, att_us, kv_bytes, sel_bytes, workload, args.rep_mode,
-                                               phases)
+                                               phases, step_us["median"])
     q_bytes = cfg.batch * rows * cfg.head_dim * esz
     line = {
         "metric": METRIC, "value": replicas * cfg.batch / (step_us["median"] * 1e-6), "unit": UNIT,

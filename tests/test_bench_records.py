@@ -41,6 +41,12 @@ def test_kernel_records(bench, fused):
         assert kernel_us["select_attend"] == 80.0 and kernel_us["select"] == 0.0
         assert roof["bytes_per_launch"] == 268435456 + 67371008
         assert abs(roof["achieved"] - (268435456 + 67371008) / 80e-6 / 1e9) < 1e-6
+        assert roof["duration_us"] == 80.0 and roof["isolated_us"] == 80.0
+        # with the timed region's time per launch: that is the duration, the event-bracketed span stays beside it
+        _, timed, _ = bench.kernel_records(True, 30.0, 50.0, 268435456, 67371008, "cfg2_llama8b_32k", region_us=73.0)
+        assert timed["duration_us"] == 73.0 and timed["isolated_us"] == 80.0
+        assert abs(timed["achieved"] - (268435456 + 67371008) / 73e-6 / 1e9) < 1e-6
+        assert abs(timed["isolated_frac"] - roof["frac"]) < 1e-12
     else:
         assert roof["kernel"] == "condition_block_finalize_attention_kernel"
         assert abs(roof["achieved"] - 268435456 / 50e-6 / 1e9) < 1e-6
