@@ -291,5 +291,6 @@ def test_phase_stamps_of_the_last_fused_step(monkeypatch):
     torch.cuda.synchronize()
     assert ops.last_decode_fused()
     sel_us, att_us = ops.last_step_phases()
-    assert 0.5 < sel_us < 1000.0 and 0.5 < att_us < 1000.0
-    assert sel_us + att_us <= a.elapsed_time(b) * 1e3 + 1.0
+    assert 0.0 < sel_us < 1000.0 and 0.0 < att_us < 1000.0
+    # two clocks: the stamps come from the global timer (its tick may be a microsecond), the span from events
+    assert sel_us + att_us <= a.elapsed_time(b) * 1e3 + 3.0
