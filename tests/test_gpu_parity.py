@@ -200,6 +200,39 @@ def test_eps_selection(bundle):
                     assert set(got) ^ set(want) <= set(near)
 
 
+def test_eps_threshold_sweep(bundle):
+    """Routing near the threshold: the reference probes its kernels with thresholds at quantiles of the reference
+    scores so that 0.1 % ... 50 % of the blocks are selected and counts the blocks on which two implementations
+    disagree (llama/script/implementation/tensorcore_selection/benchmark.py:70-117).  Here: the selected sets of
+    the CUDA kernel and of the oracle differ at most in blocks whose score lies within the score tolerance of
+    the threshold, at every such quantile; selected counts fall as the threshold rises."""
+    ops = _ops()
+    cfg, case, q, kv, summ = bundle
+    per_seq = [_oracle_selection(cfg, case, summ, b, 1) for b in range(cfg.batch)]
+    live = torch.cat([terms["score"][:, osum.counts > 0].flatten() for osum, terms, _, _ in per_seq])
+    if live.numel() < 8:
+        pytest.skip("too few blocks for quantiles")
+    totals = []
+    for frac in (0.5, 0.1, 0.01, 0.001):
+        eps = float(torch.quantile(live.double(), 1.0 - frac))
+        idx, cnt, _ = ops.select_blocks(q, summ, kv.prefix_lens, eps=eps)
+        idx, cnt = idx.cpu(), cnt.cpu()
+        disagree = 0
+        for b, (osum, terms, _, _) in enumerate(per_seq):
+            want_mask = orc.select_threshold(terms["score"], osum.counts, eps)
+            for h in range(cfg.n_kv_heads):
+                want = set(want_mask[h].nonzero().flatten().tolist())
+                got = idx[b, h, : int(cnt[b, h])].tolist()
+                assert got == sorted(got) and len(set(got)) == len(got)
+                sc = terms["score"][h]
+                near = set(((sc - eps).abs() <= 2e-4 * sc.abs() + 1e-8).nonzero().flatten().tolist())
+                assert set(got) ^ want <= near, f"quantile {frac}: seq {b} head {h}"
+                disagree += len(set(got) ^ want)
+        assert disagree <= max(1, live.numel() // 1000)
+        totals.append(int(cnt.sum()))
+    assert totals == sorted(totals, reverse=True)
+
+
 @pytest.mark.parametrize("rep_mode", ["sparse_only", "hybrid"])
 @pytest.mark.parametrize("n_splits", [1, 3])
 def test_attention_output(bundle, rep_mode, n_splits):
